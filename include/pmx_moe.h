@@ -1,0 +1,144 @@
+/*
+ * pmx_moe.h -- C ABI of the B200 (sm_100a) implementation of the OPMX
+ * mixture-of-experts inference path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, it is a cudaStream_t / CUstream), launches on that stream
+ * and returns without synchronising the host.  Return value: PMX_OK (0) or a
+ * negative pmx_status; pmx_moe_last_error() gives the text of the last failure
+ * on the calling thread.  Nothing here allocates or frees device memory; the
+ * caller provides the outputs and, where stated, a workspace whose size the
+ * matching *_workspace_bytes() function returns.  Entry points keep no state
+ * between calls (apart from per-device lookups cached on first use), so they
+ * can be called from several host threads and captured in CUDA graphs.
+ *
+ * Tensors are dense, row-major, innermost dimension contiguous.  "T1" is the
+ * activation type selected by `dtype`.  File:line citations name the OPMX
+ * reference operator each entry point replaces.
+ */
+#ifndef PMX_MOE_H_
+#define PMX_MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PMX_MOE_ABI_VERSION 1
+
+/* element type of activations and weights */
+typedef enum pmx_dtype {
+  PMX_DTYPE_F16 = 0,
+  PMX_DTYPE_BF16 = 1,
+  PMX_DTYPE_F32 = 2
+} pmx_dtype;
+
+typedef enum pmx_status {
+  PMX_OK = 0,
+  PMX_ERR_INVALID_ARGUMENT = -1, /* null pointer, non-positive size, k > E ... */
+  PMX_ERR_UNSUPPORTED = -2,      /* shape or dtype outside what the kernels cover */
+  PMX_ERR_ALIGNMENT = -3,        /* a pointer or row pitch is not aligned as required */
+  PMX_ERR_WORKSPACE = -4,        /* workspace missing or too small */
+  PMX_ERR_CUDA = -5,             /* a CUDA runtime / driver call failed */
+  PMX_ERR_DEVICE_CHECK = -6      /* a kernel recorded a failed self-check (bounded wait ran out) */
+} pmx_status;
+
+/* what the grouped linear applies to the accumulator before storing */
+typedef enum pmx_epilogue {
+  PMX_EPILOGUE_NONE = 0,  /* Y = X W^T (+ B) */
+  PMX_EPILOGUE_SWIGLU = 1 /* W holds [gate rows ; up rows]; Y = up * gate * sigmoid(beta * gate) */
+} pmx_epilogue;
+
+/* which grouped-GEMM kernel to run (PMX_GEMM_AUTO picks from shape and dtype) */
+typedef enum pmx_gemm_kernel {
+  PMX_GEMM_AUTO = 0,
+  PMX_GEMM_TC_TOKENS_M = 1,  /* tcgen05: tokens on the MMA M dimension (prefill shape) */
+  PMX_GEMM_TC_WEIGHTS_M = 2, /* tcgen05: weight rows on MMA M, tokens on MMA N (decode shape) */
+  PMX_GEMM_SIMT = 3          /* CUDA-core kernel, exact fp32 arithmetic (the only one for fp32) */
+} pmx_gemm_kernel;
+
+/* optional tiling override for pmx_moe_grouped_linear; zero fields mean "choose" */
+typedef struct pmx_gemm_plan {
+  int32_t kernel;       /* pmx_gemm_kernel */
+  int32_t tile_feat;    /* output features per tile */
+  int32_t tile_tok;     /* token rows per tile */
+  int32_t split_k;      /* number of K slices accumulated through the fp32 workspace */
+  int32_t stages;       /* shared-memory pipeline depth */
+  int32_t max_ctas;     /* cap on the persistent grid (0 = number of SMs) */
+} pmx_gemm_plan;
+
+int pmx_moe_abi_version(void);
+const char* pmx_moe_last_error(void);
+const char* pmx_moe_status_string(int status);
+
+/*
+ * moe_select -- replaces MoeSelect.forward, torch_function/MoeSelect.py:36-64.
+ *   x        [T,H]  T1        scores   [T,E] T1
+ *   x_expand_permute [T*k,H] T1   rows grouped by expert, stable in slot order t*k+j
+ *   expert_weights   [T,k]  T1    softmax over the k kept logits, descending
+ *   invert_permutation [T,k] int64  row of x_expand_permute holding slot t*k+j
+ *   expert_offset    [E+1]  int64   prefix sum of rows per expert
+ * Ranking rule: higher score first, lower expert index among equal scores.
+ * Workspace: pmx_moe_select_workspace_bytes(T,E,k) bytes, 16-byte aligned.
+ */
+size_t pmx_moe_select_workspace_bytes(int64_t T, int32_t E, int32_t k);
+int pmx_moe_select(const void* x, const void* scores, void* x_expand_permute,
+                   void* expert_weights, int64_t* invert_permutation,
+                   int64_t* expert_offset, int64_t T, int64_t H, int32_t E,
+                   int32_t k, int32_t dtype, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/*
+ * Grouped expert linear -- replaces the per-expert F.linear loops of
+ * MoeColumnParallelLinear.forward (torch_function/MoeColumnParallelLinear.py:58-69)
+ * and MoeRowParallelLinear.forward (torch_function/MoeRowParallelLinear.py:44-55):
+ *   y[r,:] = x[r,:] . w[e]^T (+ bias[e])   for expert_offset[e] <= r < expert_offset[e+1]
+ *   x [M,K] T1, w [E,N,K] T1 (K contiguous), bias [E,N] T1 or NULL, expert_offset [E+1] int64
+ *   y [M,N] T1, or [M,N/2] T1 with PMX_EPILOGUE_SWIGLU (SwiGLU.forward,
+ *   torch_function/SwiGLU.py:15-16, applied to the accumulator: rows [0,N/2) of
+ *   w[e] are the gate projection, rows [N/2,N) the up projection).
+ * zero_outside != 0 also writes zeros to rows outside [expert_offset[0],
+ * expert_offset[E]) as the reference's zero-initialised output has them.
+ * Collectives (all-reduce / all-gather of the reference ops) stay with the caller.
+ * plan may be NULL.  Workspace: pmx_moe_grouped_linear_workspace_bytes(...).
+ */
+size_t pmx_moe_grouped_linear_workspace_bytes(int64_t M, int64_t N, int64_t K,
+                                              int32_t E, int32_t dtype,
+                                              int32_t epilogue,
+                                              const pmx_gemm_plan* plan);
+int pmx_moe_grouped_linear(const void* x, const int64_t* expert_offset,
+                           const void* w, const void* bias, void* y, int64_t M,
+                           int64_t N, int64_t K, int32_t E, int32_t dtype,
+                           int32_t epilogue, float beta, int32_t zero_outside,
+                           const pmx_gemm_plan* plan, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/* Reads back (synchronising `stream`) the self-check record a grouped-linear
+ * launch left in its workspace: out[0] = 0 if clean, else a code; out[1..3] =
+ * where it happened.  Returns PMX_ERR_DEVICE_CHECK if a check failed. */
+int pmx_moe_grouped_linear_check(const void* workspace, int32_t out[4], void* stream);
+
+/* swiglu -- SwiGLU.forward, torch_function/SwiGLU.py:15-16.  x [M,D] -> y [M,D/2],
+ * y = x[:,D/2:] * x[:,:D/2] * sigmoid(beta * x[:,:D/2]). */
+int pmx_swiglu(const void* x, void* y, int64_t M, int64_t D, float beta,
+               int32_t dtype, void* stream);
+
+/* silu -- SiLU.forward, torch_function/SiLU.py:18-21.  y = silu(x) (* gate), n elements;
+ * gate may be NULL. */
+int pmx_silu(const void* x, const void* gate, void* y, int64_t n, int32_t dtype,
+             void* stream);
+
+/* moe_reduce -- MoeReduce.forward, torch_function/MoeReduce.py:23-25.
+ *   y [T*k,N] T1, expert_weights [T,k] T1, invert_permutation [T,k] int64
+ *   out[t,:] = sum_j expert_weights[t,j] * y[invert_permutation[t,j],:]   [T,N] T1
+ * accumulated in fp32, rounded once. */
+int pmx_moe_reduce(const void* y, const void* expert_weights,
+                   const int64_t* invert_permutation, void* out, int64_t T,
+                   int32_t k, int64_t N, int32_t dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PMX_MOE_H_ */

@@ -1,0 +1,168 @@
+// extern "C" entry points declared in include/pmx_moe.h: argument checks,
+// kernel choice, error text.  No torch types, no allocation, no host sync.
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace pmx {
+
+namespace {
+thread_local char g_error[512] = "";
+}
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return PMX_OK;
+  return fail(PMX_ERR_CUDA, "CUDA error %d (%s) from %s", (int)e, cudaGetErrorString(e), what);
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+namespace {
+
+struct LinearChoice {
+  bool tc;
+  TcPlan plan;
+};
+
+int choose_linear(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue,
+                  const pmx_gemm_plan* user, LinearChoice* c) {
+  if (M <= 0 || N <= 0 || K <= 0 || E <= 0)
+    return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear: M, N, K, E must be positive (M=%lld N=%lld K=%lld E=%d)", (long long)M, (long long)N, (long long)K, E);
+  if (dtype != PMX_DTYPE_F16 && dtype != PMX_DTYPE_BF16 && dtype != PMX_DTYPE_F32)
+    return fail(PMX_ERR_UNSUPPORTED, "grouped_linear: unknown dtype %d", dtype);
+  if (epilogue != PMX_EPILOGUE_NONE && epilogue != PMX_EPILOGUE_SWIGLU)
+    return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear: unknown epilogue %d", epilogue);
+  if (epilogue == PMX_EPILOGUE_SWIGLU && (N & 1))
+    return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear: SwiGLU needs an even N");
+  const int want = user ? user->kernel : PMX_GEMM_AUTO;
+  c->tc = false;
+  if (want == PMX_GEMM_SIMT) return PMX_OK;
+  c->tc = plan_gemm_tc(M, N, K, E, dtype, epilogue, user, &c->plan);
+  if (!c->tc && want != PMX_GEMM_AUTO)
+    return fail(PMX_ERR_UNSUPPORTED, "grouped_linear: the requested tensor-core plan does not cover this shape/dtype");
+  return PMX_OK;
+}
+
+}  // namespace
+}  // namespace pmx
+
+using namespace pmx;
+
+extern "C" {
+
+int pmx_moe_abi_version(void) { return PMX_MOE_ABI_VERSION; }
+
+const char* pmx_moe_last_error(void) { return g_error; }
+
+const char* pmx_moe_status_string(int status) {
+  switch (status) {
+    case PMX_OK: return "ok";
+    case PMX_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case PMX_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case PMX_ERR_ALIGNMENT: return "misaligned pointer or pitch";
+    case PMX_ERR_WORKSPACE: return "workspace missing or too small";
+    case PMX_ERR_CUDA: return "CUDA call failed";
+    case PMX_ERR_DEVICE_CHECK: return "device-side self-check failed";
+  }
+  return "unknown status";
+}
+
+size_t pmx_moe_select_workspace_bytes(int64_t T, int32_t E, int32_t k) {
+  return select_workspace_bytes(T, E, k);
+}
+
+int pmx_moe_select(const void* x, const void* scores, void* x_expand_permute, void* expert_weights,
+                   int64_t* invert_permutation, int64_t* expert_offset, int64_t T, int64_t H,
+                   int32_t E, int32_t k, int32_t dtype, void* workspace, size_t workspace_bytes,
+                   void* stream) {
+  return launch_select(x, scores, x_expand_permute, expert_weights, invert_permutation, expert_offset,
+                       T, H, E, k, dtype, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+size_t pmx_moe_grouped_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t E,
+                                              int32_t dtype, int32_t epilogue,
+                                              const pmx_gemm_plan* plan) {
+  LinearChoice c;
+  if (choose_linear(M, N, K, E, dtype, epilogue, plan, &c) != PMX_OK) return 0;
+  if (!c.tc) return kStatusBytes;
+  return gemm_tc_workspace_bytes(M, epilogue == PMX_EPILOGUE_SWIGLU ? N / 2 : N, c.plan);
+}
+
+int pmx_moe_grouped_linear(const void* x, const int64_t* expert_offset, const void* w,
+                           const void* bias, void* y, int64_t M, int64_t N, int64_t K, int32_t E,
+                           int32_t dtype, int32_t epilogue, float beta, int32_t zero_outside,
+                           const pmx_gemm_plan* plan, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+  if (!x || !expert_offset || !w || !y) return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear: null pointer");
+  LinearChoice c;
+  int st = choose_linear(M, N, K, E, dtype, epilogue, plan, &c);
+  if (st != PMX_OK) return st;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int64_t n_out = epilogue == PMX_EPILOGUE_SWIGLU ? N / 2 : N;
+  if (!c.tc) {
+    if (!workspace || workspace_bytes < kStatusBytes)
+      return fail(PMX_ERR_WORKSPACE, "grouped_linear: workspace of %zu bytes needed, %zu given", kStatusBytes, workspace_bytes);
+    PMX_CUDA_OK(cudaMemsetAsync(workspace, 0, 16, s));
+    st = launch_gemm_simt(x, expert_offset, w, bias, y, M, N, K, E, dtype, epilogue, beta, s);
+    if (st != PMX_OK) return st;
+    if (zero_outside) return launch_zero_outside(y, expert_offset, M, n_out, E, dtype, s);
+    return PMX_OK;
+  }
+  st = launch_gemm_tc(x, expert_offset, w, bias, y, M, N, K, E, dtype, epilogue, beta, c.plan,
+                      workspace, workspace_bytes, s);
+  if (st != PMX_OK) return st;
+  // with split-K the final sum already writes zeros to rows no expert owns
+  if (zero_outside && c.plan.split_k == 1) return launch_zero_outside(y, expert_offset, M, n_out, E, dtype, s);
+  return PMX_OK;
+}
+
+int pmx_moe_grouped_linear_check(const void* workspace, int32_t out[4], void* stream) {
+  if (!workspace || !out) return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear_check: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  PMX_CUDA_OK(cudaMemcpyAsync(out, workspace, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  PMX_CUDA_OK(cudaStreamSynchronize(s));
+  if (out[0] != 0)
+    return fail(PMX_ERR_DEVICE_CHECK, "grouped_linear: a bounded wait ran out (role %d, work item %d, CTA %d)", out[1], out[2], out[3]);
+  return PMX_OK;
+}
+
+int pmx_swiglu(const void* x, void* y, int64_t M, int64_t D, float beta, int32_t dtype, void* stream) {
+  return launch_swiglu(x, y, M, D, beta, dtype, (cudaStream_t)stream);
+}
+
+int pmx_silu(const void* x, const void* gate, void* y, int64_t n, int32_t dtype, void* stream) {
+  return launch_silu(x, gate, y, n, dtype, (cudaStream_t)stream);
+}
+
+int pmx_moe_reduce(const void* y, const void* expert_weights, const int64_t* invert_permutation,
+                   void* out, int64_t T, int32_t k, int64_t N, int32_t dtype, void* stream) {
+  return launch_reduce(y, expert_weights, invert_permutation, out, T, k, N, dtype, (cudaStream_t)stream);
+}
+
+}  // extern "C"

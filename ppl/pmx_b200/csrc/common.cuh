@@ -1,0 +1,109 @@
+// Shared helpers for the MoE kernels: element-type traits, 128-bit vector
+// access, error reporting for the C ABI.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../../include/pmx_moe.h"
+
+namespace pmx {
+
+// ---- error text kept per host thread for pmx_moe_last_error() ---------------
+void set_error(const char* fmt, ...);
+int fail(int status, const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+int sm_count();  // SMs of the current device (cached per device)
+
+#define PMX_CUDA_OK(expr)                                 \
+  do {                                                    \
+    int _s = ::pmx::check_cuda((expr), #expr);            \
+    if (_s != PMX_OK) return _s;                          \
+  } while (0)
+
+// ---- element traits ----------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<__half> {
+  static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float v) { return v; }
+};
+
+// number of elements in one 16-byte vector
+template <typename T> constexpr int kVec = 16 / sizeof(T);
+
+// 16 bytes of T as floats and back
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& v, float (&f)[kVec<T>]) {
+  const T* p = reinterpret_cast<const T*>(&v);
+#pragma unroll
+  for (int i = 0; i < kVec<T>; ++i) f[i] = Elem<T>::to_f(p[i]);
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack16(const float (&f)[kVec<T>]) {
+  uint4 v;
+  T* p = reinterpret_cast<T*>(&v);
+#pragma unroll
+  for (int i = 0; i < kVec<T>; ++i) p[i] = Elem<T>::from_f(f[i]);
+  return v;
+}
+
+__device__ __forceinline__ uint4 ld_nc16(const void* p) {
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+__device__ __forceinline__ float swiglu_f(float gate, float up, float beta) {
+  // up * gate * sigmoid(beta * gate)
+  return up * gate / (1.0f + __expf(-beta * gate));
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- kernels' host launchers (one translation unit each) ---------------------
+int launch_select(const void* x, const void* scores, void* xp, void* w, int64_t* inv,
+                  int64_t* off, int64_t T, int64_t H, int E, int k, int dtype, void* ws,
+                  size_t ws_bytes, cudaStream_t s);
+size_t select_workspace_bytes(int64_t T, int E, int k);
+
+int launch_swiglu(const void* x, void* y, int64_t M, int64_t D, float beta, int dtype, cudaStream_t s);
+int launch_silu(const void* x, const void* gate, void* y, int64_t n, int dtype, cudaStream_t s);
+int launch_reduce(const void* y, const void* w, const int64_t* inv, void* out, int64_t T, int k,
+                  int64_t N, int dtype, cudaStream_t s);
+int launch_zero_outside(void* y, const int64_t* off, int64_t M, int64_t n_out, int E, int dtype,
+                        cudaStream_t s);
+int launch_splitk_finish(const float* partial, const int64_t* off, const void* bias, void* y,
+                         int64_t M, int64_t n_out, int E, int split, int dtype, cudaStream_t s);
+
+int launch_gemm_simt(const void* x, const int64_t* off, const void* w, const void* bias, void* y,
+                     int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue, float beta,
+                     cudaStream_t s);
+
+struct TcPlan {
+  int kernel;      // PMX_GEMM_TC_TOKENS_M or PMX_GEMM_TC_WEIGHTS_M
+  int tile_feat;   // output features per tile
+  int tile_tok;    // token rows per tile
+  int split_k;
+  int stages;
+  int max_ctas;
+};
+// Fills `plan` for the tensor-core kernel or returns false when the shape is
+// outside what it covers (the caller then uses the CUDA-core kernel).
+bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue,
+                  const pmx_gemm_plan* user, TcPlan* plan);
+size_t gemm_tc_workspace_bytes(int64_t M, int64_t n_out, const TcPlan& plan);
+int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void* bias, void* y,
+                   int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue, float beta,
+                   const TcPlan& plan, void* ws, size_t ws_bytes, cudaStream_t s);
+
+constexpr size_t kStatusBytes = 256;  // head of every grouped-linear workspace
+
+}  // namespace pmx

@@ -1,0 +1,230 @@
+// HBM-bound kernels around the expert GEMMs: the top-k weighted combine
+// (moe_reduce), the stand-alone SwiGLU / SiLU activations, the zero fill of
+// rows no expert owns and the final sum of split-K partial results.
+// All of them move 16 bytes per thread access and accumulate in fp32.
+#include "common.cuh"
+
+namespace pmx {
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int grid_for(int64_t work_items) {
+  int64_t blocks = ceil_div(work_items, kThreads);
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+// out[t,:] = sum_j w[t,j] * y[inv[t,j],:]      (MoeReduce.py:23-25)
+template <typename T, bool VEC>
+__global__ void reduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
+                              const int64_t* __restrict__ inv, T* __restrict__ out, int64_t Tn,
+                              int k, int64_t N) {
+  constexpr int V = VEC ? kVec<T> : 1;
+  const int64_t chunks = N / V;
+  const int64_t total = Tn * chunks;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / chunks, c = i - t * chunks;
+    float acc[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[v] = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const int64_t r = inv[t * k + j];
+      const float wj = Elem<T>::to_f(w[t * k + j]);
+      if (VEC) {
+        float f[kVec<T>];
+        unpack16<T>(ld_nc16(y + r * N + c * V), f);
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] = fmaf(wj, f[v], acc[v]);
+      } else {
+        acc[0] = fmaf(wj, Elem<T>::to_f(y[r * N + c]), acc[0]);
+      }
+    }
+    if (VEC) {
+      float f[kVec<T>];
+#pragma unroll
+      for (int v = 0; v < V; ++v) f[v] = acc[v];
+      *reinterpret_cast<uint4*>(out + t * N + c * V) = pack16<T>(f);
+    } else {
+      out[t * N + c] = Elem<T>::from_f(acc[0]);
+    }
+  }
+}
+
+// y[m, j] = x[m, D/2 + j] * x[m, j] * sigmoid(beta * x[m, j])    (SwiGLU.py:15-16)
+template <typename T, bool VEC>
+__global__ void swiglu_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int64_t D,
+                              float beta) {
+  constexpr int V = VEC ? kVec<T> : 1;
+  const int64_t half = D / 2, chunks = half / V, total = M * chunks;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / chunks, c = i - m * chunks;
+    if (VEC) {
+      float a[kVec<T>], g[kVec<T>];
+      unpack16<T>(ld_nc16(x + m * D + c * V), a);
+      unpack16<T>(ld_nc16(x + m * D + half + c * V), g);
+#pragma unroll
+      for (int v = 0; v < V; ++v) a[v] = g[v] * a[v] / (1.0f + expf(-beta * a[v]));
+      *reinterpret_cast<uint4*>(y + m * half + c * V) = pack16<T>(a);
+    } else {
+      const float a = Elem<T>::to_f(x[m * D + c]), g = Elem<T>::to_f(x[m * D + half + c]);
+      y[m * half + c] = Elem<T>::from_f(g * a / (1.0f + expf(-beta * a)));
+    }
+  }
+}
+
+// y = silu(x) (* gate)    (SiLU.py:18-21)
+template <typename T, bool VEC>
+__global__ void silu_kernel(const T* __restrict__ x, const T* __restrict__ gate, T* __restrict__ y,
+                            int64_t n) {
+  constexpr int V = VEC ? kVec<T> : 1;
+  const int64_t total = n / V;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    if (VEC) {
+      float a[kVec<T>], g[kVec<T>];
+      unpack16<T>(ld_nc16(x + i * V), a);
+      if (gate) unpack16<T>(ld_nc16(gate + i * V), g);
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        a[v] = a[v] / (1.0f + expf(-a[v]));
+        if (gate) a[v] *= g[v];
+      }
+      *reinterpret_cast<uint4*>(y + i * V) = pack16<T>(a);
+    } else {
+      float a = Elem<T>::to_f(x[i]);
+      a = a / (1.0f + expf(-a));
+      if (gate) a *= Elem<T>::to_f(gate[i]);
+      y[i] = Elem<T>::from_f(a);
+    }
+  }
+}
+
+// rows outside [off[0], off[E]) <- 0   (the zero-initialised output of
+// MoeColumnParallelLinear.py:59 / MoeRowParallelLinear.py:45)
+template <typename T>
+__global__ void zero_outside_kernel(T* __restrict__ y, const int64_t* __restrict__ off, int64_t M,
+                                    int64_t n_out, int E) {
+  int64_t lo = off[0], hi = off[E];
+  lo = lo < 0 ? 0 : (lo > M ? M : lo);
+  hi = hi < lo ? lo : (hi > M ? M : hi);
+  const int64_t head = lo * n_out, tail = (M - hi) * n_out;
+  const T zero = Elem<T>::from_f(0.f);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < head + tail;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t idx = i < head ? i : hi * n_out + (i - head);
+    y[idx] = zero;
+  }
+}
+
+// y[m,:] = cast(sum_s partial[s][m][:] (+ bias[e(m)])); rows no expert owns <- 0
+template <typename T>
+__global__ void splitk_finish_kernel(const float* __restrict__ partial,
+                                     const int64_t* __restrict__ off, const T* __restrict__ bias,
+                                     T* __restrict__ y, int64_t M, int64_t n_out, int E, int split) {
+  const int64_t chunks = n_out / 4, total = M * chunks;
+  const int64_t lo = off[0], hi = off[E];
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / chunks, c = (i - m * chunks) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (m >= lo && m < hi) {
+      for (int s = 0; s < split; ++s) {
+        const float4 p = *reinterpret_cast<const float4*>(partial + ((int64_t)s * M + m) * n_out + c);
+        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+      }
+      if (bias) {
+        int e = 0;
+        while (e + 1 < E && off[e + 1] <= m) ++e;
+        const T* b = bias + (int64_t)e * n_out + c;
+        acc.x += Elem<T>::to_f(b[0]); acc.y += Elem<T>::to_f(b[1]);
+        acc.z += Elem<T>::to_f(b[2]); acc.w += Elem<T>::to_f(b[3]);
+      }
+    }
+    T* o = y + m * n_out + c;
+    o[0] = Elem<T>::from_f(acc.x); o[1] = Elem<T>::from_f(acc.y);
+    o[2] = Elem<T>::from_f(acc.z); o[3] = Elem<T>::from_f(acc.w);
+  }
+}
+
+#define PMX_DISPATCH_DTYPE(dtype, what, ...)                                       \
+  switch (dtype) {                                                                 \
+    case PMX_DTYPE_F16: { using T = __half; __VA_ARGS__ } break;                   \
+    case PMX_DTYPE_BF16: { using T = __nv_bfloat16; __VA_ARGS__ } break;           \
+    case PMX_DTYPE_F32: { using T = float; __VA_ARGS__ } break;                    \
+    default: return fail(PMX_ERR_UNSUPPORTED, what ": unknown dtype %d", dtype);   \
+  }
+
+}  // namespace
+
+int launch_reduce(const void* y, const void* w, const int64_t* inv, void* out, int64_t Tn, int k,
+                  int64_t N, int dtype, cudaStream_t s) {
+  if (!y || !w || !inv || !out) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_reduce: null pointer");
+  if (Tn <= 0 || k <= 0 || N <= 0) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_reduce: T, k, N must be positive");
+  PMX_DISPATCH_DTYPE(dtype, "moe_reduce", {
+    const bool vec = N % kVec<T> == 0 && aligned16(y) && aligned16(out);
+    const int64_t items = Tn * (vec ? N / kVec<T> : N);
+    if (vec)
+      reduce_kernel<T, true><<<grid_for(items), kThreads, 0, s>>>((const T*)y, (const T*)w, inv, (T*)out, Tn, k, N);
+    else
+      reduce_kernel<T, false><<<grid_for(items), kThreads, 0, s>>>((const T*)y, (const T*)w, inv, (T*)out, Tn, k, N);
+  })
+  PMX_CUDA_OK(cudaGetLastError());
+  return PMX_OK;
+}
+
+int launch_swiglu(const void* x, void* y, int64_t M, int64_t D, float beta, int dtype, cudaStream_t s) {
+  if (!x || !y) return fail(PMX_ERR_INVALID_ARGUMENT, "swiglu: null pointer");
+  if (M <= 0 || D <= 0 || (D & 1)) return fail(PMX_ERR_INVALID_ARGUMENT, "swiglu: M>0 and an even D>0 required");
+  PMX_DISPATCH_DTYPE(dtype, "swiglu", {
+    const bool vec = (D / 2) % kVec<T> == 0 && aligned16(x) && aligned16(y);
+    const int64_t items = M * (vec ? D / 2 / kVec<T> : D / 2);
+    if (vec)
+      swiglu_kernel<T, true><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (T*)y, M, D, beta);
+    else
+      swiglu_kernel<T, false><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (T*)y, M, D, beta);
+  })
+  PMX_CUDA_OK(cudaGetLastError());
+  return PMX_OK;
+}
+
+int launch_silu(const void* x, const void* gate, void* y, int64_t n, int dtype, cudaStream_t s) {
+  if (!x || !y) return fail(PMX_ERR_INVALID_ARGUMENT, "silu: null pointer");
+  if (n <= 0) return fail(PMX_ERR_INVALID_ARGUMENT, "silu: n must be positive");
+  PMX_DISPATCH_DTYPE(dtype, "silu", {
+    const bool vec = n % kVec<T> == 0 && aligned16(x) && aligned16(y) && (!gate || aligned16(gate));
+    const int64_t items = vec ? n / kVec<T> : n;
+    if (vec)
+      silu_kernel<T, true><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (const T*)gate, (T*)y, n);
+    else
+      silu_kernel<T, false><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (const T*)gate, (T*)y, n);
+  })
+  PMX_CUDA_OK(cudaGetLastError());
+  return PMX_OK;
+}
+
+int launch_zero_outside(void* y, const int64_t* off, int64_t M, int64_t n_out, int E, int dtype,
+                        cudaStream_t s) {
+  PMX_DISPATCH_DTYPE(dtype, "grouped_linear", {
+    zero_outside_kernel<T><<<sm_count(), kThreads, 0, s>>>((T*)y, off, M, n_out, E);
+  })
+  PMX_CUDA_OK(cudaGetLastError());
+  return PMX_OK;
+}
+
+int launch_splitk_finish(const float* partial, const int64_t* off, const void* bias, void* y,
+                         int64_t M, int64_t n_out, int E, int split, int dtype, cudaStream_t s) {
+  if (n_out % 4) return fail(PMX_ERR_UNSUPPORTED, "grouped_linear: split-K needs N %% 4 == 0");
+  PMX_DISPATCH_DTYPE(dtype, "grouped_linear", {
+    splitk_finish_kernel<T><<<grid_for(M * n_out / 4), kThreads, 0, s>>>(partial, off, (const T*)bias,
+                                                                         (T*)y, M, n_out, E, split);
+  })
+  PMX_CUDA_OK(cudaGetLastError());
+  return PMX_OK;
+}
+
+}  // namespace pmx

@@ -1,0 +1,650 @@
+// Grouped expert GEMM on the 5th-generation tensor cores (sm_100a):
+//   y[r,:] = x[r,:] . w[e]^T (+ bias[e])    for rows r owned by expert e,
+// optionally with SwiGLU applied to the fp32 accumulator before the store.
+//
+// One persistent CTA per SM, three roles:
+//   warp 0   : TMA producer.  cp.async.bulk.tensor (128-byte swizzle) of the
+//              token tile and the weight tile of every k-block into a ring of
+//              shared-memory stages, completion on mbarriers.
+//   warp 1   : owns tensor memory and issues tcgen05.mma (kind::f16, fp32
+//              accumulation in TMEM); tcgen05.commit releases ring stages and
+//              publishes finished accumulators.
+//   warps 2-5: epilogue.  tcgen05.ld of the accumulator, bias / SwiGLU / cast,
+//              predicated global stores.  Two accumulator buffers in TMEM let
+//              the epilogue of one tile overlap the MMAs of the next.
+//
+// Work items are (expert, token tile, feature tile, K slice).  The list is
+// derived on the device from expert_offset, so there is no host
+// synchronisation and the grid does not depend on the routing.  Items are
+// ordered expert-major with the token tile fastest, so the CTAs running at
+// one time share weight tiles through L2 and each weight byte leaves HBM once.
+//
+// Two operand assignments (template MODE):
+//   0  tokens on MMA-M (128 rows), weight rows on MMA-N (up to 256): prefill.
+//   1  weight rows on MMA-M (128), tokens on MMA-N (16..256): decode, where an
+//      expert owns few rows and the weights are streamed once from HBM.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out records where in
+// the status words of the workspace, raises a CTA-wide abort flag and all
+// roles drain and leave through the common exit (which frees the TMEM).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace pmx {
+namespace {
+
+constexpr int kBlockK = 64;      // 16-bit elements per k-block = one 128-byte swizzle row
+constexpr int kUmmaK = 16;       // K of one tcgen05.mma with 16-bit operands
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;   // whole tensor memory: 2 accumulator buffers x 256 columns
+constexpr int kAccStride = 256;
+constexpr int kMaxExperts = 1024;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+struct Params {
+  const int64_t* off;   // [E+1]
+  void* y;              // [M, n_out] T   or fp32 partials [split][M][n_out]
+  const void* bias;     // [E, N] T or null
+  int* status;          // 4 ints: code, role, item, aux
+  int M, N, K, E;
+  int n_out;            // N, or N/2 with SwiGLU
+  int tile_tok, tile_feat;
+  int feat_tiles;
+  int split_k, kb_per_split, kblocks;
+  int stages;
+  float beta;
+};
+
+// ----------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint64_t* bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]^T, 16-bit operands, fp32 accumulate
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// mbarrier arrives once all tcgen05.mma issued so far by this thread are done
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// 32 lanes x 16 consecutive fp32 columns: thread i gets lane (base lane + i)
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes,
+// stored with the 128-byte swizzle (8-row groups 1024 bytes apart).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr >> 4) & 0x3FFF);  // start address / 16
+  d |= static_cast<uint64_t>(1) << 16;                // leading byte offset (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;        // stride between 8-row groups / 16
+  d |= static_cast<uint64_t>(1) << 46;                // descriptor version of sm_100
+  d |= static_cast<uint64_t>(2) << 61;                // 128-byte swizzle
+  return d;
+}
+
+// tcgen05 instruction descriptor: fp32 accumulator, A and B of type T, both K-major
+template <typename T>
+__device__ __forceinline__ uint32_t make_idesc(int m, int n) {
+  const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+struct Shared {          // control block placed after the ring stages
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+// Bounded wait.  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool wait_barrier(uint64_t* bar, uint32_t parity, Shared* sh, int* status,
+                                             int role, int item) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 63u) == 0u) {
+      if (sh->abort) return false;
+      if (global_ns() - t0 > kWaitLimitNs) {
+        sh->abort = 1;
+        if (atomicCAS(status, 0, 1) == 0) {
+          status[1] = role;
+          status[2] = item;
+          status[3] = static_cast<int>(blockIdx.x);
+        }
+        return false;
+      }
+    }
+  }
+}
+
+struct Item {
+  int e, row0, row_end, f0, kb0, kb1, ks;
+};
+
+// Maps a work-item index to its tile.  `e` carries over between calls (items
+// are visited in increasing order).
+__device__ __forceinline__ void decode_item(int item, int& e, const int* s_off, const int* s_prefix,
+                                            const Params& p, Item& it) {
+  while (item >= s_prefix[e + 1]) ++e;
+  const int local = item - s_prefix[e];
+  const int rows = s_off[e + 1] - s_off[e];
+  const int ntt = (rows + p.tile_tok - 1) / p.tile_tok;
+  const int tok = local % ntt, fk = local / ntt;
+  const int ft = fk / p.split_k;
+  it.ks = fk - ft * p.split_k;
+  it.e = e;
+  it.row0 = s_off[e] + tok * p.tile_tok;
+  it.row_end = s_off[e + 1];
+  it.f0 = ft * p.tile_feat;
+  it.kb0 = it.ks * p.kb_per_split;
+  it.kb1 = min(p.kblocks, it.kb0 + p.kb_per_split);
+}
+
+template <typename T>
+__device__ __forceinline__ void store16(T* dst, const float (&v)[16]) {
+  // 16 consecutive outputs: two 16-byte stores
+  float a[8], b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { a[i] = v[i]; b[i] = v[8 + i]; }
+  reinterpret_cast<uint4*>(dst)[0] = pack16<T>(a);
+  reinterpret_cast<uint4*>(dst)[1] = pack16<T>(b);
+}
+
+template <typename T, int MODE, bool SWIGLU>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
+                       const __grid_constant__ CUtensorMap map_w, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tt = p.tile_tok, ft = p.tile_feat;
+  const int wrows = SWIGLU ? 2 * ft : ft;            // weight rows per stage
+  const uint32_t tok_bytes = tt * 128, w_bytes = wrows * 128;
+  const uint32_t stage_bytes = tok_bytes + w_bytes;
+  Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)p.stages * stage_bytes);
+  int* s_off = reinterpret_cast<int*>(sh + 1);       // [E+1] row offsets, clamped
+  int* s_prefix = s_off + (p.E + 1);                 // [E+1] first work item of each expert
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- set-up ---------------------------------------------------------------
+  for (int e = threadIdx.x; e <= p.E; e += blockDim.x) {
+    long long o = p.off[e];
+    s_off[e] = (int)(o < 0 ? 0 : (o > p.M ? p.M : o));
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < p.stages; ++i) {
+      mbar_init(&sh->full[i], 1);
+      mbar_init(&sh->empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh->acc_full[i], 1);
+      mbar_init(&sh->acc_empty[i], 4);
+    }
+    sh->abort = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < p.E; ++e) {
+      if (s_off[e + 1] < s_off[e]) s_off[e + 1] = s_off[e];  // keep it monotone
+      s_prefix[e] = acc;
+      const int rows = s_off[e + 1] - s_off[e];
+      acc += ((rows + tt - 1) / tt) * p.feat_tiles * p.split_k;
+    }
+    s_prefix[p.E] = acc;
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+  const int total_items = s_prefix[p.E];
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp == 0) {
+    // ========================= TMA producer =================================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int e = 0;
+      Item it;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        decode_item(item, e, s_off, s_prefix, p, it);
+        const int wrow = it.e * p.N + it.f0;
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
+          ok = wait_barrier(&sh->empty[stage], phase ^ 1u, sh, p.status, 0, item);
+          if (!ok) break;
+          mbar_expect_tx(&sh->full[stage], stage_bytes);
+          const uint32_t dst = smem_base + stage * stage_bytes;
+          tma_load_2d(dst, &map_x, &sh->full[stage], kb * kBlockK, it.row0);
+          tma_load_2d(dst + tok_bytes, &map_w, &sh->full[stage], kb * kBlockK, wrow);
+          if (SWIGLU)
+            tma_load_2d(dst + tok_bytes + ft * 128, &map_w, &sh->full[stage], kb * kBlockK,
+                        wrow + p.N / 2);
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // leave time for copies already in flight to land before the CTA exits
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ========================= MMA issuer ===================================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc<T>(128, MODE == 0 ? wrows : tt);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      int e = 0;
+      Item it;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        decode_item(item, e, s_off, s_prefix, p, it);
+        ok = wait_barrier(&sh->acc_empty[acc], acc_phase ^ 1u, sh, p.status, 1, item);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kAccStride;
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
+          ok = wait_barrier(&sh->full[stage], phase, sh, p.status, 2, item);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t tok_addr = smem_base + stage * stage_bytes;
+          const uint32_t w_addr = tok_addr + tok_bytes;
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            const uint32_t koff = kk * kUmmaK * 2;  // bytes inside the 128-byte row
+            const uint32_t accum = (kb > it.kb0 || kk > 0) ? 1u : 0u;
+            if (MODE == 0) {
+              umma_f16(d_tmem, smem_desc_sw128(tok_addr + koff), smem_desc_sw128(w_addr + koff), idesc, accum);
+            } else {
+              const uint64_t bdesc = smem_desc_sw128(tok_addr + koff);
+              umma_f16(d_tmem, smem_desc_sw128(w_addr + koff), bdesc, idesc, accum);
+              if (SWIGLU)
+                umma_f16(d_tmem + tt, smem_desc_sw128(w_addr + 128 * 128 + koff), bdesc, idesc, accum);
+            }
+          }
+          umma_commit(&sh->empty[stage]);  // stage reusable once these MMAs have read it
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&sh->acc_full[acc]);   // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ========================= epilogue (warps 2..5) ========================
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    int e = 0;
+    Item it;
+    bool ok = true;
+    const bool partial = p.split_k > 1;
+    T* y = reinterpret_cast<T*>(p.y);
+    float* yp = reinterpret_cast<float*>(p.y);
+    const T* bias = reinterpret_cast<const T*>(p.bias);
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      decode_item(item, e, s_off, s_prefix, p, it);
+      ok = wait_barrier(&sh->acc_full[acc], acc_phase, sh, p.status, 3, item);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * kAccStride + (static_cast<uint32_t>(q * 32) << 16);
+      if (MODE == 0) {
+        const int row = it.row0 + q * 32 + lane;
+        const bool row_ok = row < it.row_end;
+        const T* be = bias ? bias + (int64_t)it.e * p.N : nullptr;
+        for (int c = 0; c < ft; c += 16) {
+          float g[16], u[16];
+          __syncwarp();  // tcgen05.ld is warp-collective: keep the lanes together
+          tmem_ld16(taddr + c, g);
+          if (SWIGLU) tmem_ld16(taddr + ft + c, u);
+          tmem_wait_ld();
+          const int col = it.f0 + c;
+          if (col < p.n_out && row_ok) {
+            if (be) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (col + i < p.n_out) {
+                  g[i] += Elem<T>::to_f(be[col + i]);
+                  if (SWIGLU) u[i] += Elem<T>::to_f(be[p.n_out + col + i]);
+                }
+            }
+            if (SWIGLU) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) g[i] = swiglu_f(g[i], u[i], p.beta);
+            }
+            if (partial) {
+              float* dst = yp + ((int64_t)it.ks * p.M + row) * p.n_out + col;
+              if (col + 16 <= p.n_out) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  reinterpret_cast<float4*>(dst)[i] = make_float4(g[4 * i], g[4 * i + 1], g[4 * i + 2], g[4 * i + 3]);
+              } else {
+                for (int i = 0; i < 16 && col + i < p.n_out; ++i) dst[i] = g[i];
+              }
+            } else {
+              T* dst = y + (int64_t)row * p.n_out + col;
+              if (col + 16 <= p.n_out) {
+                store16<T>(dst, g);
+              } else {
+                for (int i = 0; i < 16 && col + i < p.n_out; ++i) dst[i] = Elem<T>::from_f(g[i]);
+              }
+            }
+          }
+        }
+      } else {
+        const int f = it.f0 + q * 32 + lane;  // output feature of this thread
+        const bool f_ok = f < p.n_out;
+        float bg = 0.f, bu = 0.f;
+        if (bias && f_ok) {
+          bg = Elem<T>::to_f(bias[(int64_t)it.e * p.N + f]);
+          if (SWIGLU) bu = Elem<T>::to_f(bias[(int64_t)it.e * p.N + p.n_out + f]);
+        }
+        for (int c = 0; c < tt; c += 16) {
+          if (it.row0 + c >= it.row_end) break;  // same for the whole warp
+          float g[16], u[16];
+          __syncwarp();
+          tmem_ld16(taddr + c, g);
+          if (SWIGLU) tmem_ld16(taddr + tt + c, u);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int row = it.row0 + c + i;
+            if (row < it.row_end && f_ok) {
+              float v = g[i] + bg;
+              if (SWIGLU) v = swiglu_f(v, u[i] + bu, p.beta);
+              if (partial)
+                yp[((int64_t)it.ks * p.M + row) * p.n_out + f] = v;
+              else
+                y[(int64_t)row * p.n_out + f] = Elem<T>::from_f(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // ---- common exit ------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ----------------------------------------------------------------------------- host side
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  }
+  return fn;
+}
+
+// 2-D map over a row-major [rows, cols] matrix of 16-bit elements; boxes of
+// [box_rows, 64] elements land in shared memory with the 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
+             int dtype) {
+  PFN_cuTensorMapEncodeTiled_v12000 fn = encode_fn();
+  if (!fn) return fail(PMX_ERR_CUDA, "grouped_linear: cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {kBlockK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == PMX_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PMX_ERR_CUDA, "grouped_linear: cuTensorMapEncodeTiled failed with code %d (rows=%llu cols=%llu box_rows=%u)", (int)r, (unsigned long long)rows, (unsigned long long)cols, box_rows);
+  return PMX_OK;
+}
+
+size_t smem_bytes_for(const TcPlan& plan, bool swiglu, int E) {
+  const size_t stage = (size_t)(plan.tile_tok + (swiglu ? 2 : 1) * plan.tile_feat) * 128;
+  return 1024 + stage * plan.stages + sizeof(Shared) + 2 * (size_t)(E + 1) * sizeof(int);
+}
+
+template <typename T, int MODE, bool SWIGLU>
+int launch_inst(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, int grid, size_t smem,
+                cudaStream_t s) {
+  auto kern = grouped_gemm_tc_kernel<T, MODE, SWIGLU>;
+  PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<grid, kThreads, smem, s>>>(mx, mw, p);
+  PMX_CUDA_OK(cudaGetLastError());
+  return PMX_OK;
+}
+
+int pow2_at_least(int64_t v, int lo, int hi) {
+  int r = lo;
+  while (r < v && r < hi) r <<= 1;
+  return r;
+}
+
+}  // namespace
+
+bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue,
+                  const pmx_gemm_plan* user, TcPlan* plan) {
+  const bool swiglu = epilogue == PMX_EPILOGUE_SWIGLU;
+  const int64_t n_out = swiglu ? N / 2 : N;
+  if (dtype != PMX_DTYPE_F16 && dtype != PMX_DTYPE_BF16) return false;
+  if (K % 8 || n_out % 8 || K < 8 || E > kMaxExperts) return false;
+  if (M >= (1ll << 31) || (int64_t)E * N >= (1ll << 31) || M * n_out >= (1ll << 40)) return false;
+  const int sms = sm_count();
+  TcPlan pl{};
+  const double avg_rows = (double)M / E;
+  pl.kernel = user && user->kernel ? user->kernel : (avg_rows >= 96.0 ? PMX_GEMM_TC_TOKENS_M : PMX_GEMM_TC_WEIGHTS_M);
+  if (pl.kernel != PMX_GEMM_TC_TOKENS_M && pl.kernel != PMX_GEMM_TC_WEIGHTS_M) return false;
+  if (pl.kernel == PMX_GEMM_TC_TOKENS_M) {
+    pl.tile_tok = 128;
+    const int ft_max = swiglu ? 128 : 256;
+    pl.tile_feat = user && user->tile_feat ? user->tile_feat : pow2_at_least(n_out, 16, ft_max);
+    if (pl.tile_feat % 16 || pl.tile_feat < 16 || pl.tile_feat > ft_max) return false;
+  } else {
+    pl.tile_feat = 128;
+    const int tt_max = swiglu ? 128 : 256;
+    const int64_t est = (int64_t)(avg_rows * 1.5) + 1;
+    pl.tile_tok = user && user->tile_tok ? user->tile_tok : pow2_at_least(est < M ? est : M, 16, tt_max);
+    if (pl.tile_tok % 16 || pl.tile_tok < 16 || pl.tile_tok > tt_max) return false;
+  }
+  const int kblocks = (int)ceil_div(K, kBlockK);
+  const int64_t feat_tiles = ceil_div(n_out, pl.tile_feat);
+  if (user && user->split_k) {
+    pl.split_k = user->split_k;
+  } else {
+    pl.split_k = 1;
+    if (!swiglu) {
+      // experts with at least one row (estimate) x token tiles each
+      const int64_t act = M < E ? M : E;
+      const int64_t tok_tiles = act * (int64_t)ceil_div((int64_t)(avg_rows < 1 ? 1 : avg_rows), pl.tile_tok);
+      const int64_t items = tok_tiles * feat_tiles;
+      if (items < 2 * sms) {
+        int64_t want = ceil_div(2 * sms, items);
+        const int64_t cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
+        if (want > cap) want = cap;
+        if (want > 16) want = 16;
+        pl.split_k = (int)want;
+      }
+    }
+  }
+  if (pl.split_k < 1 || (swiglu && pl.split_k != 1)) return false;
+  if (pl.split_k > kblocks) pl.split_k = kblocks;
+  {
+    const int per = (int)ceil_div(kblocks, pl.split_k);
+    pl.split_k = (int)ceil_div(kblocks, per);  // no empty slice
+  }
+  if (pl.split_k > 1 && n_out % 4) return false;
+  const size_t stage = (size_t)(pl.tile_tok + (swiglu ? 2 : 1) * pl.tile_feat) * 128;
+  const size_t fixed = 1024 + sizeof(Shared) + 2 * (size_t)(E + 1) * sizeof(int);
+  int st = (int)((227 * 1024 - fixed) / stage);
+  if (st > 8) st = 8;
+  if (user && user->stages) st = user->stages < st ? user->stages : st;
+  if (st < 2) return false;
+  pl.stages = st;
+  pl.max_ctas = user && user->max_ctas ? user->max_ctas : sms;
+  *plan = pl;
+  return true;
+}
+
+size_t gemm_tc_workspace_bytes(int64_t M, int64_t n_out, const TcPlan& plan) {
+  size_t b = kStatusBytes;
+  if (plan.split_k > 1) b += (size_t)plan.split_k * M * n_out * sizeof(float);
+  return b;
+}
+
+int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void* bias, void* y,
+                   int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue, float beta,
+                   const TcPlan& plan, void* ws, size_t ws_bytes, cudaStream_t s) {
+  const bool swiglu = epilogue == PMX_EPILOGUE_SWIGLU;
+  const int64_t n_out = swiglu ? N / 2 : N;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(y))
+    return fail(PMX_ERR_ALIGNMENT, "grouped_linear: x, w and y must be 16-byte aligned");
+  const size_t need = gemm_tc_workspace_bytes(M, n_out, plan);
+  if (!ws || ws_bytes < need) return fail(PMX_ERR_WORKSPACE, "grouped_linear: workspace of %zu bytes needed, %zu given", need, ws_bytes);
+  if (!aligned16(ws)) return fail(PMX_ERR_ALIGNMENT, "grouped_linear: workspace must be 16-byte aligned");
+
+  CUtensorMap mx, mw;
+  int st = make_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint32_t)plan.tile_tok, dtype);
+  if (st != PMX_OK) return st;
+  st = make_map(&mw, w, (uint64_t)E * N, (uint64_t)K, (uint32_t)plan.tile_feat, dtype);
+  if (st != PMX_OK) return st;
+
+  Params p{};
+  p.off = off;
+  p.bias = plan.split_k > 1 ? nullptr : bias;  // with split-K the bias joins in the final sum
+  p.status = reinterpret_cast<int*>(ws);
+  p.y = plan.split_k > 1 ? reinterpret_cast<void*>(reinterpret_cast<char*>(ws) + kStatusBytes) : y;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.E = E;
+  p.n_out = (int)n_out;
+  p.tile_tok = plan.tile_tok;
+  p.tile_feat = plan.tile_feat;
+  p.feat_tiles = (int)ceil_div(n_out, plan.tile_feat);
+  p.kblocks = (int)ceil_div(K, kBlockK);
+  p.split_k = plan.split_k;
+  p.kb_per_split = (int)ceil_div(p.kblocks, plan.split_k);
+  p.stages = plan.stages;
+  p.beta = beta;
+
+  PMX_CUDA_OK(cudaMemsetAsync(ws, 0, 16, s));
+  const size_t smem = smem_bytes_for(plan, swiglu, E);
+  const int grid = plan.max_ctas;
+  const bool bf = dtype == PMX_DTYPE_BF16;
+  const int mode = plan.kernel == PMX_GEMM_TC_TOKENS_M ? 0 : 1;
+#define PMX_TC_LAUNCH(TT, MD, SW) st = launch_inst<TT, MD, SW>(mx, mw, p, grid, smem, s)
+  if (mode == 0) {
+    if (swiglu) { if (bf) PMX_TC_LAUNCH(__nv_bfloat16, 0, true); else PMX_TC_LAUNCH(__half, 0, true); }
+    else        { if (bf) PMX_TC_LAUNCH(__nv_bfloat16, 0, false); else PMX_TC_LAUNCH(__half, 0, false); }
+  } else {
+    if (swiglu) { if (bf) PMX_TC_LAUNCH(__nv_bfloat16, 1, true); else PMX_TC_LAUNCH(__half, 1, true); }
+    else        { if (bf) PMX_TC_LAUNCH(__nv_bfloat16, 1, false); else PMX_TC_LAUNCH(__half, 1, false); }
+  }
+#undef PMX_TC_LAUNCH
+  if (st != PMX_OK) return st;
+  if (plan.split_k > 1)
+    return launch_splitk_finish(reinterpret_cast<const float*>(p.y), off, bias, y, M, n_out, E, plan.split_k, dtype, s);
+  return PMX_OK;
+}
+
+}  // namespace pmx

@@ -1,0 +1,249 @@
+// moe_select on the GPU: router top-k + softmax, per-expert histogram, prefix
+// offsets, stable permutation and the 128-bit vectorised token gather.
+//
+// Replaces MoeSelect.forward (torch_function/MoeSelect.py:36-64).  Three
+// launches, no host synchronisation, no order-dependent atomics: the
+// permutation is a pure function of the scores, so every tensor-parallel rank
+// computes the same routing bit for bit.
+//
+//   route_count : one warp per token picks the k best experts (higher score
+//                 first, lower index among equals), writes the softmax of the k
+//                 kept logits and the expert ids; each block of `tpb` tokens
+//                 leaves its per-expert row count.
+//   scan        : exclusive prefix of the counts over blocks (per expert) and
+//                 over experts -> expert_offset.
+//   place_gather: every block re-walks its slots in order, ranks them inside
+//                 their expert with warp match/popc, writes
+//                 invert_permutation and copies each token row once from X to
+//                 its k destinations.
+#include "common.cuh"
+
+namespace pmx {
+namespace {
+
+constexpr int kMaxSlotsPerBlock = 2048;
+
+// Order-preserving map of a score to an unsigned key: -0 == +0, NaN on top.
+__device__ __forceinline__ uint32_t score_key(float s) {
+  if (s != s) return 0xFFFFFFFFu;
+  if (s == 0.0f) s = 0.0f;
+  uint32_t u = __float_as_uint(s);
+  return (u >> 31) ? ~u : (u | 0x80000000u);
+}
+
+template <typename T>
+__global__ void route_count_kernel(const T* __restrict__ scores, int64_t T_tokens, int E, int k,
+                                   int tpb, T* __restrict__ weights, int* __restrict__ ids,
+                                   int* __restrict__ block_counts) {
+  extern __shared__ int hist[];  // [E]
+  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int64_t t0 = (int64_t)blockIdx.x * tpb;
+  for (int tl = warp; tl < tpb; tl += nwarps) {
+    const int64_t t = t0 + tl;
+    if (t >= T_tokens) break;
+    const T* row = scores + t * E;
+    // composite key: score key in the high word, inverted expert index in the
+    // low word, so that a plain maximum prefers the lower index among equals
+    // and every expert has a distinct key.
+    unsigned long long prev = ~0ull;
+    float vmax = 0.f, denom = 0.f, myexp = 0.f;
+    int mysel = -1;
+    for (int j = 0; j < k; ++j) {
+      unsigned long long best = 0ull;
+      for (int e = lane; e < E; e += 32) {
+        unsigned long long key =
+            ((unsigned long long)score_key(Elem<T>::to_f(row[e])) << 32) | (uint32_t)(0x7FFFFFFF - e);
+        if (key < prev && key > best) best = key;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        unsigned long long other = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+        best = other > best ? other : best;
+      }
+      prev = best;
+      const int e_sel = 0x7FFFFFFF - (int)(uint32_t)(best & 0xFFFFFFFFull);
+      const float v = Elem<T>::to_f(row[e_sel]);
+      if (j == 0) vmax = v;
+      const float ex = expf(v - vmax);
+      denom += ex;
+      if (lane == j) {  // lane j keeps slot j (k <= 32)
+        myexp = ex;
+        mysel = e_sel;
+      }
+    }
+    if (lane < k) {
+      weights[t * k + lane] = Elem<T>::from_f(myexp / denom);
+      ids[t * k + lane] = mysel;
+      atomicAdd(&hist[mysel], 1);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) block_counts[(int64_t)blockIdx.x * E + e] = hist[e];
+}
+
+// block_counts[nblk][E] -> exclusive prefix over blocks in place; expert_offset.
+__global__ void scan_kernel(int* __restrict__ block_counts, int nblk, int E,
+                            int64_t* __restrict__ expert_offset) {
+  extern __shared__ int totals[];  // [E]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < E; e += nwarps) {
+    int running = 0;
+    for (int b0 = 0; b0 < nblk; b0 += 32) {
+      const int b = b0 + lane;
+      const int v = b < nblk ? block_counts[(int64_t)b * E + e] : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      if (b < nblk) block_counts[(int64_t)b * E + e] = running + incl - v;
+      running += __shfl_sync(0xFFFFFFFFu, incl, 31);
+    }
+    if (lane == 0) totals[e] = running;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int64_t acc = 0;
+    for (int e = 0; e < E; ++e) {
+      expert_offset[e] = acc;
+      acc += totals[e];
+    }
+    expert_offset[E] = acc;
+  }
+}
+
+template <typename T, bool VEC>
+__global__ void place_gather_kernel(const T* __restrict__ x, const int* __restrict__ ids,
+                                    const int* __restrict__ block_base,
+                                    const int64_t* __restrict__ expert_offset, int64_t T_tokens,
+                                    int64_t H, int E, int k, int tpb, T* __restrict__ xp,
+                                    int64_t* __restrict__ inv) {
+  extern __shared__ int sm[];
+  int* cursor = sm;      // [E] next row of each expert for this block
+  int* pos = sm + E;     // [tpb*k] destination row of each slot of this block
+  const int64_t t0 = (int64_t)blockIdx.x * tpb;
+  const int ntok = (int)min((int64_t)tpb, T_tokens - t0);
+  const int nslots = ntok * k;
+  const int64_t slot0 = t0 * k;
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    cursor[e] = (int)expert_offset[e] + block_base[(int64_t)blockIdx.x * E + e];
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    for (int g = 0; g < nslots; g += 32) {
+      const int s = g + lane;
+      const bool valid = s < nslots;
+      const int e = valid ? ids[slot0 + s] : -1 - lane;
+      const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      int p = 0;
+      if (valid) p = cursor[e] + rank;
+      __syncwarp();
+      if (valid && rank == __popc(peers) - 1) cursor[e] = p + 1;
+      __syncwarp();
+      if (valid) {
+        pos[s] = p;
+        inv[slot0 + s] = p;
+      }
+    }
+  }
+  __syncthreads();
+  if (VEC) {
+    const int chunks = (int)(H * sizeof(T) / 16);
+    const uint4* src = reinterpret_cast<const uint4*>(x + t0 * H);
+    uint4* dst = reinterpret_cast<uint4*>(xp);
+    const int total = ntok * chunks;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+      const int tl = i / chunks, c = i - tl * chunks;
+      const uint4 v = __ldg(src + (int64_t)tl * chunks + c);
+      for (int j = 0; j < k; ++j) dst[(int64_t)pos[tl * k + j] * chunks + c] = v;
+    }
+  } else {
+    const int64_t total = (int64_t)ntok * H;
+    for (int64_t i = threadIdx.x; i < total; i += blockDim.x) {
+      const int tl = (int)(i / H);
+      const int64_t c = i - (int64_t)tl * H;
+      const T v = x[(t0 + tl) * H + c];
+      for (int j = 0; j < k; ++j) xp[(int64_t)pos[tl * k + j] * H + c] = v;
+    }
+  }
+}
+
+struct SelectGeometry {
+  int tpb;
+  int nblk;
+  size_t ids_bytes;
+  size_t counts_bytes;
+};
+
+SelectGeometry select_geometry(int64_t T, int E, int k) {
+  SelectGeometry g;
+  // enough blocks to cover the SMs twice for small T, up to 16 tokens per block
+  int64_t tpb = T / 296;
+  if (tpb < 1) tpb = 1;
+  if (tpb > 16) tpb = 16;
+  if (tpb * k > kMaxSlotsPerBlock) tpb = kMaxSlotsPerBlock / k > 0 ? kMaxSlotsPerBlock / k : 1;
+  g.tpb = (int)tpb;
+  g.nblk = (int)ceil_div(T, tpb);
+  g.ids_bytes = (size_t)ceil_div(T * k * 4, 16) * 16;
+  g.counts_bytes = (size_t)ceil_div((int64_t)g.nblk * E * 4, 16) * 16;
+  return g;
+}
+
+template <typename T>
+int run_select(const void* x, const void* scores, void* xp, void* w, int64_t* inv, int64_t* off,
+               int64_t Tn, int64_t H, int E, int k, void* ws, cudaStream_t s) {
+  const SelectGeometry g = select_geometry(Tn, E, k);
+  int* ids = reinterpret_cast<int*>(ws);
+  int* counts = reinterpret_cast<int*>(reinterpret_cast<char*>(ws) + g.ids_bytes);
+  const int route_threads = 32 * (g.tpb < 8 ? g.tpb : 8);
+  route_count_kernel<T><<<g.nblk, route_threads, E * sizeof(int), s>>>(
+      reinterpret_cast<const T*>(scores), Tn, E, k, g.tpb, reinterpret_cast<T*>(w), ids, counts);
+  PMX_CUDA_OK(cudaGetLastError());
+  scan_kernel<<<1, 1024, E * sizeof(int), s>>>(counts, g.nblk, E, off);
+  PMX_CUDA_OK(cudaGetLastError());
+  const size_t sm_bytes = (size_t)(E + g.tpb * k) * sizeof(int);
+  const bool vec = (H * sizeof(T)) % 16 == 0 && aligned16(x) && aligned16(xp);
+  if (vec)
+    place_gather_kernel<T, true><<<g.nblk, 256, sm_bytes, s>>>(
+        reinterpret_cast<const T*>(x), ids, counts, off, Tn, H, E, k, g.tpb, reinterpret_cast<T*>(xp), inv);
+  else
+    place_gather_kernel<T, false><<<g.nblk, 256, sm_bytes, s>>>(
+        reinterpret_cast<const T*>(x), ids, counts, off, Tn, H, E, k, g.tpb, reinterpret_cast<T*>(xp), inv);
+  PMX_CUDA_OK(cudaGetLastError());
+  return PMX_OK;
+}
+
+}  // namespace
+
+size_t select_workspace_bytes(int64_t T, int E, int k) {
+  if (T <= 0 || E <= 0 || k <= 0) return 0;
+  const SelectGeometry g = select_geometry(T, E, k);
+  return g.ids_bytes + g.counts_bytes;
+}
+
+int launch_select(const void* x, const void* scores, void* xp, void* w, int64_t* inv, int64_t* off,
+                  int64_t T, int64_t H, int E, int k, int dtype, void* ws, size_t ws_bytes,
+                  cudaStream_t s) {
+  if (!x || !scores || !xp || !w || !inv || !off) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_select: null pointer");
+  if (T <= 0) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_select: needs at least one token (T=%lld)", (long long)T);
+  if (H <= 0 || E <= 0 || k <= 0) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_select: H, E, k must be positive");
+  if (k > E) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_select: k=%d exceeds the number of experts %d", k, E);
+  if (k > 32) return fail(PMX_ERR_UNSUPPORTED, "moe_select: at most 32 experts per token (k=%d)", k);
+  if (E > 8192) return fail(PMX_ERR_UNSUPPORTED, "moe_select: at most 8192 experts");
+  if (T * k >= (1ll << 31)) return fail(PMX_ERR_UNSUPPORTED, "moe_select: T*k must stay below 2^31");
+  const size_t need = select_workspace_bytes(T, E, k);
+  if (!ws || ws_bytes < need) return fail(PMX_ERR_WORKSPACE, "moe_select: workspace of %zu bytes needed, %zu given", need, ws_bytes);
+  if (!aligned16(ws)) return fail(PMX_ERR_ALIGNMENT, "moe_select: workspace must be 16-byte aligned");
+  switch (dtype) {
+    case PMX_DTYPE_F16: return run_select<__half>(x, scores, xp, w, inv, off, T, H, E, k, ws, s);
+    case PMX_DTYPE_BF16: return run_select<__nv_bfloat16>(x, scores, xp, w, inv, off, T, H, E, k, ws, s);
+    case PMX_DTYPE_F32: return run_select<float>(x, scores, xp, w, inv, off, T, H, E, k, ws, s);
+  }
+  return fail(PMX_ERR_UNSUPPORTED, "moe_select: unknown dtype %d", dtype);
+}
+
+}  // namespace pmx

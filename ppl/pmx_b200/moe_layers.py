@@ -1,0 +1,132 @@
+"""Weight-owning modules of the MoE path and the fused Mixtral MoE block.
+
+`MoeColumnParallelLinear` / `MoeRowParallelLinear` mirror the reference modules
+(model_zoo/ModelParallel.py:127-159 and :162-196): same constructor arguments,
+parameter names and tensor-parallel shapes, so a reference state dict loads
+unchanged.  `MoeFeedForward` mirrors the Mixtral block
+(model_zoo/mixtral/modeling/dynamic_batching/Model.py:155-214) and runs it as
+  gate linear -> moe_select -> gate/up GEMM with SwiGLU in the epilogue ->
+  down GEMM -> moe_reduce -> one all-reduce of [T,H] over the TP group.
+The reference all-reduces the expanded [T*k,H] rows before the weighted combine
+(MoeRowParallelLinear.py:57-58); combining first is the same sum in another
+order and moves k times fewer bytes over NVLink.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from . import torch_function as OPMX
+from .torch_function.moe import moe_grouped_linear
+
+
+def _world(proc_group) -> int:
+    return 1 if proc_group is None else proc_group.size()
+
+
+class MoeColumnParallelLinear(nn.Module):
+    """weight [E, out_features/tp, in_features] (ModelParallel.py:147-149)."""
+
+    def __init__(self, proc_group, num_experts: int, in_features: int, out_features: int,
+                 bias_term: bool = True, gather_output: bool = True) -> None:
+        super().__init__()
+        self.num_experts = num_experts
+        self.in_features = in_features
+        self.out_features = out_features
+        self.gather_output = gather_output
+        self.proc_group = proc_group
+        world_size = _world(proc_group)
+        assert out_features % world_size == 0, "{} is not divisible by {}".format(out_features, world_size)
+        self.out_features_per_partition = out_features // world_size
+        self.weight = nn.Parameter(torch.ones(num_experts, self.out_features_per_partition, in_features))
+        if bias_term:
+            self.bias = nn.Parameter(torch.zeros(num_experts, self.out_features_per_partition))
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, X: torch.Tensor, expert_offset: torch.Tensor):
+        return OPMX.moe_column_parallel_linear(X, expert_offset, self.weight, self.bias, self.proc_group,
+                                               self.num_experts, self.in_features, self.out_features,
+                                               self.gather_output)
+
+
+class MoeRowParallelLinear(nn.Module):
+    """weight [E, out_features, in_features/tp] (ModelParallel.py:182-184)."""
+
+    def __init__(self, proc_group, num_experts: int, in_features: int, out_features: int,
+                 bias_term: bool = True, input_is_parallel: bool = False) -> None:
+        super().__init__()
+        self.num_experts = num_experts
+        self.in_features = in_features
+        self.out_features = out_features
+        self.input_is_parallel = input_is_parallel
+        self.proc_group = proc_group
+        world_size = _world(proc_group)
+        assert in_features % world_size == 0, "{} is not divisible by {}".format(in_features, world_size)
+        self.in_features_per_partition = in_features // world_size
+        self.weight = nn.Parameter(torch.ones(num_experts, out_features, self.in_features_per_partition))
+        if bias_term:
+            self.bias = nn.Parameter(torch.zeros(num_experts, out_features))
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, X: torch.Tensor, expert_offset: torch.Tensor):
+        return OPMX.moe_row_parallel_linear(X, expert_offset, self.weight, self.bias, self.proc_group,
+                                            self.num_experts, self.in_features, self.out_features,
+                                            self.input_is_parallel)
+
+
+class MoeFeedForward(nn.Module):
+    """The Mixtral MoE feed-forward block with the fused gate/up projection
+    `wu = [w1 ; w3]` (Model.py:171-174, weight packing Model.py:399-413).
+
+    fused=True  : SwiGLU in the GEMM epilogue, combine before the all-reduce.
+    fused=False : the reference's operator sequence and collective placement,
+                  one library call per operator (Model.py:191-211)."""
+
+    def __init__(self, hidden_dim: int, intermediate_dim: int, num_experts: int,
+                 num_experts_per_token: int, proc_group=None, linear_bias_term: bool = False,
+                 fused: bool = True) -> None:
+        super().__init__()
+        self.num_experts = num_experts
+        self.num_experts_per_token = num_experts_per_token
+        self.proc_group = proc_group
+        self.fused = fused
+        self.hidden_dim = hidden_dim
+        self.gate = nn.Linear(hidden_dim, num_experts, bias=False)
+        self.wu = MoeColumnParallelLinear(proc_group, num_experts, hidden_dim, 2 * intermediate_dim,
+                                          bias_term=linear_bias_term, gather_output=False)
+        self.w2 = MoeRowParallelLinear(proc_group, num_experts, intermediate_dim, hidden_dim,
+                                       bias_term=linear_bias_term, input_is_parallel=True)
+
+    def forward(self, x: torch.Tensor, router_logits: torch.Tensor | None = None) -> torch.Tensor:
+        if router_logits is None:
+            router_logits = torch.nn.functional.linear(x, self.gate.weight)
+        E, k = self.num_experts, self.num_experts_per_token
+        x_experts, expert_weights, invert_permutation, expert_offset = OPMX.moe_select(x, router_logits, E, k)
+        if not self.fused:
+            x13 = OPMX.swiglu(self.wu(x_experts, expert_offset))
+            x_out = self.w2(x13, expert_offset)
+            return OPMX.moe_reduce(x_out, expert_weights, invert_permutation, k)
+        world = _world(self.proc_group)
+        flat = x_experts.view(-1, self.hidden_dim)
+        h = moe_grouped_linear(flat, expert_offset, self.wu.weight, self.wu.bias, swiglu=True,
+                               zero_outside=False)
+        bias2 = self.w2.bias
+        if bias2 is not None and world > 1 and dist.get_rank(group=self.proc_group) != 0:
+            bias2 = None
+        y = moe_grouped_linear(h, expert_offset, self.w2.weight, bias2, zero_outside=False)
+        out = OPMX.moe_reduce(y.view(*expert_weights.shape, -1), expert_weights, invert_permutation, k)
+        if world > 1:
+            dist.all_reduce(out, group=self.proc_group)
+        return out
+
+
+def patch_reference(opmx_module) -> None:
+    """Rebind the MoE entry points of an imported OPMX `torch_function` module
+    (the reference resolves them through that module at call time,
+    Model.py:191-211 and ModelParallel.py:156,193) to this implementation."""
+    for name in ("moe_select", "moe_column_parallel_linear", "moe_row_parallel_linear", "moe_reduce",
+                 "swiglu", "silu"):
+        setattr(opmx_module, name, getattr(OPMX, name))

@@ -1,0 +1,342 @@
+"""The OPMX mixture-of-experts operators on B200.
+
+Same call signatures, output layouts, dtypes and ONNX custom-op export as the
+reference operators; `forward` allocates the outputs and hands raw pointers to
+the CUDA library through its C ABI.  Tensors must live on a CUDA device: there
+is no CPU implementation behind these functions (during ONNX export the
+forwards only return correctly shaped placeholders, as the reference does).
+
+Reference: torch_function/MoeSelect.py, MoeColumnParallelLinear.py,
+MoeRowParallelLinear.py, MoeReduce.py, SwiGLU.py, SiLU.py.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from .. import _cabi
+from .._cabi import lib, check, ptr, stream_of, workspace, DTYPE_CODE
+
+
+def _require_cuda(name: str, **tensors) -> None:
+    for key, t in tensors.items():
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(f"{name}: `{key}` is on {t.device}; this implementation runs on CUDA "
+                               "devices only and has no CPU fallback")
+
+
+def _dtype_code(name: str, t: torch.Tensor) -> int:
+    try:
+        return DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise TypeError(f"{name}: dtype {t.dtype} is not supported (float16, bfloat16, float32)") from None
+
+
+def _group_size(proc_group) -> int:
+    if proc_group is None or not dist.is_available() or not dist.is_initialized():
+        return 1
+    return dist.get_world_size(group=proc_group)
+
+
+def _offsets_on(expert_offset: torch.Tensor, device, num_experts: int) -> torch.Tensor:
+    if expert_offset.numel() != num_experts + 1:
+        raise ValueError(f"expert_offset has {expert_offset.numel()} entries, expected num_experts+1 = {num_experts + 1}")
+    return expert_offset.to(device=device, dtype=torch.int64).contiguous()
+
+
+# --------------------------------------------------------------------------- select
+class MoeSelect(torch.autograd.Function):
+    """opmx::MoeSelect (torch_function/MoeSelect.py:5-64)."""
+
+    @staticmethod
+    def symbolic(g, X, scores, num_experts: int, num_experts_per_token: int):
+        return g.op("opmx::MoeSelect", X, scores, num_experts_i=num_experts,
+                    num_experts_per_token_i=num_experts_per_token, outputs=4)
+
+    @staticmethod
+    def forward(ctx, X: torch.Tensor, scores: torch.Tensor, num_experts: int, num_experts_per_token: int):
+        k = int(num_experts_per_token)
+        lead = tuple(X.shape[:-1])
+        H = X.shape[-1]
+        if torch.onnx.is_in_onnx_export():
+            # placeholders in the order of the real outputs (the reference
+            # returns them permuted at MoeSelect.py:35, which only shuffles the
+            # traced type metadata)
+            return (torch.zeros(*lead, k, H, dtype=X.dtype, device=X.device),
+                    torch.zeros(*lead, k, dtype=scores.dtype, device=X.device),
+                    torch.zeros(*lead, k, dtype=torch.int64, device=X.device),
+                    torch.zeros(num_experts + 1, dtype=torch.int64, device=X.device))
+        _require_cuda("moe_select", X=X, scores=scores)
+        if scores.shape[-1] != num_experts or tuple(scores.shape[:-1]) != lead:
+            raise ValueError(f"moe_select: scores shape {tuple(scores.shape)} does not match X {tuple(X.shape)} "
+                             f"with {num_experts} experts")
+        if scores.dtype != X.dtype:
+            raise TypeError("moe_select: X and scores must have the same dtype")
+        if not 0 < k <= num_experts:
+            raise ValueError(f"moe_select: num_experts_per_token={k} out of range for {num_experts} experts")
+        T = 1
+        for d in lead:
+            T *= d
+        if T == 0 or H == 0:
+            raise ValueError("moe_select: needs at least one token")
+        code = _dtype_code("moe_select", X)
+        x2 = X.contiguous().view(T, H)
+        s2 = scores.contiguous().view(T, num_experts)
+        dev = X.device
+        xp = torch.empty(*lead, k, H, dtype=X.dtype, device=dev)
+        w = torch.empty(*lead, k, dtype=scores.dtype, device=dev)
+        inv = torch.empty(*lead, k, dtype=torch.int64, device=dev)
+        off = torch.empty(num_experts + 1, dtype=torch.int64, device=dev)
+        nbytes = lib.pmx_moe_select_workspace_bytes(T, num_experts, k)
+        ws = workspace(nbytes, dev)
+        with torch.cuda.device(dev):
+            check(lib.pmx_moe_select(ptr(x2), ptr(s2), ptr(xp), ptr(w), ptr(inv), ptr(off), T, H,
+                                     num_experts, k, code, ptr(ws), ws.numel(), stream_of(X)))
+        return xp, w, inv, off
+
+
+def moe_select(X: torch.Tensor, scores: torch.Tensor, num_experts: int, num_experts_per_token: int):
+    """-> (X_expand_permute [*,k,H], expert_weights [*,k], invert_permutation [*,k] int64,
+    expert_offset [E+1] int64); signature of torch_function/MoeSelect.py:67-70."""
+    return MoeSelect.apply(X, scores, num_experts, num_experts_per_token)
+
+
+# --------------------------------------------------------------------------- grouped linear
+def moe_grouped_linear(X: torch.Tensor, expert_offset: torch.Tensor, W: torch.Tensor,
+                       B: torch.Tensor | None = None, *, swiglu: bool = False, beta: float = 1.0,
+                       zero_outside: bool = True, plan: _cabi.GemmPlan | None = None,
+                       return_workspace: bool = False):
+    """Y[r] = X[r] @ W[e].T (+ B[e]) for rows r in [expert_offset[e], expert_offset[e+1]).
+
+    X [*,K], W [E,N,K], B [E,N] or None -> Y [*,N]; with swiglu=True W holds the
+    gate rows then the up rows and Y is [*,N/2] = up * gate * sigmoid(beta*gate).
+    The shared core of moe_column_parallel_linear and moe_row_parallel_linear
+    (the loops at MoeColumnParallelLinear.py:61-67 and MoeRowParallelLinear.py:47-53).
+    """
+    _require_cuda("moe_grouped_linear", X=X, W=W, B=B)
+    if W.dim() != 3:
+        raise ValueError("W must be [num_experts, out_features, in_features]")
+    E, N, K = W.shape
+    if X.shape[-1] != K:
+        raise ValueError(f"X has {X.shape[-1]} input features, W expects {K}")
+    if W.dtype != X.dtype or (B is not None and B.dtype != X.dtype):
+        raise TypeError("X, W and B must have the same dtype")
+    if B is not None and tuple(B.shape) != (E, N):
+        raise ValueError(f"B must be [{E}, {N}]")
+    code = _dtype_code("moe_grouped_linear", X)
+    dev = X.device
+    lead = tuple(X.shape[:-1])
+    M = 1
+    for d in lead:
+        M *= d
+    n_out = N // 2 if swiglu else N
+    y = torch.empty(*lead, n_out, dtype=X.dtype, device=dev)
+    if M == 0:
+        return (y, None) if return_workspace else y
+    x2 = X.contiguous().view(M, K)
+    w = W.contiguous()
+    b = B.contiguous() if B is not None else None
+    off = _offsets_on(expert_offset, dev, E)
+    epi = _cabi.EPILOGUE_SWIGLU if swiglu else _cabi.EPILOGUE_NONE
+    plan_ref = C.byref(plan) if plan is not None else None
+    nbytes = lib.pmx_moe_grouped_linear_workspace_bytes(M, N, K, E, code, epi, plan_ref)
+    if nbytes == 0:
+        raise _cabi.PmxError(-1, lib.pmx_moe_last_error().decode() or "grouped_linear: invalid arguments")
+    ws = workspace(nbytes, dev)
+    with torch.cuda.device(dev):
+        check(lib.pmx_moe_grouped_linear(ptr(x2), ptr(off), ptr(w), ptr(b), ptr(y), M, N, K, E, code, epi,
+                                         float(beta), 1 if zero_outside else 0, plan_ref, ptr(ws),
+                                         ws.numel(), stream_of(X)))
+    return (y, ws) if return_workspace else y
+
+
+def grouped_linear_check(ws: torch.Tensor) -> None:
+    """Synchronises and raises if the launch that used `ws` recorded a failed self-check."""
+    out = (C.c_int32 * 4)()
+    with torch.cuda.device(ws.device):
+        check(lib.pmx_moe_grouped_linear_check(ptr(ws), C.byref(out), stream_of(ws)))
+
+
+class MoeColumnParallelLinear(torch.autograd.Function):
+    """opmx::MoeColumnParallelLinear (torch_function/MoeColumnParallelLinear.py:7-81)."""
+
+    @staticmethod
+    def symbolic(g, X, expert_offset, W, B, proc_group, num_experts: int, in_features: int,
+                 out_features: int, gather_output: bool = True):
+        attrs = dict(num_experts_i=num_experts, in_features_i=in_features, out_features_i=out_features,
+                     gather_output_i=gather_output)
+        if B is not None:
+            return g.op("opmx::MoeColumnParallelLinear", X, expert_offset, W, B, bias_term_i=True, **attrs)
+        return g.op("opmx::MoeColumnParallelLinear", X, expert_offset, W, bias_term_i=False, **attrs)
+
+    @staticmethod
+    def forward(ctx, X, expert_offset, W, B, proc_group, num_experts: int, in_features: int,
+                out_features: int, gather_output: bool = True):
+        assert X.shape[-1] == in_features, "X.shape is {}, in_features is {}".format(X.shape, in_features)
+        world = _group_size(proc_group)
+        if torch.onnx.is_in_onnx_export():
+            width = W.shape[1] * (world if gather_output else 1)
+            return torch.zeros(*X.shape[:-1], width, dtype=W.dtype, device=X.device)
+        if W.shape[0] != num_experts:
+            raise ValueError(f"W has {W.shape[0]} experts, num_experts={num_experts}")
+        y = moe_grouped_linear(X, expert_offset, W, B)
+        if gather_output and world > 1:
+            parts = [torch.empty_like(y) for _ in range(world)]
+            dist.all_gather(parts, y, group=proc_group)
+            y = torch.cat(parts, dim=-1).contiguous()
+        return y
+
+
+def moe_column_parallel_linear(X, expert_offset, W, B, proc_group, num_experts: int, in_features: int,
+                               out_features: int, gather_output: bool = True) -> torch.Tensor:
+    """Signature of torch_function/MoeColumnParallelLinear.py:84-93.  W is this rank's
+    [E, out_features/tp, in_features] shard; the output keeps X's dtype and device."""
+    return MoeColumnParallelLinear.apply(X, expert_offset, W, B, proc_group, num_experts, in_features,
+                                         out_features, gather_output)
+
+
+class MoeRowParallelLinear(torch.autograd.Function):
+    """opmx::MoeRowParallelLinear (torch_function/MoeRowParallelLinear.py:8-62)."""
+
+    @staticmethod
+    def symbolic(g, X, expert_offset, W, B, proc_group, num_experts: int, in_features: int,
+                 out_features: int, input_is_parallel: bool = False):
+        attrs = dict(num_experts_i=num_experts, in_features_i=in_features, out_features_i=out_features,
+                     input_is_parallel_i=input_is_parallel)
+        if B is not None:
+            return g.op("opmx::MoeRowParallelLinear", X, expert_offset, W, B, bias_term_i=True, **attrs)
+        return g.op("opmx::MoeRowParallelLinear", X, expert_offset, W, bias_term_i=False, **attrs)
+
+    @staticmethod
+    def forward(ctx, X, expert_offset, W, B, proc_group, num_experts: int, in_features: int,
+                out_features: int, input_is_parallel: bool = False):
+        if torch.onnx.is_in_onnx_export():
+            return torch.zeros(*X.shape[:-1], W.shape[1], dtype=W.dtype, device=X.device)
+        if W.shape[0] != num_experts:
+            raise ValueError(f"W has {W.shape[0]} experts, num_experts={num_experts}")
+        world = _group_size(proc_group)
+        # X is taken as already split along K (the reference ignores
+        # input_is_parallel too, MoeRowParallelLinear.py:44-53).  The bias is
+        # per expert and must enter the sum once: only group rank 0 adds it.
+        # (The reference's `output + B` at :59-60 broadcasts [E,N] against the
+        # row dimension and is not per expert; the operator spec asks for B:(E,N).)
+        bias = B
+        if B is not None and world > 1 and dist.get_rank(group=proc_group) != 0:
+            bias = None
+        y = moe_grouped_linear(X, expert_offset, W, bias)
+        if world > 1:
+            dist.all_reduce(y, group=proc_group)
+        return y
+
+
+def moe_row_parallel_linear(X, expert_offset, W, B, proc_group, num_experts: int, in_features: int,
+                            out_features: int, input_is_parallel: bool = False) -> torch.Tensor:
+    """Signature of torch_function/MoeRowParallelLinear.py:65-74.  W is this rank's
+    [E, out_features, in_features/tp] shard; partial sums are all-reduced over proc_group."""
+    return MoeRowParallelLinear.apply(X, expert_offset, W, B, proc_group, num_experts, in_features,
+                                      out_features, input_is_parallel)
+
+
+# --------------------------------------------------------------------------- reduce
+class MoeReduce(torch.autograd.Function):
+    """opmx::MoeReduce (torch_function/MoeReduce.py:4-26)."""
+
+    @staticmethod
+    def symbolic(g, Y, expert_weights, invert_permutation, num_experts_per_token: int):
+        out = g.op("opmx::MoeReduce", Y, expert_weights, invert_permutation,
+                   num_experts_per_token_i=num_experts_per_token)
+        return out.setTypeAs(Y)
+
+    @staticmethod
+    def forward(ctx, Y, expert_weights, invert_permutation, num_experts_per_token: int):
+        k = int(num_experts_per_token)
+        N = Y.shape[-1]
+        lead = tuple(expert_weights.shape[:-1])
+        if torch.onnx.is_in_onnx_export():
+            return torch.zeros(*lead, N, dtype=Y.dtype, device=Y.device)
+        _require_cuda("moe_reduce", Y=Y, expert_weights=expert_weights, invert_permutation=invert_permutation)
+        if expert_weights.shape[-1] != k or tuple(invert_permutation.shape) != tuple(expert_weights.shape):
+            raise ValueError("moe_reduce: expert_weights and invert_permutation must be [*, num_experts_per_token]")
+        T = expert_weights.numel() // k
+        if Y.numel() != T * k * N:
+            raise ValueError(f"moe_reduce: Y has {Y.numel()} elements, expected {T}*{k}*{N}")
+        code = _dtype_code("moe_reduce", Y)
+        out = torch.empty(*lead, N, dtype=Y.dtype, device=Y.device)
+        if T == 0:
+            return out
+        y2 = Y.contiguous()
+        w = expert_weights.to(Y.dtype).contiguous()
+        inv = invert_permutation.to(torch.int64).contiguous()
+        with torch.cuda.device(Y.device):
+            check(lib.pmx_moe_reduce(ptr(y2), ptr(w), ptr(inv), ptr(out), T, k, N, code, stream_of(Y)))
+        return out
+
+
+def moe_reduce(Y, expert_weights, invert_permutation, num_experts_per_token: int):
+    """Signature of torch_function/MoeReduce.py:29-32.  -> [*, N] in Y's dtype."""
+    return MoeReduce.apply(Y, expert_weights, invert_permutation, num_experts_per_token)
+
+
+# --------------------------------------------------------------------------- activations
+class SwiGLU(torch.autograd.Function):
+    """opmx::SwiGLU (torch_function/SwiGLU.py:4-17)."""
+
+    @staticmethod
+    def symbolic(g, X, beta: float = 1.0):
+        return g.op("opmx::SwiGLU", X, beta_f=beta)
+
+    @staticmethod
+    def forward(ctx, X, beta: float = 1.0):
+        D = X.shape[-1]
+        if torch.onnx.is_in_onnx_export():
+            return torch.zeros(*X.shape[:-1], D // 2, dtype=X.dtype, device=X.device)
+        _require_cuda("swiglu", X=X)
+        if D % 2:
+            raise ValueError("swiglu: the last dimension must be even")
+        code = _dtype_code("swiglu", X)
+        y = torch.empty(*X.shape[:-1], D // 2, dtype=X.dtype, device=X.device)
+        M = X.numel() // D if D else 0
+        if M == 0:
+            return y
+        x2 = X.contiguous()
+        with torch.cuda.device(X.device):
+            check(lib.pmx_swiglu(ptr(x2), ptr(y), M, D, float(beta), code, stream_of(X)))
+        return y
+
+
+def swiglu(X: torch.Tensor, beta: float = 1.0):
+    """Signature of torch_function/SwiGLU.py:20-21."""
+    return SwiGLU.apply(X, beta)
+
+
+class SiLU(torch.autograd.Function):
+    """opmx::SiLU (torch_function/SiLU.py:4-21)."""
+
+    @staticmethod
+    def symbolic(g, X, gate=None):
+        y = g.op("opmx::SiLU", X, gate) if gate is not None else g.op("opmx::SiLU", X)
+        return y.setTypeAs(X)
+
+    @staticmethod
+    def forward(ctx, X, gate=None):
+        if torch.onnx.is_in_onnx_export():
+            return X
+        _require_cuda("silu", X=X, gate=gate)
+        if gate is not None and (gate.shape != X.shape or gate.dtype != X.dtype):
+            raise ValueError("silu: gate must match X in shape and dtype")
+        code = _dtype_code("silu", X)
+        y = torch.empty_like(X, memory_format=torch.contiguous_format)
+        if X.numel() == 0:
+            return y
+        x2 = X.contiguous()
+        g2 = gate.contiguous() if gate is not None else None
+        with torch.cuda.device(X.device):
+            check(lib.pmx_silu(ptr(x2), ptr(g2), ptr(y), X.numel(), code, stream_of(X)))
+        return y
+
+
+def silu(X: torch.Tensor, gate: torch.Tensor = None):
+    """Signature of torch_function/SiLU.py:24-25."""
+    return SiLU.apply(X, gate)

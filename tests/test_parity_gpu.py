@@ -1,0 +1,301 @@
+"""Parity of the CUDA path, called through the C ABI, with the CPU oracle and
+with the golden vectors the OPMX reference operators produced.
+
+Integer results (expert_offset, invert_permutation, the gathered rows) must be
+bit-exact; expert_weights within 1 ulp of one rounding of the fp32 softmax;
+fp16/bf16 GEMM results within max-abs 2e-2 / rel 1e-2 of the fp32 reference.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as orc
+from tests.helpers import GOLDEN, TAG, assert_close, assert_ulp, dev, host, load
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def F():
+    import ppl.pmx_b200.torch_function as F
+    return F
+
+
+def gpu_select(F, x, sc, E, k, dtype):
+    xe, ew, inv, off = F.moe_select(dev(x, dtype), dev(sc, dtype), E, k)
+    torch.cuda.synchronize()
+    return xe, ew, inv, off
+
+
+def check_select(F, x, sc, E, k, dtype, golden=None):
+    H = x.shape[-1]
+    xe, ew, inv, off = gpu_select(F, x, sc, E, k, dtype)
+    assert inv.dtype == torch.int64 and off.dtype == torch.int64
+    assert tuple(xe.shape) == (*x.shape[:-1], k, H) and tuple(ew.shape) == (*x.shape[:-1], k)
+    oxe, oew, oinv, ooff = orc.moe_select(x.reshape(-1, H), sc.reshape(-1, E), E, k, dtype)
+    assert np.array_equal(off.cpu().numpy(), ooff)
+    assert np.array_equal(inv.cpu().numpy().reshape(-1), oinv.reshape(-1))
+    assert np.array_equal(host(xe).reshape(-1, H), oxe)
+    assert_ulp(ew.reshape(-1), oew.reshape(-1), dtype, msg="expert_weights vs oracle")
+    if golden is not None:
+        assert np.array_equal(off.cpu().numpy(), golden["expert_offset"])
+        assert np.array_equal(inv.cpu().numpy(), golden["invert_permutation"])
+        assert np.array_equal(host(xe), golden["x_expand_permute"])
+        assert_ulp(ew, golden["expert_weights"], dtype, msg="expert_weights vs reference")
+    return xe, ew, inv, off
+
+
+SELECT = sorted(os.path.basename(p) for p in glob.glob(os.path.join(GOLDEN, "select_*.npz")))
+
+
+@pytest.mark.parametrize("name", SELECT)
+def test_select_golden(F, name):
+    g = load(name)
+    check_select(F, g["x"], g["scores"], int(g["E"]), int(g["k"]), str(g["dtype"]), golden=g)
+
+
+@pytest.mark.parametrize("T,H,E,k,dtype", [
+    (1, 8, 8, 2, "f16"), (2, 24, 8, 2, "bf16"), (17, 5, 3, 1, "f32"), (300, 40, 8, 2, "f16"),
+    (513, 16, 64, 8, "f16"), (4097, 8, 8, 2, "bf16"), (64, 7, 8, 8, "f32"), (1000, 3, 160, 6, "f16"),
+    (9000, 8, 32, 32, "bf16"),
+])
+def test_select_random_shapes(F, T, H, E, k, dtype):
+    rng = np.random.default_rng(T * 7 + E)
+    x = orc.round_to_dtype(rng.standard_normal((T, H)).astype(np.float32), dtype)
+    sc, _ = orc.detie_scores(rng.standard_normal((T, E)).astype(np.float32), dtype)
+    check_select(F, x, sc, E, k, dtype)
+
+
+def test_select_ties_follow_the_stated_rule(F):
+    # equal scores: higher score first, lower expert index among equals (not torch.topk's
+    # implementation-defined order); -0.0 ties with +0.0
+    sc = np.array([[1, 1, 1, 1, .5, 1, 1, 1], [0.0, -0.0, -1, -1, -2, -3, -4, -5],
+                   [3, 3, 3, 3, 3, 3, 3, 3], [-1, 2, 2, -1, 2, 0, 0, 7]], np.float32)
+    x = np.arange(4 * 8, dtype=np.float32).reshape(4, 8)
+    for dtype in ("f16", "bf16", "f32"):
+        for k in (1, 2, 3, 8):
+            check_select(F, x, sc, 8, k, dtype)
+
+
+def test_select_all_tokens_to_one_expert_and_empty_experts(F):
+    T, E = 257, 16
+    sc = np.full((T, E), -1e4, np.float32)
+    sc[:, 5] = 3.0
+    sc[:, 11] = 1.0
+    x = np.random.default_rng(1).standard_normal((T, 32)).astype(np.float16).astype(np.float32)
+    sc2, _ = orc.detie_scores(sc, "f16")
+    xe, ew, inv, off = check_select(F, x, sc2, E, 2, "f16")
+    counts = np.diff(off.cpu().numpy())
+    assert counts[5] == T and counts[11] == T and counts.sum() == 2 * T
+
+
+def test_select_leading_dims_and_noncontiguous_input(F):
+    rng = np.random.default_rng(3)
+    x = orc.round_to_dtype(rng.standard_normal((3, 5, 64)).astype(np.float32), "f16")
+    sc, _ = orc.detie_scores(rng.standard_normal((15, 8)).astype(np.float32), "f16")
+    sc = sc.reshape(3, 5, 8)
+    check_select(F, x, sc, 8, 2, "f16")
+    xt = dev(x.reshape(15, 64), "f16").t().contiguous().t()      # non-contiguous view
+    assert not xt.is_contiguous()
+    xe, ew, inv, off = F.moe_select(xt, dev(sc.reshape(15, 8), "f16"), 8, 2)
+    oxe, _, oinv, ooff = orc.moe_select(x.reshape(15, 64), sc.reshape(15, 8), 8, 2, "f16")
+    assert np.array_equal(host(xe).reshape(-1, 64), oxe) and np.array_equal(inv.cpu().numpy(), oinv)
+
+
+def test_select_errors(F):
+    x = torch.randn(4, 8, device="cuda", dtype=torch.float16)
+    s = torch.randn(4, 8, device="cuda", dtype=torch.float16)
+    with pytest.raises(ValueError):
+        F.moe_select(x, s, 8, 9)                      # k > E
+    with pytest.raises(ValueError):
+        F.moe_select(x[:0], s[:0], 8, 2)              # no tokens
+    with pytest.raises(ValueError):
+        F.moe_select(x, s[:, :4], 8, 2)               # scores width
+    with pytest.raises(RuntimeError):
+        F.moe_select(x.cpu(), s.cpu(), 8, 2)          # no CPU fallback
+    with pytest.raises(TypeError):
+        F.moe_select(x.double(), s.double(), 8, 2)
+
+
+# --------------------------------------------------------------------------- linears
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_linear_golden(F, dtype):
+    g = load(f"linear_{dtype}.npz")
+    E, N, K = g["w"].shape
+    x, w, b = dev(g["x"], dtype), dev(g["w"], dtype), dev(g["b"], dtype)
+    for tag in ("arange", "ragged"):
+        off = torch.from_numpy(g["off_" + tag])
+        y = F.moe_column_parallel_linear(x, off, w, b, None, E, K, N, False)
+        assert y.dtype == x.dtype and y.shape == (*x.shape[:-1], N)
+        assert_close(y, g["col_bias_" + tag], dtype, "col bias " + tag)
+        y = F.moe_column_parallel_linear(x, off.to(torch.int32).cuda(), w, None, None, E, K, N, True)
+        assert_close(y, g["col_nobias_" + tag], dtype, "col " + tag)
+        y = F.moe_row_parallel_linear(x, off.cuda(), w, None, None, E, K, N, True)
+        assert_close(y, g["row_nobias_" + tag], dtype, "row " + tag)
+        # rows no expert owns are exactly zero
+        outside = np.ones(x.shape[0] * x.shape[1], bool)
+        outside[g["off_" + tag][0]:g["off_" + tag][-1]] = False
+        assert not host(y).reshape(-1, N)[outside].any()
+    assert_close(F.swiglu(dev(g["swiglu_in"], dtype)), g["swiglu_out"], dtype)
+    assert_close(F.swiglu(dev(g["swiglu_in"], dtype), 1.7), g["swiglu_out_beta"], dtype)
+    d = g["swiglu_in"].shape[-1] // 2
+    a, c = dev(g["swiglu_in"][..., :d], dtype), dev(g["swiglu_in"][..., d:], dtype)
+    assert_close(F.silu(a, c), g["silu_gate_out"], dtype)
+    assert_close(F.silu(a), g["silu_out"], dtype)
+
+
+def ragged_offsets(rng, M, E, empty=2, lead=0, trail=0):
+    cuts = np.sort(rng.integers(lead, M - trail + 1, E - 1))
+    off = np.concatenate([[lead], cuts, [M - trail]]).astype(np.int64)
+    for e in rng.choice(E, size=min(empty, E - 1), replace=False):
+        off[e + 1] = off[e]
+    return np.maximum.accumulate(off)
+
+
+def run_linear(F, rng, M, N, K, E, dtype, plan=None, bias=False, swiglu=False, off=None):
+    from ppl.pmx_b200._cabi import GemmPlan
+    from ppl.pmx_b200.torch_function.moe import moe_grouped_linear, grouped_linear_check
+    x = orc.round_to_dtype(rng.standard_normal((M, K)).astype(np.float32), dtype)
+    w = orc.round_to_dtype((rng.standard_normal((E, N, K)) / np.sqrt(K)).astype(np.float32), dtype)
+    b = orc.round_to_dtype(rng.standard_normal((E, N)).astype(np.float32), dtype) if bias else None
+    if off is None:
+        off = ragged_offsets(rng, M, E)
+    p = GemmPlan(**plan) if plan else None
+    y, ws = moe_grouped_linear(dev(x, dtype), torch.from_numpy(off).cuda(), dev(w, dtype),
+                               dev(b, dtype) if bias else None, swiglu=swiglu, plan=p,
+                               return_workspace=True)
+    grouped_linear_check(ws)
+    ref = orc.moe_grouped_linear(x, off, w, b)
+    if swiglu:
+        ref = orc.swiglu(ref)
+    assert_close(y, ref, dtype, f"M={M} N={N} K={K} E={E} plan={plan}")
+    return y
+
+
+TC_SHAPES = [
+    # M, N, K, E
+    (64, 128, 64, 4), (200, 256, 128, 8), (300, 384, 192, 8), (1000, 512, 320, 8),
+    (77, 136, 72, 3), (16, 1024, 512, 8), (2048, 256, 256, 2),
+]
+
+
+@pytest.mark.parametrize("M,N,K,E", TC_SHAPES)
+@pytest.mark.parametrize("kernel", [1, 2, 3])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_grouped_linear_kernels(F, M, N, K, E, kernel, dtype):
+    rng = np.random.default_rng(M + N + K + kernel)
+    run_linear(F, rng, M, N, K, E, dtype, plan=dict(kernel=kernel), bias=(M % 2 == 0))
+
+
+@pytest.mark.parametrize("M,N,K,E", TC_SHAPES)
+@pytest.mark.parametrize("kernel", [1, 2, 3])
+def test_grouped_linear_swiglu_fused(F, M, N, K, E, kernel):
+    rng = np.random.default_rng(M * 3 + N + K + kernel)
+    run_linear(F, rng, M, N, K, E, "bf16" if kernel == 1 else "f16", plan=dict(kernel=kernel),
+               bias=(M % 2 == 1), swiglu=True)
+
+
+@pytest.mark.parametrize("kernel,split", [(1, 2), (1, 3), (2, 4), (2, 7)])
+def test_grouped_linear_split_k(F, kernel, split):
+    rng = np.random.default_rng(split)
+    off = ragged_offsets(rng, 90, 8, lead=5, trail=9)      # rows outside every expert -> zeros
+    y = run_linear(F, rng, 90, 256, 1024, 8, "f16", plan=dict(kernel=kernel, split_k=split), bias=True, off=off)
+    assert not host(y)[:5].any() and not host(y)[81:].any()
+
+
+@pytest.mark.parametrize("tile", [dict(kernel=1, tile_feat=32), dict(kernel=1, tile_feat=64),
+                                  dict(kernel=1, tile_feat=128, stages=2), dict(kernel=2, tile_tok=16),
+                                  dict(kernel=2, tile_tok=64, stages=3), dict(kernel=2, tile_tok=256),
+                                  dict(kernel=1, max_ctas=3), dict(kernel=2, max_ctas=1)])
+def test_grouped_linear_tilings(F, tile):
+    rng = np.random.default_rng(11)
+    run_linear(F, rng, 333, 320, 256, 5, "bf16", plan=tile, bias=True)
+
+
+def test_grouped_linear_auto_plan_and_fp32(F):
+    rng = np.random.default_rng(12)
+    run_linear(F, rng, 700, 256, 128, 4, "f16")          # auto -> tokens on M
+    run_linear(F, rng, 24, 256, 1024, 8, "f16")          # auto -> weights on M (+ split-K)
+    run_linear(F, rng, 50, 100, 36, 4, "f16")            # N, K not multiples of 8 -> CUDA-core kernel
+    run_linear(F, rng, 130, 96, 200, 6, "f32", bias=True)
+    run_linear(F, rng, 130, 96, 200, 6, "f32", swiglu=True)
+
+
+def test_grouped_linear_errors(F):
+    x = torch.randn(8, 64, device="cuda", dtype=torch.float16)
+    w = torch.randn(4, 32, 64, device="cuda", dtype=torch.float16)
+    off = torch.tensor([0, 2, 4, 6, 8])
+    with pytest.raises(AssertionError):
+        F.moe_column_parallel_linear(x, off, w, None, None, 4, 32, 32, False)   # in_features mismatch
+    with pytest.raises(ValueError):
+        F.moe_column_parallel_linear(x, off[:4], w, None, None, 4, 64, 32, False)
+    with pytest.raises(TypeError):
+        F.moe_column_parallel_linear(x, off, w.float(), None, None, 4, 64, 32, False)
+    with pytest.raises(RuntimeError):
+        F.moe_row_parallel_linear(x.cpu(), off, w.cpu(), None, None, 4, 64, 32, True)
+
+
+# --------------------------------------------------------------------------- reduce
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_reduce_golden(F, dtype):
+    g = load(f"reduce_{dtype}.npz")
+    out = F.moe_reduce(dev(g["y"], dtype), dev(g["expert_weights"], dtype),
+                       torch.from_numpy(g["invert_permutation"]).cuda(), int(g["k"]))
+    assert_close(out, g["out"], dtype)
+    ref = orc.moe_reduce(g["y"].reshape(-1, g["y"].shape[-1]), g["expert_weights"], g["invert_permutation"], int(g["k"]))
+    assert_close(out, ref, dtype)
+
+
+@pytest.mark.parametrize("T,k,N,dtype", [(1, 2, 4096, "f16"), (300, 8, 2048, "bf16"), (33, 3, 50, "f16"), (64, 2, 72, "f32")])
+def test_reduce_shapes(F, T, k, N, dtype):
+    rng = np.random.default_rng(T)
+    y = orc.round_to_dtype(rng.standard_normal((T * k, N)).astype(np.float32), dtype)
+    w = orc.round_to_dtype(rng.random((T, k)).astype(np.float32), dtype)
+    inv = rng.permutation(T * k).reshape(T, k)
+    out = F.moe_reduce(dev(y, dtype).view(T, k, N), dev(w, dtype), torch.from_numpy(inv).cuda(), k)
+    assert out.shape == (T, N)
+    assert_close(out, orc.moe_reduce(y, w, inv, k), dtype)
+
+
+# --------------------------------------------------------------------------- block
+@pytest.mark.parametrize("name", ["block_f32", "block_f16", "block_bf16", "block_f16_fine"])
+@pytest.mark.parametrize("fused", [False, True])
+def test_block_golden(F, name, fused):
+    from ppl.pmx_b200.moe_layers import MoeFeedForward
+    g = load(name + ".npz")
+    dtype, E, k = str(g["dtype"]), int(g["E"]), int(g["k"])
+    H, I = g["x"].shape[-1], g["w_down"].shape[-1]
+    blk = MoeFeedForward(H, I, E, k, None, False, fused=fused).cuda().to(dev(g["x"], dtype).dtype)
+    with torch.no_grad():
+        blk.gate.weight.copy_(dev(g["w_router"], dtype))
+        blk.wu.weight.copy_(dev(g["w_gate_up"], dtype))
+        blk.w2.weight.copy_(dev(g["w_down"], dtype))
+        out = blk(dev(g["x"], dtype), router_logits=dev(g["scores"], dtype))
+    assert_close(out, g["out_fp32_reference"], dtype, "vs fp32 run of the reference ops")
+    assert_close(out, g["out"], dtype, "vs low-precision run of the reference ops")
+    r = orc.moe_block(g["x"], g["w_router"], g["w_gate_up"], g["w_down"], E, k, dtype, scores=g["scores"],
+                      round_intermediates=False)
+    assert_close(out, r["out"], dtype, "vs oracle")
+
+
+@pytest.mark.parametrize("wl,scale", [("decode_t64", 8), ("prefill", 16), ("finegrained_empty", 4)])
+def test_block_scaled_workloads(F, wl, scale):
+    """The measured workloads with H and I divided by `scale` (T, E, k and the
+    router statistics kept), end to end against the oracle."""
+    from ppl.pmx_b200 import workloads as W
+    from ppl.pmx_b200.moe_layers import MoeFeedForward
+    sh = W.WORKLOADS[wl]
+    sh = W.scaled(sh, H=sh.H // scale, I=sh.I // scale, T=min(sh.T, 1024))
+    x, wr, sc, _ = W.make_activations(sh)
+    wu, w2 = W.make_expert_weights(sh, "cuda")
+    blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, None, False).cuda().to(W.TORCH_DTYPE[sh.dtype])
+    with torch.no_grad():
+        blk.wu.weight.copy_(wu)
+        blk.w2.weight.copy_(w2)
+        out = blk(x.cuda(), router_logits=sc.cuda())
+    r = orc.moe_block(host(x), host(wr), host(wu), host(w2), sh.E, sh.k, sh.dtype, scores=host(sc),
+                      round_intermediates=False)
+    assert_close(out, r["out"], sh.dtype)
