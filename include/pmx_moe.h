@@ -72,6 +72,9 @@ typedef struct pmx_gemm_plan {
 int pmx_moe_abi_version(void);
 const char* pmx_moe_last_error(void);
 const char* pmx_moe_status_string(int status);
+/* Number of kernels this library has launched (or recorded into a CUDA graph
+ * under capture) in this process so far; for benchmark accounting. */
+long long pmx_moe_kernel_launches(void);
 
 /*
  * moe_select -- replaces MoeSelect.forward, torch_function/MoeSelect.py:36-64.

@@ -1,5 +1,6 @@
 // extern "C" entry points declared in include/pmx_moe.h: argument checks,
 // kernel choice, error text.  No torch types, no allocation, no host sync.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
@@ -9,7 +10,10 @@ namespace pmx {
 
 namespace {
 thread_local char g_error[512] = "";
+std::atomic<long long> g_launches{0};
 }
+
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -79,6 +83,8 @@ extern "C" {
 int pmx_moe_abi_version(void) { return PMX_MOE_ABI_VERSION; }
 
 const char* pmx_moe_last_error(void) { return g_error; }
+
+long long pmx_moe_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char* pmx_moe_status_string(int status) {
   switch (status) {

@@ -15,11 +15,19 @@ void set_error(const char* fmt, ...);
 int fail(int status, const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
 int sm_count();  // SMs of the current device (cached per device)
+void count_launches(int n);  // adds to the process-wide kernel-launch counter
 
 #define PMX_CUDA_OK(expr)                                 \
   do {                                                    \
     int _s = ::pmx::check_cuda((expr), #expr);            \
     if (_s != PMX_OK) return _s;                          \
+  } while (0)
+
+// after every kernel launch: count it, then surface a launch error
+#define PMX_LAUNCHED()                       \
+  do {                                       \
+    ::pmx::count_launches(1);                \
+    PMX_CUDA_OK(cudaGetLastError());         \
   } while (0)
 
 // ---- element traits ----------------------------------------------------------

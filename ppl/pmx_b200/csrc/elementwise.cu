@@ -173,7 +173,7 @@ int launch_reduce(const void* y, const void* w, const int64_t* inv, void* out, i
     else
       reduce_kernel<T, false><<<grid_for(items), kThreads, 0, s>>>((const T*)y, (const T*)w, inv, (T*)out, Tn, k, N);
   })
-  PMX_CUDA_OK(cudaGetLastError());
+  PMX_LAUNCHED();
   return PMX_OK;
 }
 
@@ -188,7 +188,7 @@ int launch_swiglu(const void* x, void* y, int64_t M, int64_t D, float beta, int 
     else
       swiglu_kernel<T, false><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (T*)y, M, D, beta);
   })
-  PMX_CUDA_OK(cudaGetLastError());
+  PMX_LAUNCHED();
   return PMX_OK;
 }
 
@@ -203,7 +203,7 @@ int launch_silu(const void* x, const void* gate, void* y, int64_t n, int dtype, 
     else
       silu_kernel<T, false><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (const T*)gate, (T*)y, n);
   })
-  PMX_CUDA_OK(cudaGetLastError());
+  PMX_LAUNCHED();
   return PMX_OK;
 }
 
@@ -212,7 +212,7 @@ int launch_zero_outside(void* y, const int64_t* off, int64_t M, int64_t n_out, i
   PMX_DISPATCH_DTYPE(dtype, "grouped_linear", {
     zero_outside_kernel<T><<<sm_count(), kThreads, 0, s>>>((T*)y, off, M, n_out, E);
   })
-  PMX_CUDA_OK(cudaGetLastError());
+  PMX_LAUNCHED();
   return PMX_OK;
 }
 
@@ -223,7 +223,7 @@ int launch_splitk_finish(const float* partial, const int64_t* off, const void* b
     splitk_finish_kernel<T><<<grid_for(M * n_out / 4), kThreads, 0, s>>>(partial, off, (const T*)bias,
                                                                          (T*)y, M, n_out, E, split);
   })
-  PMX_CUDA_OK(cudaGetLastError());
+  PMX_LAUNCHED();
   return PMX_OK;
 }
 

@@ -116,7 +116,7 @@ int run(const void* x, const int64_t* off, const void* w, const void* bias, void
     grouped_gemm_simt_kernel<T, true><<<grid, 256, 0, s>>>((const T*)x, off, (const T*)w, (const T*)bias, (T*)y, M, (int)N, (int)K, E, beta);
   else
     grouped_gemm_simt_kernel<T, false><<<grid, 256, 0, s>>>((const T*)x, off, (const T*)w, (const T*)bias, (T*)y, M, (int)N, (int)K, E, beta);
-  PMX_CUDA_OK(cudaGetLastError());
+  PMX_LAUNCHED();
   return PMX_OK;
 }
 

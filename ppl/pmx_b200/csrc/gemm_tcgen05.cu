@@ -513,7 +513,7 @@ int launch_inst(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, i
   auto kern = grouped_gemm_tc_kernel<T, MODE, SWIGLU>;
   PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<grid, kThreads, smem, s>>>(mx, mw, p);
-  PMX_CUDA_OK(cudaGetLastError());
+  PMX_LAUNCHED();
   return PMX_OK;
 }
 

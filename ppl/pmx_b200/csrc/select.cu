@@ -202,9 +202,9 @@ int run_select(const void* x, const void* scores, void* xp, void* w, int64_t* in
   const int route_threads = 32 * (g.tpb < 8 ? g.tpb : 8);
   route_count_kernel<T><<<g.nblk, route_threads, E * sizeof(int), s>>>(
       reinterpret_cast<const T*>(scores), Tn, E, k, g.tpb, reinterpret_cast<T*>(w), ids, counts);
-  PMX_CUDA_OK(cudaGetLastError());
+  PMX_LAUNCHED();
   scan_kernel<<<1, 1024, E * sizeof(int), s>>>(counts, g.nblk, E, off);
-  PMX_CUDA_OK(cudaGetLastError());
+  PMX_LAUNCHED();
   const size_t sm_bytes = (size_t)(E + g.tpb * k) * sizeof(int);
   const bool vec = (H * sizeof(T)) % 16 == 0 && aligned16(x) && aligned16(xp);
   if (vec)
@@ -213,7 +213,7 @@ int run_select(const void* x, const void* scores, void* xp, void* w, int64_t* in
   else
     place_gather_kernel<T, false><<<g.nblk, 256, sm_bytes, s>>>(
         reinterpret_cast<const T*>(x), ids, counts, off, Tn, H, E, k, g.tpb, reinterpret_cast<T*>(xp), inv);
-  PMX_CUDA_OK(cudaGetLastError());
+  PMX_LAUNCHED();
   return PMX_OK;
 }
 
