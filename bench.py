@@ -173,11 +173,15 @@ def main():
     ap.add_argument("--workload", default="decode_t64")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ffn-div", type=int, default=1,
+                    help="divide the ffn size by this (small cases for profiler captures; traffic and flops scale with it)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     from ppl.pmx_b200 import workloads as W
     shape = W.WORKLOADS[args.workload]
+    if args.ffn_div != 1:
+        shape = W.scaled(shape, I=shape.I // args.ffn_div, name=f"{shape.name}_ffn_div{args.ffn_div}")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
