@@ -94,6 +94,38 @@ int pmx_moe_select(const void* x, const void* scores, void* x_expand_permute,
                    size_t workspace_bytes, void* stream);
 
 /*
+ * moe_select without a workspace argument.  Has no counterpart in the OPMX
+ * reference: it exists for hosts that may not allocate device memory around
+ * the call -- for example an inference-engine plug-in whose enqueue hook is
+ * handed its input and output bindings and nothing else, or a server that gave
+ * the whole device to its own arena at start-up and treats any later
+ * allocation as a bug.  Same inputs, outputs and results as pmx_moe_select;
+ * the ids and per-block counts the kernels need are kept in an array of
+ * PMX_MOE_SELECT_STATIC_SCRATCH_BYTES bytes that is part of the library's
+ * device image (each GPU that loads the library carries it until the process
+ * ends).  The call performs no cudaMalloc / cudaFree and calls no allocating
+ * library routine.
+ *   - Limit: pmx_moe_select_workspace_bytes(T,E,k) must not exceed
+ *     PMX_MOE_SELECT_STATIC_SCRATCH_BYTES (1 MiB: e.g. T*k up to 131072 slots
+ *     with 8 experts); larger problems get PMX_ERR_WORKSPACE and a message
+ *     naming the size, and should use pmx_moe_select.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with the caller's device current) and caches it;
+ *     make that first call before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps whatever the last
+ *     call left there.  Nothing in it needs clearing between calls (every byte
+ *     a call reads it has written itself first), but two calls whose kernels
+ *     overlap on the GPU -- different streams, or different host threads
+ *     without ordering -- race on it.  Keep calls on one stream, or order them.
+ */
+#define PMX_MOE_SELECT_STATIC_SCRATCH_BYTES (1 << 20)
+int pmx_moe_select_static(const void* x, const void* scores,
+                          void* x_expand_permute, void* expert_weights,
+                          int64_t* invert_permutation, int64_t* expert_offset,
+                          int64_t T, int64_t H, int32_t E, int32_t k,
+                          int32_t dtype, void* stream);
+
+/*
  * Grouped expert linear -- replaces the per-expert F.linear loops of
  * MoeColumnParallelLinear.forward (torch_function/MoeColumnParallelLinear.py:58-69)
  * and MoeRowParallelLinear.forward (torch_function/MoeRowParallelLinear.py:44-55):

@@ -111,6 +111,13 @@ int pmx_moe_select(const void* x, const void* scores, void* x_expand_permute, vo
                        T, H, E, k, dtype, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+int pmx_moe_select_static(const void* x, const void* scores, void* x_expand_permute,
+                          void* expert_weights, int64_t* invert_permutation, int64_t* expert_offset,
+                          int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype, void* stream) {
+  return launch_select_static(x, scores, x_expand_permute, expert_weights, invert_permutation,
+                              expert_offset, T, H, E, k, dtype, (cudaStream_t)stream);
+}
+
 size_t pmx_moe_grouped_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t E,
                                               int32_t dtype, int32_t epilogue,
                                               const pmx_gemm_plan* plan) {

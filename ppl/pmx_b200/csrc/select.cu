@@ -16,12 +16,20 @@
 //                 their expert with warp match/popc, writes
 //                 invert_permutation and copies each token row once from X to
 //                 its k destinations.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace pmx {
 namespace {
 
 constexpr int kMaxSlotsPerBlock = 2048;
+
+// Scratch of pmx_moe_select_static: lives in the library's device image, so
+// every GPU that loads the library holds these bytes until the process exits.
+// In host code the name below is only a handle for cudaGetSymbolAddress; the
+// kernels are always given the address that call returns.
+static __device__ __align__(256) unsigned char g_select_static_scratch[PMX_MOE_SELECT_STATIC_SCRATCH_BYTES];
 
 // Order-preserving map of a score to an unsigned key: -0 == +0, NaN on top.
 __device__ __forceinline__ uint32_t score_key(float s) {
@@ -244,6 +252,43 @@ int launch_select(const void* x, const void* scores, void* xp, void* w, int64_t*
     case PMX_DTYPE_F32: return run_select<float>(x, scores, xp, w, inv, off, T, H, E, k, ws, s);
   }
   return fail(PMX_ERR_UNSUPPORTED, "moe_select: unknown dtype %d", dtype);
+}
+
+// Device address of the built-in scratch on the current device, looked up once
+// per device (with that device current) and cached.
+int select_static_scratch(void** out) {
+  static std::mutex mu;
+  static void* cached[64] = {nullptr};
+  int dev = -1;
+  PMX_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(PMX_ERR_UNSUPPORTED, "moe_select_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    PMX_CUDA_OK(cudaGetSymbolAddress(&p, g_select_static_scratch));
+    if (!p) return fail(PMX_ERR_CUDA, "moe_select_static: cudaGetSymbolAddress returned a null address");
+    cached[dev] = p;
+  }
+  *out = cached[dev];
+  return PMX_OK;
+}
+
+int launch_select_static(const void* x, const void* scores, void* xp, void* w, int64_t* inv,
+                         int64_t* off, int64_t T, int64_t H, int E, int k, int dtype, cudaStream_t s) {
+  if (T <= 0 || E <= 0 || k <= 0 || k > E)
+    return fail(PMX_ERR_INVALID_ARGUMENT, "moe_select_static: need T > 0 and 0 < k <= E (T=%lld E=%d k=%d)", (long long)T, E, k);
+  const size_t need = select_workspace_bytes(T, E, k);
+  if (need > (size_t)PMX_MOE_SELECT_STATIC_SCRATCH_BYTES)
+    return fail(PMX_ERR_WORKSPACE,
+                "moe_select_static: T=%lld E=%d k=%d needs %zu bytes of scratch, the built-in scratch holds %d; "
+                "use pmx_moe_select with a workspace of your own",
+                (long long)T, E, k, need, (int)PMX_MOE_SELECT_STATIC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  const int st = select_static_scratch(&scratch);
+  if (st != PMX_OK) return st;
+  // nothing in the scratch has to start at zero: the routing kernel overwrites
+  // every id and every per-block count this call reads back
+  return launch_select(x, scores, xp, w, inv, off, T, H, E, k, dtype, scratch, need, s);
 }
 
 }  // namespace pmx
