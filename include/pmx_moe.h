@@ -8,9 +8,10 @@
  * negative pmx_status; pmx_moe_last_error() gives the text of the last failure
  * on the calling thread.  Nothing here allocates or frees device memory; the
  * caller provides the outputs and, where stated, a workspace whose size the
- * matching *_workspace_bytes() function returns.  Entry points keep no state
- * between calls (apart from per-device lookups cached on first use), so they
- * can be called from several host threads and captured in CUDA graphs.
+ * matching *_workspace_bytes() function returns.  The entry points that take
+ * their scratch from the caller keep no state between calls (apart from
+ * per-device lookups cached on first use), so they can be called from several
+ * host threads and captured in CUDA graphs.
  *
  * Tensors are dense, row-major, innermost dimension contiguous.  "T1" is the
  * activation type selected by `dtype`.  File:line citations name the OPMX
