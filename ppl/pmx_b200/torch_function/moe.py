@@ -177,8 +177,10 @@ class MoeColumnParallelLinear(torch.autograd.Function):
         assert X.shape[-1] == in_features, "X.shape is {}, in_features is {}".format(X.shape, in_features)
         world = _group_size(proc_group)
         if torch.onnx.is_in_onnx_export():
-            width = W.shape[1] * (world if gather_output else 1)
-            return torch.zeros(*X.shape[:-1], width, dtype=W.dtype, device=X.device)
+            part = torch.zeros(*X.shape[:-1], W.shape[1], dtype=W.dtype, device=X.device)
+            if gather_output and world > 1:
+                return torch.cat([part] * world, dim=-1)
+            return part
         if W.shape[0] != num_experts:
             raise ValueError(f"W has {W.shape[0]} experts, num_experts={num_experts}")
         y = moe_grouped_linear(X, expert_offset, W, B)

@@ -1,0 +1,72 @@
+"""Tensor-parallel MoE block on 2 GPUs (NCCL) against the single-process oracle.
+Skipped where fewer than two devices are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        group = dist.new_group(list(range(world)))
+        from oracle import moe_oracle as orc
+        from ppl.pmx_b200 import workloads as W
+        from ppl.pmx_b200.moe_layers import MoeFeedForward
+        for base, kw in (("decode_t64", dict(H=512, I=1024)), ("prefill", dict(T=1024, H=256, I=512))):
+            sh = W.scaled(W.WORKLOADS[base], **kw)
+            x, wr, sc, _ = W.make_activations(sh)
+            full_u, full_d = W.make_expert_weights(sh, dev)
+            f = lambda t: t.detach().float().cpu().numpy()
+            ref = orc.moe_block(f(x), f(wr), f(full_u), f(full_d), sh.E, sh.k, sh.dtype, scores=f(sc),
+                                round_intermediates=False)
+            for fused in (True, False):
+                blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, False, fused=fused).to(dev, W.TORCH_DTYPE[sh.dtype])
+                u, d = W.make_expert_weights(sh, dev, tp_rank=rank, tp_size=world)
+                with torch.no_grad():
+                    blk.wu.weight.copy_(u)
+                    blk.w2.weight.copy_(d)
+                    out = blk(x.to(dev), router_logits=sc.to(dev))
+                torch.cuda.synchronize()
+                np.testing.assert_allclose(f(out), ref["out"], atol=2e-2, rtol=1e-2,
+                                           err_msg=f"{sh.name} fused={fused} rank={rank}")
+        q.put((rank, "ok"))
+    except Exception:                            # noqa: BLE001
+        import traceback
+        q.put((rank, traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_block_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
