@@ -175,6 +175,9 @@ def main():
     ap.add_argument("--workload", default="decode_t64")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allreduce", default="auto", choices=["auto", "peer", "nccl"],
+                    help="N > 1: fused combine + all-reduce kernel over NVLink peer memory, or moe_reduce + NCCL "
+                         "(auto: peer when the [T,H] result is at most 4 MB)")
     ap.add_argument("--ffn-div", type=int, default=1,
                     help="divide the ffn size by this (small cases for profiler captures; traffic and flops scale with it)")
     args = ap.parse_args()
@@ -213,7 +216,10 @@ def main():
     x_host, w_router, _, _ = W.make_activations(shape, detie=False)
     x_host = x_host.pin_memory()
     out_host = torch.empty(shape.T, shape.H, dtype=dt).pin_memory()
-    blk = MoeFeedForward(shape.H, shape.I, shape.E, shape.k, group, False).to(device, dt)
+    result_bytes = shape.T * shape.H * torch.empty((), dtype=dt).element_size()
+    use_peer = world > 1 and (args.allreduce == "peer" or (args.allreduce == "auto" and result_bytes <= (4 << 20)))
+    blk = MoeFeedForward(shape.H, shape.I, shape.E, shape.k, group, False,
+                         peer_reduce_tokens=shape.T if use_peer else 0).to(device, dt)
     wu, w2 = W.make_expert_weights(shape, device, tp_rank=rank, tp_size=world)
     with torch.no_grad():
         blk.gate.weight.copy_(w_router)
@@ -284,7 +290,7 @@ def main():
         ms_e2e = timed(e2e_step, args.steps)
 
         # instrumented eager pass: CUDA events around every launch of the step
-        names = ["gate", "select", "gate_up", "down", "reduce", "allreduce"]
+        names = ["gate", "select", "gate_up", "down", "reduce", "allreduce", "reduce_allreduce"]
         ev = {n: [] for n in names}
 
         def probe(name, fn):
@@ -303,6 +309,9 @@ def main():
                 h = probe("gate_up", lambda: moe_grouped_linear(xe.view(-1, shape.H), off, blk.wu.weight, None,
                                                                 swiglu=True, zero_outside=False))
                 y = probe("down", lambda: moe_grouped_linear(h, off, blk.w2.weight, None, zero_outside=False))
+                if use_peer:
+                    probe("reduce_allreduce", lambda: blk._peer.combine_allreduce(y, ew, inv, k))
+                    continue
                 o = probe("reduce", lambda: OPMX.moe_reduce(y.view(shape.T, k, -1), ew, inv, k))
                 if world > 1:
                     probe("allreduce", lambda: dist.all_reduce(o, group=group))
@@ -356,6 +365,7 @@ def main():
             "roofline": roof,
             "layer": {"ms_floor": layer_floor_s * 1e3, "frac_of_roofline": layer_floor_s * 1e3 / ms_step,
                       "active_experts": active, "graph": graph is not None,
+                      "allreduce": ("peer-memory kernel fused with the combine" if use_peer else "nccl") if world > 1 else None,
                       "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items()}},
         }
         if world == 1 and not args.no_cpu_baseline:

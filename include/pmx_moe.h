@@ -174,6 +174,33 @@ int pmx_moe_reduce(const void* y, const void* expert_weights,
                    const int64_t* invert_permutation, void* out, int64_t T,
                    int32_t k, int64_t N, int32_t dtype, void* stream);
 
+/*
+ * moe_reduce fused with the tensor-parallel all-reduce over NVLink peer memory:
+ *   out[t,:] = sum over ranks r of  sum_j expert_weights[t,j] * y_r[invert_permutation[t,j],:]
+ * i.e. MoeReduce.forward (torch_function/MoeReduce.py:23-25) applied to the
+ * all-reduced output of MoeRowParallelLinear.forward
+ * (torch_function/MoeRowParallelLinear.py:57-58), with the sum over ranks moved
+ * after the weighted combine (same sum, another order; [T,N] crosses NVLink
+ * instead of [T*k,N]).  Every rank of the group calls it once per step with its
+ * own partial y_r; all ranks must pass identical expert_weights and
+ * invert_permutation (the routing is replicated).
+ *   peer_buffers: host array of `world` device pointers, entry r = rank r's
+ *   exchange buffer of pmx_moe_reduce_allreduce_buffer_bytes(T_max,N,dtype)
+ *   bytes, mapped into this process (CUDA IPC / symmetric memory), zeroed once
+ *   before the first call and followed by a barrier of the group.  All ranks
+ *   use the same T_max and N for the size.
+ * One-shot exchange (each rank reads world-1 buffers): meant for decode-size
+ * messages; use NCCL above a few MB.  Waits on peers are bounded (1 s);
+ * pmx_moe_reduce_allreduce_check reads the record a failed wait left behind.
+ */
+size_t pmx_moe_reduce_allreduce_buffer_bytes(int64_t T, int64_t N, int32_t dtype);
+int pmx_moe_reduce_allreduce(const void* y, const void* expert_weights,
+                             const int64_t* invert_permutation, void* out,
+                             int64_t T, int32_t k, int64_t N, int32_t dtype,
+                             void* const* peer_buffers, int32_t rank,
+                             int32_t world, size_t buffer_bytes, void* stream);
+int pmx_moe_reduce_allreduce_check(const void* my_buffer, int32_t out[4], void* stream);
+
 #ifdef __cplusplus
 }
 #endif

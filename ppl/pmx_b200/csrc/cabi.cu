@@ -178,4 +178,22 @@ int pmx_moe_reduce(const void* y, const void* expert_weights, const int64_t* inv
   return launch_reduce(y, expert_weights, invert_permutation, out, T, k, N, dtype, (cudaStream_t)stream);
 }
 
+size_t pmx_moe_reduce_allreduce_buffer_bytes(int64_t T, int64_t N, int32_t dtype) {
+  if (T <= 0 || N <= 0) return 0;
+  return reduce_allreduce_buffer_bytes(T, N, dtype);
+}
+
+int pmx_moe_reduce_allreduce(const void* y, const void* expert_weights, const int64_t* invert_permutation,
+                             void* out, int64_t T, int32_t k, int64_t N, int32_t dtype,
+                             void* const* peer_buffers, int32_t rank, int32_t world,
+                             size_t buffer_bytes, void* stream) {
+  return launch_reduce_allreduce(y, expert_weights, invert_permutation, out, T, k, N, dtype, peer_buffers,
+                                 rank, world, buffer_bytes, (cudaStream_t)stream);
+}
+
+int pmx_moe_reduce_allreduce_check(const void* my_buffer, int32_t out[4], void* stream) {
+  if (!my_buffer || !out) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_reduce_allreduce_check: null pointer");
+  return reduce_allreduce_check(my_buffer, out, (cudaStream_t)stream);
+}
+
 }  // extern "C"

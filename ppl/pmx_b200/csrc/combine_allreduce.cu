@@ -1,0 +1,219 @@
+// moe_reduce fused with the tensor-parallel all-reduce, over NVLink peer memory.
+//
+// In the tensor-parallel MoE block every rank holds a partial down-projection
+// y_r [T*k, N].  The result is  out[t] = sum_r sum_j w[t,j] * y_r[inv[t,j]]
+// (MoeReduce.py:23-25 applied to the all-reduced rows of
+// MoeRowParallelLinear.py:57-58; the weighted combine is linear, so it can run
+// before the sum over ranks, which then moves [T,N] instead of [T*k,N]).
+//
+// One kernel per rank does both:
+//   1. combine the local rows into this rank's exchange buffer (T1, fp32 math);
+//   2. the last CTA to finish publishes the epoch number in every peer's flag
+//      word (release, system scope);
+//   3. every CTA waits (bounded) until all peers have published this epoch;
+//   4. each CTA sums its share of the rows over all ranks' buffers, reading the
+//      peers' buffers with plain 16-byte loads over NVLink, and writes `out`.
+// One-shot exchange: each rank pulls (world-1) * T*N*b bytes, which is the
+// right trade below a few MB (decode); larger messages stay with NCCL.
+//
+// Exchange buffer of a rank (the same layout on every rank, allocated
+// symmetrically by the host side):
+//   [0, 4096)      control: flags[src] written by peers, epoch counter, tickets,
+//                  status words
+//   [4096, ...)    two data buffers used alternately (epoch parity), so a rank
+//                  may start the next call while a slower peer still reads the
+//                  previous one.
+// The grid never exceeds one CTA per SM, so all CTAs are resident and the
+// ticket / flag waits cannot starve each other.  Waits are bounded to 1 s; on
+// expiry the CTA records where it gave up in the status words and skips the sum.
+#include "common.cuh"
+
+namespace pmx {
+namespace {
+
+constexpr int kMaxWorld = 16;
+constexpr size_t kCtrlBytes = 4096;
+constexpr unsigned long long kWaitNs = 1000000000ull;
+
+struct Ctrl {
+  unsigned int flags[kMaxWorld];  // flags[src] = last epoch published by rank src
+  unsigned int pad0[64 - kMaxWorld];
+  unsigned int epoch;             // last completed epoch of this rank
+  unsigned int ticket_combine;
+  unsigned int ticket_done;
+  unsigned int pad1[61];
+  int status[4];                  // code, peer, epoch, CTA
+};
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
+
+struct Peers {
+  char* base[kMaxWorld];
+};
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+combine_allreduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
+                         const int64_t* __restrict__ inv, T* __restrict__ out, int64_t Tn, int k,
+                         int64_t N, Peers peers, int rank, int world, size_t data_bytes) {
+  constexpr int V = kVec<T>;
+  __shared__ unsigned int s_epoch;
+  __shared__ int s_abort;
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(peers.base[rank]);
+  if (threadIdx.x == 0) {
+    s_epoch = *reinterpret_cast<volatile unsigned int*>(&ctrl->epoch) + 1u;
+    s_abort = 0;
+  }
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
+  const size_t data_off = kCtrlBytes + (epoch & 1u) * data_bytes;
+  const int64_t chunks = N / V, total = Tn * chunks;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+
+  // 1. local weighted combine -> my exchange buffer
+  T* mine = reinterpret_cast<T*>(peers.base[rank] + data_off);
+  for (int64_t i = first; i < total; i += stride) {
+    const int64_t t = i / chunks, c = i - t * chunks;
+    float acc[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[v] = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const int64_t r = inv[t * k + j];
+      const float wj = Elem<T>::to_f(w[t * k + j]);
+      float f[V];
+      unpack16<T>(ld_nc16(y + r * N + c * V), f);
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[v] = fmaf(wj, f[v], acc[v]);
+    }
+    *reinterpret_cast<uint4*>(mine + t * N + c * V) = pack16<T>(acc);
+  }
+  __syncthreads();
+  // 2. last CTA publishes the epoch to every peer
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int done = atomicAdd(&ctrl->ticket_combine, 1u);
+    if (done == gridDim.x - 1) {
+      ctrl->ticket_combine = 0;
+      __threadfence_system();
+      for (int p = 0; p < world; ++p)
+        if (p != rank) st_release_sys(&reinterpret_cast<Ctrl*>(peers.base[p])->flags[rank], epoch);
+    }
+  }
+  // 3. wait for every peer's epoch (thread p watches peer p)
+  if (threadIdx.x < world && threadIdx.x != rank) {
+    const unsigned int* flag = &ctrl->flags[threadIdx.x];
+    const unsigned long long t0 = now_ns();
+    unsigned int it = 0;
+    while ((int)(ld_acquire_sys(flag) - epoch) < 0) {
+      if ((++it & 255u) == 0u && now_ns() - t0 > kWaitNs) {
+        s_abort = 1;
+        if (atomicCAS(&ctrl->status[0], 0, 1) == 0) {
+          ctrl->status[1] = threadIdx.x;
+          ctrl->status[2] = (int)epoch;
+          ctrl->status[3] = blockIdx.x;
+        }
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  // 4. sum over ranks
+  if (!s_abort) {
+    for (int64_t i = first; i < total; i += stride) {
+      float acc[V];
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[v] = 0.f;
+      for (int p = 0; p < world; ++p) {
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(peers.base[p] + data_off) + i);
+        float f[V];
+        unpack16<T>(raw, f);
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc[v] += f[v];
+      }
+      reinterpret_cast<uint4*>(out)[i] = pack16<T>(acc);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(&ctrl->ticket_done, 1u);
+    if (done == gridDim.x - 1) {
+      ctrl->ticket_done = 0;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(&ctrl->epoch) = epoch;
+    }
+  }
+}
+
+}  // namespace
+
+size_t reduce_allreduce_buffer_bytes(int64_t T, int64_t N, int dtype) {
+  const size_t b = dtype == PMX_DTYPE_F32 ? 4 : 2;
+  const size_t data = (size_t)ceil_div((int64_t)(T * N * b), 256) * 256;
+  return kCtrlBytes + 2 * data;
+}
+
+int launch_reduce_allreduce(const void* y, const void* w, const int64_t* inv, void* out, int64_t Tn,
+                            int k, int64_t N, int dtype, void* const* peer_buffers, int rank,
+                            int world, size_t buffer_bytes, cudaStream_t s) {
+  if (!y || !w || !inv || !out || !peer_buffers)
+    return fail(PMX_ERR_INVALID_ARGUMENT, "moe_reduce_allreduce: null pointer");
+  if (Tn <= 0 || k <= 0 || N <= 0) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_reduce_allreduce: T, k, N must be positive");
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
+    return fail(PMX_ERR_INVALID_ARGUMENT, "moe_reduce_allreduce: rank %d / world %d out of range (at most %d ranks)", rank, world, kMaxWorld);
+  const size_t need = reduce_allreduce_buffer_bytes(Tn, N, dtype);
+  if (buffer_bytes < need)
+    return fail(PMX_ERR_WORKSPACE, "moe_reduce_allreduce: exchange buffers of %zu bytes needed, %zu given", need, buffer_bytes);
+  const int vec = dtype == PMX_DTYPE_F32 ? 4 : 8;
+  if (N % vec || !aligned16(y) || !aligned16(out))
+    return fail(PMX_ERR_ALIGNMENT, "moe_reduce_allreduce: N must be a multiple of %d elements and y, out 16-byte aligned", vec);
+  Peers peers{};
+  for (int p = 0; p < world; ++p) {
+    if (!peer_buffers[p] || !aligned16(peer_buffers[p]))
+      return fail(PMX_ERR_INVALID_ARGUMENT, "moe_reduce_allreduce: exchange buffer of rank %d missing or misaligned", p);
+    peers.base[p] = reinterpret_cast<char*>(peer_buffers[p]);
+  }
+  const size_t data_bytes = (need - kCtrlBytes) / 2;
+  const int64_t items = Tn * (N / vec);
+  int64_t blocks = ceil_div(items, 256);
+  if (blocks > sm_count()) blocks = sm_count();  // all CTAs resident: one per SM at most
+  switch (dtype) {
+    case PMX_DTYPE_F16:
+      combine_allreduce_kernel<__half><<<(int)blocks, 256, 0, s>>>((const __half*)y, (const __half*)w, inv, (__half*)out, Tn, k, N, peers, rank, world, data_bytes);
+      break;
+    case PMX_DTYPE_BF16:
+      combine_allreduce_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)w, inv, (__nv_bfloat16*)out, Tn, k, N, peers, rank, world, data_bytes);
+      break;
+    case PMX_DTYPE_F32:
+      combine_allreduce_kernel<float><<<(int)blocks, 256, 0, s>>>((const float*)y, (const float*)w, inv, (float*)out, Tn, k, N, peers, rank, world, data_bytes);
+      break;
+    default:
+      return fail(PMX_ERR_UNSUPPORTED, "moe_reduce_allreduce: unknown dtype %d", dtype);
+  }
+  PMX_LAUNCHED();
+  return PMX_OK;
+}
+
+int reduce_allreduce_check(const void* my_buffer, int out[4], cudaStream_t s) {
+  const Ctrl* ctrl = reinterpret_cast<const Ctrl*>(my_buffer);
+  PMX_CUDA_OK(cudaMemcpyAsync(out, ctrl->status, 4 * sizeof(int), cudaMemcpyDeviceToHost, s));
+  PMX_CUDA_OK(cudaStreamSynchronize(s));
+  if (out[0] != 0)
+    return fail(PMX_ERR_DEVICE_CHECK, "moe_reduce_allreduce: gave up waiting for rank %d in epoch %d (CTA %d)", out[1], out[2], out[3]);
+  return PMX_OK;
+}
+
+}  // namespace pmx

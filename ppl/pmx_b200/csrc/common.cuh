@@ -88,6 +88,11 @@ int launch_swiglu(const void* x, void* y, int64_t M, int64_t D, float beta, int 
 int launch_silu(const void* x, const void* gate, void* y, int64_t n, int dtype, cudaStream_t s);
 int launch_reduce(const void* y, const void* w, const int64_t* inv, void* out, int64_t T, int k,
                   int64_t N, int dtype, cudaStream_t s);
+size_t reduce_allreduce_buffer_bytes(int64_t T, int64_t N, int dtype);
+int launch_reduce_allreduce(const void* y, const void* w, const int64_t* inv, void* out, int64_t T,
+                            int k, int64_t N, int dtype, void* const* peer_buffers, int rank,
+                            int world, size_t buffer_bytes, cudaStream_t s);
+int reduce_allreduce_check(const void* my_buffer, int out[4], cudaStream_t s);
 int launch_zero_outside(void* y, const int64_t* off, int64_t M, int64_t n_out, int E, int dtype,
                         cudaStream_t s);
 int launch_splitk_finish(const float* partial, const int64_t* off, const void* bias, void* y,

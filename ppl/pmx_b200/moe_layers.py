@@ -87,13 +87,17 @@ class MoeFeedForward(nn.Module):
 
     def __init__(self, hidden_dim: int, intermediate_dim: int, num_experts: int,
                  num_experts_per_token: int, proc_group=None, linear_bias_term: bool = False,
-                 fused: bool = True) -> None:
+                 fused: bool = True, peer_reduce_tokens: int = 0) -> None:
         super().__init__()
         self.num_experts = num_experts
         self.num_experts_per_token = num_experts_per_token
         self.proc_group = proc_group
         self.fused = fused
         self.hidden_dim = hidden_dim
+        # peer_reduce_tokens > 0: for up to that many tokens the combine and the
+        # all-reduce run as one kernel over NVLink peer memory (set up on first use)
+        self.peer_reduce_tokens = peer_reduce_tokens
+        self._peer = None
         self.gate = nn.Linear(hidden_dim, num_experts, bias=False)
         self.wu = MoeColumnParallelLinear(proc_group, num_experts, hidden_dim, 2 * intermediate_dim,
                                           bias_term=linear_bias_term, gather_output=False)
@@ -117,6 +121,12 @@ class MoeFeedForward(nn.Module):
         if bias2 is not None and world > 1 and dist.get_rank(group=self.proc_group) != 0:
             bias2 = None
         y = moe_grouped_linear(h, expert_offset, self.w2.weight, bias2, zero_outside=False)
+        if world > 1 and self.peer_reduce_tokens > 0:
+            if self._peer is None:
+                from .peer_reduce import PeerCombine
+                self._peer = PeerCombine(self.proc_group, self.peer_reduce_tokens, self.hidden_dim, y.dtype, y.device)
+            if self._peer.fits(expert_weights.numel() // k, self.hidden_dim, y.dtype):
+                return self._peer.combine_allreduce(y, expert_weights, invert_permutation, k)
         out = OPMX.moe_reduce(y.view(*expert_weights.shape, -1), expert_weights, invert_permutation, k)
         if world > 1:
             dist.all_reduce(out, group=self.proc_group)

@@ -269,6 +269,30 @@ def test_reduce_shapes(F, T, k, N, dtype):
     assert_close(out, orc.moe_reduce(y, w, inv, k), dtype)
 
 
+def test_reduce_allreduce_kernel_with_a_single_rank(F):
+    """The fused combine + all-reduce kernel with world = 1 (its exchange buffer is then
+    just local memory): same result as moe_reduce, on consecutive calls (epoch parity)."""
+    import ctypes as C
+    from ppl.pmx_b200._cabi import lib, check, ptr, stream_of
+    T, k, N = 70, 2, 512
+    nbytes = lib.pmx_moe_reduce_allreduce_buffer_bytes(T, N, 0)
+    buf = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    table = (C.c_void_p * 1)(buf.data_ptr())
+    for call in range(3):
+        rng = np.random.default_rng(call)
+        y = orc.round_to_dtype(rng.standard_normal((T * k, N)).astype(np.float32), "f16")
+        w = orc.round_to_dtype(rng.random((T, k)).astype(np.float32), "f16")
+        inv = rng.permutation(T * k).reshape(T, k)
+        out = torch.empty(T, N, dtype=torch.float16, device="cuda")
+        yd, wd, invd = dev(y, "f16"), dev(w, "f16"), torch.from_numpy(inv).cuda()
+        check(lib.pmx_moe_reduce_allreduce(ptr(yd), ptr(wd), ptr(invd), ptr(out), T, k, N, 0, table, 0, 1,
+                                           nbytes, stream_of(out)))
+        rec = (C.c_int32 * 4)()
+        check(lib.pmx_moe_reduce_allreduce_check(ptr(buf), C.byref(rec), stream_of(out)))
+        assert_close(out, orc.moe_reduce(y, w, inv, k), "f16")
+        assert torch.equal(out, F.moe_reduce(yd.view(T, k, N), wd, invd, k))
+
+
 # --------------------------------------------------------------------------- block
 @pytest.mark.parametrize("name", ["block_f32", "block_f16", "block_bf16", "block_f16_fine"])
 @pytest.mark.parametrize("fused", [False, True])

@@ -37,16 +37,38 @@ def _worker(rank, world, port, q):
             f = lambda t: t.detach().float().cpu().numpy()
             ref = orc.moe_block(f(x), f(wr), f(full_u), f(full_d), sh.E, sh.k, sh.dtype, scores=f(sc),
                                 round_intermediates=False)
-            for fused in (True, False):
-                blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, False, fused=fused).to(dev, W.TORCH_DTYPE[sh.dtype])
+            for fused, peer in ((True, 0), (False, 0), (True, sh.T)):
+                blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, False, fused=fused,
+                                     peer_reduce_tokens=peer).to(dev, W.TORCH_DTYPE[sh.dtype])
                 u, d = W.make_expert_weights(sh, dev, tp_rank=rank, tp_size=world)
+                xd, scd = x.to(dev), sc.to(dev)
                 with torch.no_grad():
                     blk.wu.weight.copy_(u)
                     blk.w2.weight.copy_(d)
-                    out = blk(x.to(dev), router_logits=sc.to(dev))
+                    for _ in range(3 if peer else 1):       # consecutive calls alternate the exchange buffers
+                        out = blk(xd, router_logits=scd)
                 torch.cuda.synchronize()
                 np.testing.assert_allclose(f(out), ref["out"], atol=2e-2, rtol=1e-2,
-                                           err_msg=f"{sh.name} fused={fused} rank={rank}")
+                                           err_msg=f"{sh.name} fused={fused} peer={peer} rank={rank}")
+                if peer:
+                    blk._peer.check()
+                    # the same step captured in a CUDA graph and replayed
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side), torch.no_grad():
+                        blk(xd, router_logits=scd)
+                    torch.cuda.current_stream().wait_stream(side)
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph), torch.no_grad():
+                        gout = blk(xd, router_logits=scd)
+                    for _ in range(4):
+                        graph.replay()
+                    torch.cuda.synchronize()
+                    np.testing.assert_allclose(f(gout), ref["out"], atol=2e-2, rtol=1e-2,
+                                               err_msg=f"{sh.name} graph replay rank={rank}")
+                    blk._peer.check()
+                    graph.reset()
+                    del graph
         q.put((rank, "ok"))
     except Exception:                            # noqa: BLE001
         import traceback
