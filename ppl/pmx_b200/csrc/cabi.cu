@@ -124,7 +124,7 @@ size_t pmx_moe_grouped_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, i
   LinearChoice c;
   if (choose_linear(M, N, K, E, dtype, epilogue, plan, &c) != PMX_OK) return 0;
   if (!c.tc) return kStatusBytes;
-  return gemm_tc_workspace_bytes(M, epilogue == PMX_EPILOGUE_SWIGLU ? N / 2 : N, c.plan);
+  return gemm_tc_workspace_bytes(M, N, epilogue, c.plan);
 }
 
 int pmx_moe_grouped_linear(const void* x, const int64_t* expert_offset, const void* w,

@@ -96,7 +96,8 @@ int reduce_allreduce_check(const void* my_buffer, int out[4], cudaStream_t s);
 int launch_zero_outside(void* y, const int64_t* off, int64_t M, int64_t n_out, int E, int dtype,
                         cudaStream_t s);
 int launch_splitk_finish(const float* partial, const int64_t* off, const void* bias, void* y,
-                         int64_t M, int64_t n_out, int E, int split, int dtype, cudaStream_t s);
+                         int64_t M, int64_t n_out, int E, int split, int dtype, bool swiglu,
+                         float beta, cudaStream_t s);
 
 int launch_gemm_simt(const void* x, const int64_t* off, const void* w, const void* bias, void* y,
                      int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue, float beta,
@@ -114,7 +115,9 @@ struct TcPlan {
 // outside what it covers (the caller then uses the CUDA-core kernel).
 bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue,
                   const pmx_gemm_plan* user, TcPlan* plan);
-size_t gemm_tc_workspace_bytes(int64_t M, int64_t n_out, const TcPlan& plan);
+// n_cols: columns of the accumulator the kernel produces (N, or N/2 when SwiGLU
+// runs in the kernel's epilogue)
+size_t gemm_tc_workspace_bytes(int64_t M, int64_t N, int epilogue, const TcPlan& plan);
 int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void* bias, void* y,
                    int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue, float beta,
                    const TcPlan& plan, void* ws, size_t ws_bytes, cudaStream_t s);

@@ -121,28 +121,45 @@ __global__ void zero_outside_kernel(T* __restrict__ y, const int64_t* __restrict
   }
 }
 
-// y[m,:] = cast(sum_s partial[s][m][:] (+ bias[e(m)])); rows no expert owns <- 0
-template <typename T>
+// y[m,:] = cast(sum_s partial[s][m][:] (+ bias[e(m)])); rows no expert owns <- 0.
+// With SWIGLU the partial rows hold [gate | up] (n_in = 2*n_out columns) and the
+// activation is applied to the finished sums: y = up * gate * sigmoid(beta*gate).
+template <typename T, bool SWIGLU>
 __global__ void splitk_finish_kernel(const float* __restrict__ partial,
                                      const int64_t* __restrict__ off, const T* __restrict__ bias,
-                                     T* __restrict__ y, int64_t M, int64_t n_out, int E, int split) {
+                                     T* __restrict__ y, int64_t M, int64_t n_out, int E, int split,
+                                     float beta) {
+  const int64_t n_in = SWIGLU ? 2 * n_out : n_out;
   const int64_t chunks = n_out / 4, total = M * chunks;
   const int64_t lo = off[0], hi = off[E];
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t m = i / chunks, c = (i - m * chunks) * 4;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), up = make_float4(0.f, 0.f, 0.f, 0.f);
     if (m >= lo && m < hi) {
       for (int s = 0; s < split; ++s) {
-        const float4 p = *reinterpret_cast<const float4*>(partial + ((int64_t)s * M + m) * n_out + c);
+        const float* row = partial + ((int64_t)s * M + m) * n_in;
+        const float4 p = *reinterpret_cast<const float4*>(row + c);
         acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+        if (SWIGLU) {
+          const float4 q = *reinterpret_cast<const float4*>(row + n_out + c);
+          up.x += q.x; up.y += q.y; up.z += q.z; up.w += q.w;
+        }
       }
       if (bias) {
         int e = 0;
         while (e + 1 < E && off[e + 1] <= m) ++e;
-        const T* b = bias + (int64_t)e * n_out + c;
+        const T* b = bias + (int64_t)e * n_in + c;
         acc.x += Elem<T>::to_f(b[0]); acc.y += Elem<T>::to_f(b[1]);
         acc.z += Elem<T>::to_f(b[2]); acc.w += Elem<T>::to_f(b[3]);
+        if (SWIGLU) {
+          up.x += Elem<T>::to_f(b[n_out]); up.y += Elem<T>::to_f(b[n_out + 1]);
+          up.z += Elem<T>::to_f(b[n_out + 2]); up.w += Elem<T>::to_f(b[n_out + 3]);
+        }
+      }
+      if (SWIGLU) {
+        acc.x = swiglu_f(acc.x, up.x, beta); acc.y = swiglu_f(acc.y, up.y, beta);
+        acc.z = swiglu_f(acc.z, up.z, beta); acc.w = swiglu_f(acc.w, up.w, beta);
       }
     }
     T* o = y + m * n_out + c;
@@ -217,11 +234,14 @@ int launch_zero_outside(void* y, const int64_t* off, int64_t M, int64_t n_out, i
 }
 
 int launch_splitk_finish(const float* partial, const int64_t* off, const void* bias, void* y,
-                         int64_t M, int64_t n_out, int E, int split, int dtype, cudaStream_t s) {
+                         int64_t M, int64_t n_out, int E, int split, int dtype, bool swiglu,
+                         float beta, cudaStream_t s) {
   if (n_out % 4) return fail(PMX_ERR_UNSUPPORTED, "grouped_linear: split-K needs N %% 4 == 0");
   PMX_DISPATCH_DTYPE(dtype, "grouped_linear", {
-    splitk_finish_kernel<T><<<grid_for(M * n_out / 4), kThreads, 0, s>>>(partial, off, (const T*)bias,
-                                                                         (T*)y, M, n_out, E, split);
+    if (swiglu)
+      splitk_finish_kernel<T, true><<<grid_for(M * n_out / 4), kThreads, 0, s>>>(partial, off, (const T*)bias, (T*)y, M, n_out, E, split, beta);
+    else
+      splitk_finish_kernel<T, false><<<grid_for(M * n_out / 4), kThreads, 0, s>>>(partial, off, (const T*)bias, (T*)y, M, n_out, E, split, beta);
   })
   PMX_LAUNCHED();
   return PMX_OK;

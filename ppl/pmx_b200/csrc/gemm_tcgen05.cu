@@ -555,28 +555,33 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
     pl.split_k = user->split_k;
   } else {
     pl.split_k = 1;
-    if (!swiglu) {
-      // experts with at least one row (estimate) x token tiles each
-      const int64_t act = M < E ? M : E;
-      const int64_t tok_tiles = act * (int64_t)ceil_div((int64_t)(avg_rows < 1 ? 1 : avg_rows), pl.tile_tok);
-      const int64_t items = tok_tiles * feat_tiles;
-      if (items < 2 * sms) {
-        int64_t want = ceil_div(2 * sms, items);
-        const int64_t cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
-        if (want > cap) want = cap;
-        if (want > 16) want = 16;
-        pl.split_k = (int)want;
-      }
+    // experts with at least one row (estimate) x token tiles each
+    const int64_t act = M < E ? M : E;
+    const int64_t tok_tiles = act * (int64_t)ceil_div((int64_t)(avg_rows < 1 ? 1 : avg_rows), pl.tile_tok);
+    const int64_t items = tok_tiles * feat_tiles;
+    if (items < 2 * sms) {
+      // too few work items to keep every SM streaming: slice K.  With SwiGLU the
+      // kernel then produces plain [gate | up] partial sums (twice the feature
+      // tiles) and the activation moves into the final sum.
+      const int64_t base = swiglu ? tok_tiles * ceil_div(N, pl.tile_feat) : items;
+      int64_t want = ceil_div((swiglu ? 4 : 2) * sms, base);
+      const int64_t cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
+      if (want > cap) want = cap;
+      if (want > 16) want = 16;
+      pl.split_k = (int)want;
     }
   }
-  if (pl.split_k < 1 || (swiglu && pl.split_k != 1)) return false;
+  if (pl.split_k < 1) return false;
   if (pl.split_k > kblocks) pl.split_k = kblocks;
   {
     const int per = (int)ceil_div(kblocks, pl.split_k);
     pl.split_k = (int)ceil_div(kblocks, per);  // no empty slice
   }
   if (pl.split_k > 1 && n_out % 4) return false;
-  const size_t stage = (size_t)(pl.tile_tok + (swiglu ? 2 : 1) * pl.tile_feat) * 128;
+  const bool kernel_swiglu = swiglu && pl.split_k == 1;
+  if (!kernel_swiglu && pl.kernel == PMX_GEMM_TC_TOKENS_M && !(user && user->tile_feat) && swiglu)
+    pl.tile_feat = pow2_at_least(N, 16, 256);
+  const size_t stage = (size_t)(pl.tile_tok + (kernel_swiglu ? 2 : 1) * pl.tile_feat) * 128;
   const size_t fixed = 1024 + sizeof(Shared) + 2 * (size_t)(E + 1) * sizeof(int);
   int st = (int)((227 * 1024 - fixed) / stage);
   if (st > 8) st = 8;
@@ -588,20 +593,23 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   return true;
 }
 
-size_t gemm_tc_workspace_bytes(int64_t M, int64_t n_out, const TcPlan& plan) {
+size_t gemm_tc_workspace_bytes(int64_t M, int64_t N, int epilogue, const TcPlan& plan) {
   size_t b = kStatusBytes;
-  if (plan.split_k > 1) b += (size_t)plan.split_k * M * n_out * sizeof(float);
+  // split-K partial sums cover all N accumulator columns (SwiGLU is then applied in the final sum)
+  if (plan.split_k > 1) b += (size_t)plan.split_k * M * N * sizeof(float);
+  (void)epilogue;
   return b;
 }
 
 int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void* bias, void* y,
                    int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue, float beta,
                    const TcPlan& plan, void* ws, size_t ws_bytes, cudaStream_t s) {
-  const bool swiglu = epilogue == PMX_EPILOGUE_SWIGLU;
-  const int64_t n_out = swiglu ? N / 2 : N;
+  const bool swiglu_any = epilogue == PMX_EPILOGUE_SWIGLU;
+  const bool swiglu = swiglu_any && plan.split_k == 1;   // SwiGLU inside the kernel's epilogue
+  const int64_t n_out = swiglu ? N / 2 : N;               // accumulator columns the kernel stores
   if (!aligned16(x) || !aligned16(w) || !aligned16(y))
     return fail(PMX_ERR_ALIGNMENT, "grouped_linear: x, w and y must be 16-byte aligned");
-  const size_t need = gemm_tc_workspace_bytes(M, n_out, plan);
+  const size_t need = gemm_tc_workspace_bytes(M, N, epilogue, plan);
   if (!ws || ws_bytes < need) return fail(PMX_ERR_WORKSPACE, "grouped_linear: workspace of %zu bytes needed, %zu given", need, ws_bytes);
   if (!aligned16(ws)) return fail(PMX_ERR_ALIGNMENT, "grouped_linear: workspace must be 16-byte aligned");
 
@@ -643,7 +651,8 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
 #undef PMX_TC_LAUNCH
   if (st != PMX_OK) return st;
   if (plan.split_k > 1)
-    return launch_splitk_finish(reinterpret_cast<const float*>(p.y), off, bias, y, M, n_out, E, plan.split_k, dtype, s);
+    return launch_splitk_finish(reinterpret_cast<const float*>(p.y), off, bias, y, M,
+                                swiglu_any ? N / 2 : N, E, plan.split_k, dtype, swiglu_any, beta, s);
   return PMX_OK;
 }
 

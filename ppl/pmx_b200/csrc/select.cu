@@ -180,6 +180,147 @@ __global__ void place_gather_kernel(const T* __restrict__ x, const int* __restri
   }
 }
 
+// ---- single-launch variant for decode-size batches ---------------------------
+// Every block repeats the routing of ALL tokens (a thread per token, cheap for
+// T <= 1024) instead of exchanging counts through global memory, then gathers
+// only its own tokens.  Because the k experts of one token are distinct, the
+// stable position of slot (t, j) with expert e is
+//     expert_offset[e] + number of tokens t' < t that selected e,
+// which comes from warp ballots: B[g][e] = ballot over the 32 tokens of group g
+// of "token selected e".
+constexpr int kSmallMaxTokens = 1024;
+constexpr int kSmallMaxExperts = 64;
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+select_small_kernel(const T* __restrict__ x, const T* __restrict__ scores, int Tn, int64_t H, int E,
+                    int k, int tpb, T* __restrict__ xp, T* __restrict__ weights,
+                    int64_t* __restrict__ inv, int64_t* __restrict__ expert_offset) {
+  extern __shared__ unsigned int sm_small[];
+  const int groups = (Tn + 31) / 32;
+  unsigned int* ballots = sm_small;                                     // [groups][E]
+  int* group_base = reinterpret_cast<int*>(ballots + groups * E);       // [groups][E] tokens of earlier groups
+  int* offs = group_base + groups * E;                                   // [E+1]
+  short* ids = reinterpret_cast<short*>(offs + E + 1);                   // [groups*32][k]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const bool writer = blockIdx.x == 0;   // block 0 also writes the small outputs
+
+  for (int g = warp; g < groups; g += nwarps) {
+    const int t = g * 32 + lane;
+    unsigned long long mask = 0ull;      // experts selected by this token
+    if (t < Tn) {
+      const T* row = scores + (int64_t)t * E;
+      unsigned long long prev = ~0ull;
+      float vmax = 0.f, denom = 0.f;
+      for (int j = 0; j < k; ++j) {
+        unsigned long long best = 0ull;
+        for (int e = 0; e < E; ++e) {
+          const unsigned long long key =
+              ((unsigned long long)score_key(Elem<T>::to_f(row[e])) << 32) | (uint32_t)(0x7FFFFFFF - e);
+          if (key < prev && key > best) best = key;
+        }
+        prev = best;
+        const int e_sel = 0x7FFFFFFF - (int)(uint32_t)(best & 0xFFFFFFFFull);
+        ids[t * k + j] = (short)e_sel;
+        mask |= 1ull << e_sel;
+        const float v = Elem<T>::to_f(row[e_sel]);
+        if (j == 0) vmax = v;
+        denom += expf(v - vmax);
+      }
+      if (writer) {
+        for (int j = 0; j < k; ++j) {
+          const float v = Elem<T>::to_f(row[ids[t * k + j]]);
+          weights[(int64_t)t * k + j] = Elem<T>::from_f(expf(v - vmax) / denom);
+        }
+      }
+    }
+    for (int e = 0; e < E; ++e) {
+      const unsigned int b = __ballot_sync(0xFFFFFFFFu, (mask >> e) & 1ull);
+      if (lane == 0) ballots[g * E + e] = b;
+    }
+  }
+  __syncthreads();
+  // per expert: tokens in earlier groups, total, then offsets
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int g = 0; g < groups; ++g) {
+      group_base[g * E + e] = run;
+      run += __popc(ballots[g * E + e]);
+    }
+    offs[e + 1] = run;   // totals for now
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = offs[e + 1];
+      offs[e] = acc;
+      acc += c;
+    }
+    offs[E] = acc;
+  }
+  __syncthreads();
+  if (writer) {
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) expert_offset[e] = offs[e];
+    for (int s = threadIdx.x; s < Tn * k; s += blockDim.x) {
+      const int t = s / k, e = ids[s];
+      const int g = t >> 5, l = t & 31;
+      inv[s] = offs[e] + group_base[g * E + e] + __popc(ballots[g * E + e] & ((1u << l) - 1u));
+    }
+  }
+  // gather this block's tokens
+  const int t0 = blockIdx.x * tpb;
+  const int ntok = min(tpb, Tn - t0);
+  if (ntok <= 0) return;
+  int* pos = reinterpret_cast<int*>(ids + (size_t)groups * 32 * k);   // [tpb*k] rows of my slots
+  for (int i = threadIdx.x; i < ntok * k; i += blockDim.x) {
+    const int t = t0 + i / k, e = ids[t0 * k + i];
+    const int g = t >> 5, l = t & 31;
+    pos[i] = offs[e] + group_base[g * E + e] + __popc(ballots[g * E + e] & ((1u << l) - 1u));
+  }
+  __syncthreads();
+  if (VEC) {
+    const int chunks = (int)(H * sizeof(T) / 16);
+    const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)t0 * H);
+    uint4* dst = reinterpret_cast<uint4*>(xp);
+    for (int i = threadIdx.x; i < ntok * chunks; i += blockDim.x) {
+      const int tl = i / chunks, c = i - tl * chunks;
+      const uint4 v = __ldg(src + (int64_t)tl * chunks + c);
+      for (int j = 0; j < k; ++j) dst[(int64_t)pos[tl * k + j] * chunks + c] = v;
+    }
+  } else {
+    for (int64_t i = threadIdx.x; i < (int64_t)ntok * H; i += blockDim.x) {
+      const int tl = (int)(i / H);
+      const int64_t c = i - (int64_t)tl * H;
+      const T v = x[(int64_t)(t0 + tl) * H + c];
+      for (int j = 0; j < k; ++j) xp[(int64_t)pos[tl * k + j] * H + c] = v;
+    }
+  }
+}
+
+bool select_small_applies(int64_t T, int E, int k) {
+  return T <= kSmallMaxTokens && E <= kSmallMaxExperts && k <= 32;
+}
+
+template <typename T>
+int run_select_small(const void* x, const void* scores, void* xp, void* w, int64_t* inv, int64_t* off,
+                     int64_t Tn, int64_t H, int E, int k, cudaStream_t s) {
+  const int groups = (int)ceil_div(Tn, 32);
+  // tokens per block: spread the row copies over the SMs
+  int tpb = (int)ceil_div(Tn, (int64_t)sm_count());
+  if (tpb < 1) tpb = 1;
+  const int nblk = (int)ceil_div(Tn, tpb);
+  size_t smem = (size_t)groups * E * 8 + (size_t)(E + 1) * 4 + (size_t)groups * 32 * k * 2;
+  smem = ((smem + 3) & ~(size_t)3) + (size_t)tpb * k * 4 + 16;
+  const bool vec = (H * sizeof(T)) % 16 == 0 && aligned16(x) && aligned16(xp);
+  auto kern = vec ? select_small_kernel<T, true> : select_small_kernel<T, false>;
+  if (smem > 48 * 1024) PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<nblk, 256, smem, s>>>(reinterpret_cast<const T*>(x), reinterpret_cast<const T*>(scores), (int)Tn, H, E, k, tpb,
+                               reinterpret_cast<T*>(xp), reinterpret_cast<T*>(w), inv, off);
+  PMX_LAUNCHED();
+  return PMX_OK;
+}
+
 struct SelectGeometry {
   int tpb;
   int nblk;
@@ -204,6 +345,7 @@ SelectGeometry select_geometry(int64_t T, int E, int k) {
 template <typename T>
 int run_select(const void* x, const void* scores, void* xp, void* w, int64_t* inv, int64_t* off,
                int64_t Tn, int64_t H, int E, int k, void* ws, cudaStream_t s) {
+  if (select_small_applies(Tn, E, k)) return run_select_small<T>(x, scores, xp, w, inv, off, Tn, H, E, k, s);
   const SelectGeometry g = select_geometry(Tn, E, k);
   int* ids = reinterpret_cast<int*>(ws);
   int* counts = reinterpret_cast<int*>(reinterpret_cast<char*>(ws) + g.ids_bytes);

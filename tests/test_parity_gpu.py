@@ -215,6 +215,17 @@ def test_grouped_linear_split_k(F, kernel, split):
     assert not host(y)[:5].any() and not host(y)[81:].any()
 
 
+@pytest.mark.parametrize("kernel,split,M", [(2, 2, 16), (2, 4, 90), (1, 2, 300), (0, 0, 2), (0, 0, 40)])
+def test_grouped_linear_split_k_with_swiglu_in_the_final_sum(F, kernel, split, M):
+    """Few rows per expert: K is sliced, the kernel leaves fp32 [gate | up] partial sums and
+    the activation is applied when they are added up.  (0, 0) = the automatic plan."""
+    rng = np.random.default_rng(split + M)
+    plan = dict(kernel=kernel, split_k=split) if kernel else None
+    run_linear(F, rng, M, 512, 1024, 8, "f16", plan=plan, bias=True, swiglu=True,
+               off=ragged_offsets(rng, M, 8, empty=3))
+    run_linear(F, rng, M, 1024, 2048, 8, "bf16", plan=plan, swiglu=True)
+
+
 @pytest.mark.parametrize("tile", [dict(kernel=1, tile_feat=32), dict(kernel=1, tile_feat=64),
                                   dict(kernel=1, tile_feat=128, stages=2), dict(kernel=2, tile_tok=16),
                                   dict(kernel=2, tile_tok=64, stages=3), dict(kernel=2, tile_tok=256),

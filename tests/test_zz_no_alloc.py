@@ -37,7 +37,7 @@ def _call(fn_static, x, sc, E, k):
 def test_static_scratch_select_matches_workspace_select_twice():
     from oracle import moe_oracle as orc
     torch.cuda.set_device(0)
-    cases = [(777, 64, 8, 2, torch.float16, 1), (300, 40, 64, 8, torch.bfloat16, 2)]
+    cases = [(5000, 64, 8, 2, torch.float16, 1), (2100, 40, 64, 8, torch.bfloat16, 2)]   # sizes that use the scratch
     for T, H, E, k, dt, seed in cases:
         g = torch.Generator().manual_seed(seed)
         x = torch.randn(T, H, generator=g).to(dt).cuda()
