@@ -14,8 +14,8 @@ The line printed by rank 0:
             CUDA graph of the step, CUDA events on the launching stream, max over ranks
   e2e       the same with the step's input copied from pinned host memory and
             its output copied back inside the timed region, every step
-  roofline  the dominant kernel (gate/up grouped GEMM), timed with CUDA events
-            around that launch in an instrumented eager pass of K more steps
+  roofline  the dominant kernel (gate/up grouped GEMM): its launch alone captured in a
+            CUDA graph and replayed K times between two CUDA events, in the same run
   cpu_baseline  the CPU port of the reference algorithm (oracle/cpu_port.py) on
             the host cores of this machine, a bounded sample of the same workload
 """
@@ -289,34 +289,51 @@ def main():
         ms_total = timed(run_step, args.steps)
         ms_e2e = timed(e2e_step, args.steps)
 
-        # instrumented eager pass: CUDA events around every launch of the step
-        names = ["gate", "select", "gate_up", "down", "reduce", "allreduce", "reduce_allreduce"]
-        ev = {n: [] for n in names}
+        # per-stage pass: every stage of the step is captured in a CUDA graph of its own and
+        # replayed K times between two CUDA events (no host launch gaps inside the figure);
+        # with --no-graph the stages are launched eagerly instead
+        names = ["gate", "select", "route_select", "gate_up", "down", "reduce", "allreduce", "reduce_allreduce"]
+        kernel_ms = {n: 0.0 for n in names}
+        keep = []
 
-        def probe(name, fn):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            r = fn()
-            b.record()
-            ev[name].append((a, b))
+        def stage(name, fn):
+            with torch.no_grad():
+                r = fn()                                   # eager: produces the next stage's inputs
+                if args.no_graph:
+                    run = fn
+                else:
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side):
+                        fn()
+                    torch.cuda.current_stream().wait_stream(side)
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        fn()
+                    keep.append(g)
+                    run = g.replay
+                kernel_ms[name] = timed(run, args.steps) / args.steps
             return r
 
         sync_all()
-        with torch.no_grad():
-            for _ in range(args.steps):
-                logits = probe("gate", lambda: torch.nn.functional.linear(x_dev, blk.gate.weight))
-                xe, ew, inv, off = probe("select", lambda: OPMX.moe_select(x_dev, logits, E, k))
-                h = probe("gate_up", lambda: moe_grouped_linear(xe.view(-1, shape.H), off, blk.wu.weight, None,
-                                                                swiglu=True, zero_outside=False))
-                y = probe("down", lambda: moe_grouped_linear(h, off, blk.w2.weight, None, zero_outside=False))
-                if use_peer:
-                    probe("reduce_allreduce", lambda: blk._peer.combine_allreduce(y, ew, inv, k))
-                    continue
-                o = probe("reduce", lambda: OPMX.moe_reduce(y.view(shape.T, k, -1), ew, inv, k))
-                if world > 1:
-                    probe("allreduce", lambda: dist.all_reduce(o, group=group))
+        if OPMX.moe_route_select(x_dev, blk.gate.weight, E, k) is not None:
+            _, xe, ew, inv, off = stage("route_select", lambda: OPMX.moe_route_select(x_dev, blk.gate.weight, E, k))
+        else:
+            logits = stage("gate", lambda: torch.nn.functional.linear(x_dev, blk.gate.weight))
+            xe, ew, inv, off = stage("select", lambda: OPMX.moe_select(x_dev, logits, E, k))
+        h = stage("gate_up", lambda: moe_grouped_linear(xe.view(-1, shape.H), off, blk.wu.weight, None,
+                                                        swiglu=True, zero_outside=False))
+        y = stage("down", lambda: moe_grouped_linear(h, off, blk.w2.weight, None, zero_outside=False))
+        if use_peer:
+            stage("reduce_allreduce", lambda: blk._peer.combine_allreduce(y, ew, inv, k))
+        else:
+            o = stage("reduce", lambda: OPMX.moe_reduce(y.view(shape.T, k, -1), ew, inv, k))
+            if world > 1:
+                stage("allreduce", lambda: dist.all_reduce(o, group=group))
         sync_all()
-    kernel_ms = {n: (sum(a.elapsed_time(b) for a, b in v) / len(v) if v else 0.0) for n, v in ev.items()}
+        for g in keep:
+            g.reset()
+        del keep
     active = int((off[1:] - off[:-1]).gt(0).sum().item())
 
     if rank == 0:
@@ -350,7 +367,7 @@ def main():
         roof.update({"traffic": work["bytes_gate_up"] * ratio if ratio else None, "kernel": "grouped_gemm_tc_kernel (gate/up projection + SwiGLU)",
                      "kernel_ms": kernel_ms["gate_up"], "peak_source": peaks["source"],
                      "algorithmic_bytes": work["bytes_gate_up"], "algorithmic_flops": work["flops_gate_up"],
-                     "timing": "CUDA events around the launch, instrumented eager pass of the same steps"})
+                     "timing": "CUDA events around K back-to-back replays of a CUDA graph holding this launch alone, same run"})
         # whole-layer figures against the layer's own roofline
         layer_floor_s = max(work["bytes"] / (peaks["hbm_gbs"] * 1e9), work["flops"] / (tensor_peak * 1e12))
         line = {

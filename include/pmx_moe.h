@@ -95,6 +95,26 @@ int pmx_moe_select(const void* x, const void* scores, void* x_expand_permute,
                    size_t workspace_bytes, void* stream);
 
 /*
+ * Router gate + moe_select in one launch, for decode-size batches: replaces
+ * Linear.forward (torch_function/Linear.py:24-33, the `gate` call at
+ * model_zoo/mixtral/modeling/dynamic_batching/Model.py:188) followed by
+ * MoeSelect.forward (torch_function/MoeSelect.py:36-64).
+ *   x [T,H] T1, w_router [E,H] T1  ->  scores [T,E] T1 = x . w_router^T (fp32
+ *   accumulation, one rounding), then the four outputs of pmx_moe_select computed
+ *   from exactly those scores.
+ * Covers 1 <= T <= 1024, E <= 64, k <= 32, H*sizeof(T1) a multiple of 16;
+ * pmx_moe_route_select_workspace_bytes returns 0 for other shapes (use a linear
+ * and pmx_moe_select then).  The launch is cooperative (its blocks meet at one
+ * bounded grid-wide barrier).
+ */
+size_t pmx_moe_route_select_workspace_bytes(int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype);
+int pmx_moe_route_select(const void* x, const void* w_router, void* scores,
+                         void* x_expand_permute, void* expert_weights,
+                         int64_t* invert_permutation, int64_t* expert_offset,
+                         int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * moe_select without a workspace argument.  Has no counterpart in the OPMX
  * reference: it exists for hosts that may not allocate device memory around
  * the call -- for example an inference-engine plug-in whose enqueue hook is

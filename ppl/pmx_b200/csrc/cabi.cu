@@ -111,6 +111,18 @@ int pmx_moe_select(const void* x, const void* scores, void* x_expand_permute, vo
                        T, H, E, k, dtype, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+size_t pmx_moe_route_select_workspace_bytes(int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype) {
+  return route_select_workspace_bytes(T, H, E, k, dtype);
+}
+
+int pmx_moe_route_select(const void* x, const void* w_router, void* scores, void* x_expand_permute,
+                         void* expert_weights, int64_t* invert_permutation, int64_t* expert_offset,
+                         int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  return launch_route_select(x, w_router, scores, x_expand_permute, expert_weights, invert_permutation,
+                             expert_offset, T, H, E, k, dtype, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
 int pmx_moe_select_static(const void* x, const void* scores, void* x_expand_permute,
                           void* expert_weights, int64_t* invert_permutation, int64_t* expert_offset,
                           int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype, void* stream) {

@@ -559,12 +559,14 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
     const int64_t act = M < E ? M : E;
     const int64_t tok_tiles = act * (int64_t)ceil_div((int64_t)(avg_rows < 1 ? 1 : avg_rows), pl.tile_tok);
     const int64_t items = tok_tiles * feat_tiles;
-    if (items < 2 * sms) {
-      // too few work items to keep every SM streaming: slice K.  With SwiGLU the
-      // kernel then produces plain [gate | up] partial sums (twice the feature
-      // tiles) and the activation moves into the final sum.
+    if (2 * items <= sms) {
+      // fewer work items than half the SMs (one token, or a thin tensor-parallel
+      // shard): slice K.  With SwiGLU the kernel then produces plain [gate | up]
+      // partial sums (twice the feature tiles) and the activation moves into the
+      // final sum.  Measured on B200: with more items than that the extra
+      // partial-sum traffic and launch cost more than the better balance gains.
       const int64_t base = swiglu ? tok_tiles * ceil_div(N, pl.tile_feat) : items;
-      int64_t want = ceil_div((swiglu ? 4 : 2) * sms, base);
+      int64_t want = ceil_div(2 * sms, base);
       const int64_t cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
       if (want > cap) want = cap;
       if (want > 16) want = 16;

@@ -88,39 +88,59 @@ __global__ void route_count_kernel(const T* __restrict__ scores, int64_t T_token
     }
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) block_counts[(int64_t)blockIdx.x * E + e] = hist[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) block_counts[(int64_t)e * gridDim.x + blockIdx.x] = hist[e];
 }
 
-// block_counts[nblk][E] -> exclusive prefix over blocks in place; expert_offset.
-__global__ void scan_kernel(int* __restrict__ block_counts, int nblk, int E,
-                            int64_t* __restrict__ expert_offset) {
-  extern __shared__ int totals[];  // [E]
+// block_counts[E][nblk] -> exclusive prefix over blocks in place (one block of
+// threads per expert, coalesced); the last block to finish turns the per-expert
+// totals into expert_offset.
+__global__ void scan_kernel(int* __restrict__ block_counts, int nblk, int E, int* __restrict__ totals,
+                            unsigned int* __restrict__ ticket, int64_t* __restrict__ expert_offset) {
+  __shared__ int warp_sum[32];
+  __shared__ int carry;
+  __shared__ bool last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int e = warp; e < E; e += nwarps) {
-    int running = 0;
-    for (int b0 = 0; b0 < nblk; b0 += 32) {
-      const int b = b0 + lane;
-      const int v = b < nblk ? block_counts[(int64_t)b * E + e] : 0;
-      int incl = v;
+  const int e = blockIdx.x;
+  int* col = block_counts + (int64_t)e * nblk;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int b0 = 0; b0 < nblk; b0 += blockDim.x) {
+    const int b = b0 + threadIdx.x;
+    const int v = b < nblk ? col[b] : 0;
+    int incl = v;
 #pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        int n = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-        if (lane >= o) incl += n;
-      }
-      if (b < nblk) block_counts[(int64_t)b * E + e] = running + incl - v;
-      running += __shfl_sync(0xFFFFFFFFu, incl, 31);
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+      if (lane >= o) incl += n;
     }
-    if (lane == 0) totals[e] = running;
+    if (lane == 31) warp_sum[warp] = incl;
+    __syncthreads();
+    int before = carry;
+    for (int w = 0; w < warp; ++w) before += warp_sum[w];
+    if (b < nblk) col[b] = before + incl - v;
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) carry = before + incl;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    totals[e] = carry;
+    __threadfence();
+    last = atomicAdd(ticket, 1u) == gridDim.x - 1;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int64_t acc = 0;
-    for (int e = 0; e < E; ++e) {
-      expert_offset[e] = acc;
-      acc += totals[e];
+  if (last) {
+    __threadfence();
+    if (threadIdx.x == 0) {
+      int64_t acc = 0;
+      for (int i = 0; i < E; ++i) {
+        expert_offset[i] = acc;
+        acc += *reinterpret_cast<volatile int*>(&totals[i]);
+      }
+      expert_offset[E] = acc;
+      *ticket = 0;
     }
-    expert_offset[E] = acc;
   }
+  (void)nwarps;
 }
 
 template <typename T, bool VEC>
@@ -137,7 +157,7 @@ __global__ void place_gather_kernel(const T* __restrict__ x, const int* __restri
   const int nslots = ntok * k;
   const int64_t slot0 = t0 * k;
   for (int e = threadIdx.x; e < E; e += blockDim.x)
-    cursor[e] = (int)expert_offset[e] + block_base[(int64_t)blockIdx.x * E + e];
+    cursor[e] = (int)expert_offset[e] + block_base[(int64_t)e * gridDim.x + blockIdx.x];
   __syncthreads();
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
@@ -321,6 +341,195 @@ int run_select_small(const void* x, const void* scores, void* xp, void* w, int64
   return PMX_OK;
 }
 
+// ---- router gate + select in one cooperative launch ---------------------------
+// For decode-size batches the router logits (Linear.forward, Linear.py:24-33,
+// called at Model.py:188) are computed by the same kernel that routes: each
+// block computes the E logits of its own tokens (fp32 accumulation, one rounding
+// to T1 -- the scores the reference would hand to moe_select), picks their top-k
+// and publishes one 64-bit expert mask per token; after a grid-wide barrier
+// (bounded spin on a counter; the launch is cooperative, so all blocks are
+// resident) every block derives the stable positions of its own slots from the
+// masks of all tokens and gathers its rows.
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, int64_t H, int E, int k,
+                    int tpb, T* __restrict__ scores, T* __restrict__ xp, T* __restrict__ weights,
+                    int64_t* __restrict__ inv, int64_t* __restrict__ expert_offset,
+                    unsigned long long* __restrict__ masks, unsigned int* __restrict__ counter,
+                    int* __restrict__ status) {
+  extern __shared__ unsigned int sm_rs[];
+  const int groups = (Tn + 31) / 32;
+  unsigned int* ballots = sm_rs;                                        // [groups][E]
+  int* group_base = reinterpret_cast<int*>(ballots + groups * E);      // [groups][E]
+  int* offs = group_base + groups * E;                                  // [E+1]
+  float* logit = reinterpret_cast<float*>(offs + E + 1);                // [tpb][E]
+  int* my_ids = reinterpret_cast<int*>(logit + tpb * E);                // [tpb][k]
+  int* pos = my_ids + tpb * k;                                          // [tpb][k]
+  float* partial = reinterpret_cast<float*>(pos + tpb * k);             // [warps][E]
+  __shared__ int s_abort;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int t0 = blockIdx.x * tpb;
+  const int ntok = max(0, min(tpb, Tn - t0));
+  constexpr int V = kVec<T>;
+  const int chunks = (int)(H / V);
+  if (threadIdx.x == 0) s_abort = 0;
+
+  // A1. logits of my tokens.  The warps split the hidden dimension; every lane
+  // keeps 8 experts' partial dot products, so one pass issues 9 independent
+  // 16-byte loads per lane.  Partial sums meet in shared memory.
+  for (int tl = 0; tl < ntok; ++tl) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + (int64_t)(t0 + tl) * H);
+    for (int e0 = 0; e0 < E; e0 += 8) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        float a[V];
+        unpack16<T>(__ldg(xr + c), a);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (e0 + j < E) {
+            float b[V];
+            unpack16<T>(__ldg(reinterpret_cast<const uint4*>(wr + (int64_t)(e0 + j) * H) + c), b);
+#pragma unroll
+            for (int v = 0; v < V; ++v) acc[j] = fmaf(a[v], b[v], acc[j]);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xFFFFFFFFu, acc[j], o);
+        if (lane == 0 && e0 + j < E) partial[warp * E + e0 + j] = acc[j];
+      }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      float sum = 0.f;
+      for (int w = 0; w < nwarps; ++w) sum += partial[w * E + e];
+      const T r = Elem<T>::from_f(sum);
+      scores[(int64_t)(t0 + tl) * E + e] = r;
+      logit[tl * E + e] = Elem<T>::to_f(r);
+    }
+    __syncthreads();
+  }
+  // A2. top-k of my tokens (a thread per token), softmax weights, expert mask
+  if (threadIdx.x < ntok) {
+    const int tl = threadIdx.x, t = t0 + tl;
+    const float* row = logit + tl * E;
+    unsigned long long prev = ~0ull, mask = 0ull;
+    float vmax = 0.f, denom = 0.f;
+    for (int j = 0; j < k; ++j) {
+      unsigned long long best = 0ull;
+      for (int e = 0; e < E; ++e) {
+        const unsigned long long key = ((unsigned long long)score_key(row[e]) << 32) | (uint32_t)(0x7FFFFFFF - e);
+        if (key < prev && key > best) best = key;
+      }
+      prev = best;
+      const int e_sel = 0x7FFFFFFF - (int)(uint32_t)(best & 0xFFFFFFFFull);
+      my_ids[tl * k + j] = e_sel;
+      mask |= 1ull << e_sel;
+      if (j == 0) vmax = row[e_sel];
+      denom += expf(row[e_sel] - vmax);
+    }
+    for (int j = 0; j < k; ++j)
+      weights[(int64_t)t * k + j] = Elem<T>::from_f(expf(row[my_ids[tl * k + j]] - vmax) / denom);
+    masks[t] = mask;
+  }
+  // grid-wide barrier: everybody's masks are in global memory
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(counter, 1u);
+    unsigned long long t_start = 0;
+    unsigned int it = 0;
+    while (ld_acquire_gpu(counter) < gridDim.x) {
+      if ((++it & 1023u) == 0u) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (t_start == 0) t_start = now;
+        if (now - t_start > 1000000000ull) {   // 1 s: give up, record it
+          s_abort = 1;
+          atomicCAS(status, 0, 2);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (s_abort) return;
+
+  // B. ballots over all tokens from the masks
+  for (int g = warp; g < groups; g += nwarps) {
+    const int t = g * 32 + lane;
+    const unsigned long long m = t < Tn ? __ldcg(masks + t) : 0ull;
+    for (int e = 0; e < E; ++e) {
+      const unsigned int b = __ballot_sync(0xFFFFFFFFu, (m >> e) & 1ull);
+      if (lane == 0) ballots[g * E + e] = b;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int g = 0; g < groups; ++g) {
+      group_base[g * E + e] = run;
+      run += __popc(ballots[g * E + e]);
+    }
+    offs[e + 1] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = offs[e + 1];
+      offs[e] = acc;
+      acc += c;
+    }
+    offs[E] = acc;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0)
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) expert_offset[e] = offs[e];
+  for (int i = threadIdx.x; i < ntok * k; i += blockDim.x) {
+    const int t = t0 + i / k, e = my_ids[i];
+    const int g = t >> 5, l = t & 31;
+    const int p = offs[e] + group_base[g * E + e] + __popc(ballots[g * E + e] & ((1u << l) - 1u));
+    pos[i] = p;
+    inv[(int64_t)t0 * k + i] = p;
+  }
+  __syncthreads();
+  // C. gather my tokens
+  const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)t0 * H);
+  uint4* dst = reinterpret_cast<uint4*>(xp);
+  for (int i = threadIdx.x; i < ntok * chunks; i += blockDim.x) {
+    const int tl = i / chunks, c = i - tl * chunks;
+    const uint4 v = __ldg(src + (int64_t)tl * chunks + c);
+    for (int j = 0; j < k; ++j) dst[(int64_t)pos[tl * k + j] * chunks + c] = v;
+  }
+}
+
+struct RouteSelectGeometry {
+  int tpb, nblk;
+  size_t smem;
+};
+
+bool route_select_geometry(int64_t T, int64_t H, int E, int k, int dtype, RouteSelectGeometry* g) {
+  const int vec = dtype == PMX_DTYPE_F32 ? 4 : 8;
+  if (T <= 0 || T > kSmallMaxTokens || E <= 0 || E > kSmallMaxExperts || k <= 0 || k > 32 || k > E || H % vec) return false;
+  const int sms = sm_count();
+  g->tpb = (int)ceil_div(T, (int64_t)sms);
+  g->nblk = (int)ceil_div(T, g->tpb);
+  const int groups = (int)ceil_div(T, 32);
+  g->smem = ((size_t)groups * E * 2 + (E + 1) + (size_t)g->tpb * E + 2 * (size_t)g->tpb * k + 8 * (size_t)E) * 4 + 16;
+  return g->nblk <= sms;
+}
+
 struct SelectGeometry {
   int tpb;
   int nblk;
@@ -338,7 +547,8 @@ SelectGeometry select_geometry(int64_t T, int E, int k) {
   g.tpb = (int)tpb;
   g.nblk = (int)ceil_div(T, tpb);
   g.ids_bytes = (size_t)ceil_div(T * k * 4, 16) * 16;
-  g.counts_bytes = (size_t)ceil_div((int64_t)g.nblk * E * 4, 16) * 16;
+  // per-block counts [E][nblk], then per-expert totals [E] and the scan's ticket word
+  g.counts_bytes = (size_t)ceil_div(((int64_t)g.nblk * E + E + 4) * 4, 16) * 16;
   return g;
 }
 
@@ -353,7 +563,10 @@ int run_select(const void* x, const void* scores, void* xp, void* w, int64_t* in
   route_count_kernel<T><<<g.nblk, route_threads, E * sizeof(int), s>>>(
       reinterpret_cast<const T*>(scores), Tn, E, k, g.tpb, reinterpret_cast<T*>(w), ids, counts);
   PMX_LAUNCHED();
-  scan_kernel<<<1, 1024, E * sizeof(int), s>>>(counts, g.nblk, E, off);
+  int* totals = counts + (int64_t)g.nblk * E;
+  unsigned int* ticket = reinterpret_cast<unsigned int*>(totals + E);
+  PMX_CUDA_OK(cudaMemsetAsync(ticket, 0, sizeof(unsigned int), s));
+  scan_kernel<<<E, 256, 0, s>>>(counts, g.nblk, E, totals, ticket, off);
   PMX_LAUNCHED();
   const size_t sm_bytes = (size_t)(E + g.tpb * k) * sizeof(int);
   const bool vec = (H * sizeof(T)) % 16 == 0 && aligned16(x) && aligned16(xp);
@@ -396,6 +609,43 @@ int launch_select(const void* x, const void* scores, void* xp, void* w, int64_t*
   return fail(PMX_ERR_UNSUPPORTED, "moe_select: unknown dtype %d", dtype);
 }
 
+size_t route_select_workspace_bytes(int64_t T, int64_t H, int E, int k, int dtype) {
+  RouteSelectGeometry g;
+  if (!route_select_geometry(T, H, E, k, dtype, &g)) return 0;
+  return 64 + (size_t)T * 8;   // counter + status words, then one expert mask per token
+}
+
+int launch_route_select(const void* x, const void* wr, void* scores, void* xp, void* w, int64_t* inv,
+                        int64_t* off, int64_t T, int64_t H, int E, int k, int dtype, void* ws,
+                        size_t ws_bytes, cudaStream_t s) {
+  if (!x || !wr || !scores || !xp || !w || !inv || !off) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_route_select: null pointer");
+  RouteSelectGeometry g;
+  if (!route_select_geometry(T, H, E, k, dtype, &g))
+    return fail(PMX_ERR_UNSUPPORTED, "moe_route_select: covers 1..%d tokens, up to %d experts, k <= 32 and 16-byte rows (T=%lld E=%d k=%d H=%lld); use a linear followed by moe_select", kSmallMaxTokens, kSmallMaxExperts, (long long)T, E, k, (long long)H);
+  const size_t need = route_select_workspace_bytes(T, H, E, k, dtype);
+  if (!ws || ws_bytes < need) return fail(PMX_ERR_WORKSPACE, "moe_route_select: workspace of %zu bytes needed, %zu given", need, ws_bytes);
+  if (!aligned16(ws) || !aligned16(x) || !aligned16(wr) || !aligned16(xp))
+    return fail(PMX_ERR_ALIGNMENT, "moe_route_select: x, w_router, x_expand_permute and the workspace must be 16-byte aligned");
+  unsigned int* counter = reinterpret_cast<unsigned int*>(ws);
+  int* status = reinterpret_cast<int*>(ws) + 4;
+  unsigned long long* masks = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(ws) + 64);
+  PMX_CUDA_OK(cudaMemsetAsync(ws, 0, 64, s));
+  int Tn = (int)T;
+  void* args[] = {(void*)&x, (void*)&wr, (void*)&Tn, (void*)&H, (void*)&E, (void*)&k, (void*)&g.tpb, (void*)&scores,
+                  (void*)&xp, (void*)&w, (void*)&inv, (void*)&off, (void*)&masks, (void*)&counter, (void*)&status};
+  const void* kern = nullptr;
+  switch (dtype) {
+    case PMX_DTYPE_F16: kern = (const void*)route_select_kernel<__half>; break;
+    case PMX_DTYPE_BF16: kern = (const void*)route_select_kernel<__nv_bfloat16>; break;
+    case PMX_DTYPE_F32: kern = (const void*)route_select_kernel<float>; break;
+    default: return fail(PMX_ERR_UNSUPPORTED, "moe_route_select: unknown dtype %d", dtype);
+  }
+  if (g.smem > 48 * 1024) PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
+  PMX_CUDA_OK(cudaLaunchCooperativeKernel(kern, dim3(g.nblk), dim3(256), args, g.smem, s));
+  count_launches(1);
+  return PMX_OK;
+}
+
 // Device address of the built-in scratch on the current device, looked up once
 // per device (with that device current) and cached.
 int select_static_scratch(void** out) {
@@ -428,8 +678,9 @@ int launch_select_static(const void* x, const void* scores, void* xp, void* w, i
   void* scratch = nullptr;
   const int st = select_static_scratch(&scratch);
   if (st != PMX_OK) return st;
-  // nothing in the scratch has to start at zero: the routing kernel overwrites
-  // every id and every per-block count this call reads back
+  // the call prepares what it reads back: ids and per-block counts are
+  // overwritten by the routing kernel, the scan's ticket word is cleared by a
+  // memset node ahead of the scan; leftovers of earlier calls are never read
   return launch_select(x, scores, xp, w, inv, off, T, H, E, k, dtype, scratch, need, s);
 }
 

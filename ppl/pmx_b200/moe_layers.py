@@ -18,7 +18,7 @@ import torch.distributed as dist
 from torch import nn
 
 from . import torch_function as OPMX
-from .torch_function.moe import moe_grouped_linear
+from .torch_function.moe import moe_grouped_linear, moe_route_select
 
 
 def _world(proc_group) -> int:
@@ -105,10 +105,16 @@ class MoeFeedForward(nn.Module):
                                        bias_term=linear_bias_term, input_is_parallel=True)
 
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor | None = None) -> torch.Tensor:
-        if router_logits is None:
-            router_logits = torch.nn.functional.linear(x, self.gate.weight)
         E, k = self.num_experts, self.num_experts_per_token
-        x_experts, expert_weights, invert_permutation, expert_offset = OPMX.moe_select(x, router_logits, E, k)
+        routed = None
+        if router_logits is None and self.fused:
+            routed = moe_route_select(x, self.gate.weight, E, k)     # decode-size batches: one launch
+        if routed is not None:
+            _, x_experts, expert_weights, invert_permutation, expert_offset = routed
+        else:
+            if router_logits is None:
+                router_logits = torch.nn.functional.linear(x, self.gate.weight)
+            x_experts, expert_weights, invert_permutation, expert_offset = OPMX.moe_select(x, router_logits, E, k)
         if not self.fused:
             x13 = OPMX.swiglu(self.wu(x_experts, expert_offset))
             x_out = self.w2(x13, expert_offset)

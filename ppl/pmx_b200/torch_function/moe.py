@@ -103,6 +103,40 @@ def moe_select(X: torch.Tensor, scores: torch.Tensor, num_experts: int, num_expe
     return MoeSelect.apply(X, scores, num_experts, num_experts_per_token)
 
 
+def moe_route_select(X: torch.Tensor, W_router: torch.Tensor, num_experts: int, num_experts_per_token: int):
+    """Router gate and moe_select in one launch for decode-size batches:
+    scores = X @ W_router.T (Linear.py:24-33 as called at Model.py:188), then
+    MoeSelect (MoeSelect.py:36-64) on those scores.
+    -> (scores [*,E], X_expand_permute, expert_weights, invert_permutation, expert_offset),
+    or None when the shape is outside what the fused kernel covers (more than 1024
+    tokens, more than 64 experts, ...): call a linear and moe_select then."""
+    _require_cuda("moe_route_select", X=X, W_router=W_router)
+    k, E = int(num_experts_per_token), int(num_experts)
+    lead, H = tuple(X.shape[:-1]), X.shape[-1]
+    if tuple(W_router.shape) != (E, H) or W_router.dtype != X.dtype:
+        raise ValueError(f"W_router must be [{E}, {H}] in X's dtype")
+    T = 1
+    for d in lead:
+        T *= d
+    code = _dtype_code("moe_route_select", X)
+    nbytes = lib.pmx_moe_route_select_workspace_bytes(T, H, E, k, code) if T > 0 else 0
+    if nbytes == 0:
+        return None
+    dev = X.device
+    x2 = X.contiguous().view(T, H)
+    wr = W_router.contiguous()
+    scores = torch.empty(*lead, E, dtype=X.dtype, device=dev)
+    xp = torch.empty(*lead, k, H, dtype=X.dtype, device=dev)
+    w = torch.empty(*lead, k, dtype=X.dtype, device=dev)
+    inv = torch.empty(*lead, k, dtype=torch.int64, device=dev)
+    off = torch.empty(E + 1, dtype=torch.int64, device=dev)
+    ws = workspace(nbytes, dev)
+    with torch.cuda.device(dev):
+        check(lib.pmx_moe_route_select(ptr(x2), ptr(wr), ptr(scores), ptr(xp), ptr(w), ptr(inv), ptr(off), T, H,
+                                       E, k, code, ptr(ws), ws.numel(), stream_of(X)))
+    return scores, xp, w, inv, off
+
+
 # --------------------------------------------------------------------------- grouped linear
 def moe_grouped_linear(X: torch.Tensor, expert_offset: torch.Tensor, W: torch.Tensor,
                        B: torch.Tensor | None = None, *, swiglu: bool = False, beta: float = 1.0,

@@ -105,6 +105,36 @@ def test_select_leading_dims_and_noncontiguous_input(F):
     assert np.array_equal(host(xe).reshape(-1, 64), oxe) and np.array_equal(inv.cpu().numpy(), oinv)
 
 
+@pytest.mark.parametrize("T,H,E,k,dtype", [(1, 4096, 8, 2, "f16"), (64, 4096, 8, 2, "f16"), (300, 512, 8, 2, "bf16"),
+                                            (1024, 256, 64, 8, "f16"), (77, 64, 5, 3, "f32"), (500, 128, 16, 16, "bf16")])
+def test_route_select_fused_router(F, T, H, E, k, dtype):
+    """Router gate + select in one launch: the scores it returns match the gate linear, and
+    the routing is bit-exact for exactly those scores."""
+    rng = np.random.default_rng(T + E)
+    x = orc.round_to_dtype(rng.standard_normal((T, H)).astype(np.float32), dtype)
+    wr = orc.round_to_dtype((rng.standard_normal((E, H)) * 0.02).astype(np.float32), dtype)
+    for rep in range(2):
+        out = F.moe_route_select(dev(x, dtype), dev(wr, dtype), E, k)
+        assert out is not None
+        sc, xe, ew, inv, off = out
+        torch.cuda.synchronize()
+        ref_scores = (x.astype(np.float64) @ wr.astype(np.float64).T).astype(np.float32)
+        assert_close(sc, ref_scores, dtype, "router scores")
+        s32 = host(sc)
+        oxe, oew, oinv, ooff = orc.moe_select(x, s32, E, k, dtype)
+        tied = orc.rows_with_ties(s32, k)
+        if not tied.any():
+            assert np.array_equal(off.cpu().numpy(), ooff)
+            assert np.array_equal(inv.cpu().numpy(), oinv)
+            assert np.array_equal(host(xe).reshape(-1, H), oxe)
+            assert_ulp(ew, oew, dtype, msg="expert_weights")
+        # the stand-alone moe_select on the same scores gives the same result in any case
+        xe2, ew2, inv2, off2 = F.moe_select(dev(x, dtype), sc, E, k)
+        assert torch.equal(off, off2) and torch.equal(inv, inv2) and torch.equal(xe, xe2) and torch.equal(ew, ew2)
+    assert F.moe_route_select(torch.zeros(2000, 64, device="cuda", dtype=torch.float16),
+                              torch.zeros(8, 64, device="cuda", dtype=torch.float16), 8, 2) is None
+
+
 def test_select_errors(F):
     x = torch.randn(4, 8, device="cuda", dtype=torch.float16)
     s = torch.randn(4, 8, device="cuda", dtype=torch.float16)
@@ -323,6 +353,29 @@ def test_block_golden(F, name, fused):
     r = orc.moe_block(g["x"], g["w_router"], g["w_gate_up"], g["w_down"], E, k, dtype, scores=g["scores"],
                       round_intermediates=False)
     assert_close(out, r["out"], dtype, "vs oracle")
+
+
+def test_block_with_its_own_router(F):
+    """MoeFeedForward computing the router logits itself (fused router + select for a
+    decode-size batch, cuBLAS linear + moe_select for a large one) against the oracle fed
+    with the scores the block produced."""
+    from ppl.pmx_b200 import workloads as W
+    from ppl.pmx_b200.moe_layers import MoeFeedForward
+    for wl, kw in (("decode_t64", dict(H=512, I=1024)), ("prefill", dict(T=1500, H=256, I=512))):
+        sh = W.scaled(W.WORKLOADS[wl], **kw)
+        x, wr, _, _ = W.make_activations(sh)
+        wu, w2 = W.make_expert_weights(sh, "cuda")
+        blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, None, False).cuda().to(W.TORCH_DTYPE[sh.dtype])
+        with torch.no_grad():
+            blk.gate.weight.copy_(wr)
+            blk.wu.weight.copy_(wu)
+            blk.w2.weight.copy_(w2)
+            out = blk(x.cuda())
+            routed = F.moe_route_select(x.cuda(), blk.gate.weight, sh.E, sh.k)
+            sc = routed[0] if routed is not None else torch.nn.functional.linear(x.cuda(), blk.gate.weight)
+        r = orc.moe_block(host(x), host(wr), host(wu), host(w2), sh.E, sh.k, sh.dtype, scores=host(sc),
+                          round_intermediates=False)
+        assert_close(out, r["out"], sh.dtype, wl)
 
 
 @pytest.mark.parametrize("wl,scale", [("decode_t64", 8), ("prefill", 16), ("finegrained_empty", 4)])
