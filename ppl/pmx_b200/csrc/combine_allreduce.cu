@@ -23,21 +23,22 @@
 //   [4096, ...)    two data buffers used alternately (epoch parity), so a rank
 //                  may start the next call while a slower peer still reads the
 //                  previous one.
-// The grid never exceeds one CTA per SM, so all CTAs are resident and the
-// ticket / flag waits cannot starve each other.  Waits are bounded to 1 s; on
+// The grid never exceeds two 256-thread CTAs per SM, which the kernel's launch
+// bounds guarantee to fit, so all CTAs are resident and the ticket / flag waits
+// cannot starve each other.  Waits are bounded to 1 s; on
 // expiry the CTA records where it gave up in the status words and skips the sum.
 #include "common.cuh"
 
 namespace pmx {
 namespace {
 
-constexpr int kMaxWorld = 16;
+constexpr int kMaxWorld = 8;   // one NVSwitch domain of B200s; also the unroll depth of the peer loads
 constexpr size_t kCtrlBytes = 4096;
 constexpr unsigned long long kWaitNs = 1000000000ull;
 
 struct Ctrl {
-  unsigned int flags[kMaxWorld];  // flags[src] = last epoch published by rank src
-  unsigned int pad0[64 - kMaxWorld];
+  unsigned int flags[8];          // flags[src] = last epoch published by rank src
+  unsigned int pad0[64 - 8];
   unsigned int epoch;             // last completed epoch of this rank
   unsigned int ticket_combine;
   unsigned int ticket_done;
@@ -65,7 +66,7 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 combine_allreduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
                          const int64_t* __restrict__ inv, T* __restrict__ out, int64_t Tn, int k,
                          int64_t N, Peers peers, int rank, int world, size_t data_bytes) {
@@ -134,15 +135,23 @@ combine_allreduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
   // 4. sum over ranks
   if (!s_abort) {
     for (int64_t i = first; i < total; i += stride) {
+      // issue the loads from all ranks before using any of them: NVLink latency
+      // is paid once per item, not once per rank
+      uint4 raw[kMaxWorld];
+#pragma unroll
+      for (int p = 0; p < kMaxWorld; ++p)
+        if (p < world) raw[p] = __ldcg(reinterpret_cast<const uint4*>(peers.base[p] + data_off) + i);
       float acc[V];
 #pragma unroll
       for (int v = 0; v < V; ++v) acc[v] = 0.f;
-      for (int p = 0; p < world; ++p) {
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(peers.base[p] + data_off) + i);
-        float f[V];
-        unpack16<T>(raw, f);
 #pragma unroll
-        for (int v = 0; v < V; ++v) acc[v] += f[v];
+      for (int p = 0; p < kMaxWorld; ++p) {
+        if (p < world) {
+          float f[V];
+          unpack16<T>(raw[p], f);
+#pragma unroll
+          for (int v = 0; v < V; ++v) acc[v] += f[v];
+        }
       }
       reinterpret_cast<uint4*>(out)[i] = pack16<T>(acc);
     }
@@ -189,7 +198,9 @@ int launch_reduce_allreduce(const void* y, const void* w, const int64_t* inv, vo
   const size_t data_bytes = (need - kCtrlBytes) / 2;
   const int64_t items = Tn * (N / vec);
   int64_t blocks = ceil_div(items, 256);
-  if (blocks > sm_count()) blocks = sm_count();  // all CTAs resident: one per SM at most
+  // all CTAs must be resident at once (they meet at the ticket and wait on peers):
+  // the kernel is compiled for two 256-thread CTAs per SM (__launch_bounds__)
+  if (blocks > 2 * (int64_t)sm_count()) blocks = 2 * (int64_t)sm_count();
   switch (dtype) {
     case PMX_DTYPE_F16:
       combine_allreduce_kernel<__half><<<(int)blocks, 256, 0, s>>>((const __half*)y, (const __half*)w, inv, (__half*)out, Tn, k, N, peers, rank, world, data_bytes);

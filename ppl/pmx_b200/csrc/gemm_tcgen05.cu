@@ -194,7 +194,7 @@ __device__ __forceinline__ bool wait_barrier(uint64_t* bar, uint32_t parity, Sha
       if (sh->abort) return false;
       if (global_ns() - t0 > kWaitLimitNs) {
         sh->abort = 1;
-        if (atomicCAS(status, 0, 1) == 0) {
+        if (atomicExch(status, 1) != 1) {
           status[1] = role;
           status[2] = item;
           status[3] = static_cast<int>(blockIdx.x);
@@ -255,6 +255,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // ---- set-up ---------------------------------------------------------------
+  // CTA 0 clears the status words (a failed wait is recorded no earlier than
+  // its 2 s limit, long after this store)
+  if (blockIdx.x == 0 && threadIdx.x < 4) p.status[threadIdx.x] = 0;
   for (int e = threadIdx.x; e <= p.E; e += blockDim.x) {
     long long o = p.off[e];
     s_off[e] = (int)(o < 0 ? 0 : (o > p.M ? p.M : o));
@@ -637,7 +640,6 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   p.stages = plan.stages;
   p.beta = beta;
 
-  PMX_CUDA_OK(cudaMemsetAsync(ws, 0, 16, s));
   const size_t smem = smem_bytes_for(plan, swiglu, E);
   const int grid = plan.max_ctas;
   const bool bf = dtype == PMX_DTYPE_BF16;
