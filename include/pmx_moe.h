@@ -68,6 +68,8 @@ typedef struct pmx_gemm_plan {
   int32_t split_k;      /* number of K slices accumulated through the fp32 workspace */
   int32_t stages;       /* shared-memory pipeline depth */
   int32_t max_ctas;     /* cap on the persistent grid (0 = number of SMs) */
+  int32_t stream_k;     /* 0 = choose, 1 = deal k-blocks evenly over the CTAs (partial tiles
+                           are exchanged through the workspace), 2 = whole tiles per CTA */
 } pmx_gemm_plan;
 
 int pmx_moe_abi_version(void);

@@ -22,7 +22,7 @@ GEMM_AUTO, GEMM_TC_TOKENS_M, GEMM_TC_WEIGHTS_M, GEMM_SIMT = 0, 1, 2, 3
 class GemmPlan(C.Structure):
     """Mirror of pmx_gemm_plan."""
     _fields_ = [("kernel", C.c_int32), ("tile_feat", C.c_int32), ("tile_tok", C.c_int32),
-                ("split_k", C.c_int32), ("stages", C.c_int32), ("max_ctas", C.c_int32)]
+                ("split_k", C.c_int32), ("stages", C.c_int32), ("max_ctas", C.c_int32), ("stream_k", C.c_int32)]
 
 
 class PmxError(RuntimeError):

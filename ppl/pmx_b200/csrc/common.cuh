@@ -114,6 +114,7 @@ struct TcPlan {
   int split_k;
   int stages;
   int max_ctas;
+  int stream_k;
 };
 // Fills `plan` for the tensor-core kernel or returns false when the shape is
 // outside what it covers (the caller then uses the CUDA-core kernel).

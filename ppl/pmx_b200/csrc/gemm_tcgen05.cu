@@ -44,6 +44,7 @@ constexpr int kTmemCols = 512;   // whole tensor memory: 2 accumulator buffers x
 constexpr int kAccStride = 256;
 constexpr int kMaxExperts = 1024;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr size_t kStreamKFlagBytes = 1024;                  // room for the per-CTA flags (<= 256 CTAs)
 
 struct Params {
   const int64_t* off;   // [E+1]
@@ -57,6 +58,9 @@ struct Params {
   int split_k, kb_per_split, kblocks;
   int stages;
   float beta;
+  int stream_k;         // 1: the k-blocks of all work items are dealt out evenly over the CTAs
+  int* sk_flags;        // [grid] number of epilogue warps that have stored CTA c's partial tile
+  float* sk_slots;      // [grid][256 columns][128 lanes] fp32 partial accumulators
 };
 
 // ----------------------------------------------------------------------------- PTX wrappers
@@ -154,6 +158,27 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+      "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+      "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+      "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+      "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+      "r"(__float_as_uint(v[15]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu_s32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes,
 // stored with the 128-byte swizzle (8-row groups 1024 bytes apart).
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
@@ -228,6 +253,43 @@ __device__ __forceinline__ void decode_item(int item, int& e, const int* s_off, 
   it.kb1 = min(p.kblocks, it.kb0 + p.kb_per_split);
 }
 
+// Walks the work of one CTA.  Plain mode: items blockIdx.x, +gridDim.x, ... with
+// their (split-K) k range.  Stream-K mode: the CTA owns the contiguous range
+// [c*U/G, (c+1)*U/G) of the U = items * kblocks k-block units and meets it as a
+// sequence of segments (item, k range); a segment that does not start at k = 0
+// is a partial tile that goes to the CTA's slot, a segment that starts at 0 but
+// stops early is finished by its owner from the slots of the following CTAs.
+struct WorkIter {
+  int e;
+  int next_item;
+  long long u, u_end, units;
+  __device__ __forceinline__ void init(const Params& p, int total_items) {
+    e = 0;
+    next_item = blockIdx.x;
+    units = (long long)total_items * p.kblocks;
+    u = (long long)blockIdx.x * units / gridDim.x;
+    u_end = (long long)(blockIdx.x + 1) * units / gridDim.x;
+  }
+  __device__ __forceinline__ bool next(const Params& p, int total_items, const int* s_off,
+                                       const int* s_prefix, Item& it, int& item) {
+    if (p.stream_k) {
+      if (u >= u_end) return false;
+      item = (int)(u / p.kblocks);
+      decode_item(item, e, s_off, s_prefix, p, it);
+      const long long base = (long long)item * p.kblocks;
+      it.kb0 = (int)(u - base);
+      it.kb1 = (int)((u_end < base + p.kblocks ? u_end : base + p.kblocks) - base);
+      u = base + it.kb1;
+      return true;
+    }
+    if (next_item >= total_items) return false;
+    item = next_item;
+    decode_item(item, e, s_off, s_prefix, p, it);
+    next_item += gridDim.x;
+    return true;
+  }
+};
+
 template <typename T>
 __device__ __forceinline__ void store16(T* dst, const float (&v)[16]) {
   // 16 consecutive outputs: two 16-byte stores
@@ -301,11 +363,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      int e = 0;
       Item it;
+      int item = 0;
+      WorkIter work;
+      work.init(p, total_items);
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        decode_item(item, e, s_off, s_prefix, p, it);
+      while (ok && work.next(p, total_items, s_off, s_prefix, it, item)) {
         const int wrow = it.e * p.N + it.f0;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           ok = wait_barrier(&sh->empty[stage], phase ^ 1u, sh, p.status, 0, item);
@@ -332,11 +395,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       const uint32_t idesc = make_idesc<T>(128, MODE == 0 ? wrows : tt);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      int e = 0;
       Item it;
+      int item = 0;
+      WorkIter work;
+      work.init(p, total_items);
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        decode_item(item, e, s_off, s_prefix, p, it);
+      while (ok && work.next(p, total_items, s_off, s_prefix, it, item)) {
         ok = wait_barrier(&sh->acc_empty[acc], acc_phase ^ 1u, sh, p.status, 1, item);
         if (!ok) break;
         tc_fence_after();
@@ -373,20 +437,77 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
-    int e = 0;
     Item it;
+    int item = 0;
+    WorkIter work;
+    work.init(p, total_items);
     bool ok = true;
     const bool partial = p.split_k > 1;
     T* y = reinterpret_cast<T*>(p.y);
     float* yp = reinterpret_cast<float*>(p.y);
     const T* bias = reinterpret_cast<const T*>(p.bias);
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
-      decode_item(item, e, s_off, s_prefix, p, it);
+    const int acc_cols = MODE == 0 ? wrows : (SWIGLU ? 2 * tt : tt);   // accumulator columns in use
+    while (work.next(p, total_items, s_off, s_prefix, it, item)) {
       ok = wait_barrier(&sh->acc_full[acc], acc_phase, sh, p.status, 3, item);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * kAccStride + (static_cast<uint32_t>(q * 32) << 16);
+      if (p.stream_k && it.kb0 > 0) {
+        // partial tile: raw accumulators -> this CTA's slot, then one count per warp
+        float* slot = p.sk_slots + (size_t)blockIdx.x * (256 * 128) + q * 32 + lane;
+        for (int c = 0; c < acc_cols; c += 16) {
+          float g[16];
+          __syncwarp();
+          tmem_ld16(taddr + c, g);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) slot[(size_t)(c + i) * 128] = g[i];
+        }
+        __threadfence();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          atomicAdd(p.sk_flags + blockIdx.x, 1);
+          mbar_arrive(&sh->acc_empty[acc]);
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        continue;
+      }
+      if (p.stream_k && it.kb1 < p.kblocks) {
+        // owner of a tile whose remaining k-blocks went to the following CTAs:
+        // add their partial tiles to the accumulator in tensor memory
+        const long long item_end = ((long long)item + 1) * p.kblocks;
+        for (int c2 = blockIdx.x + 1; c2 < (int)gridDim.x && (long long)c2 * work.units / gridDim.x < item_end; ++c2) {
+          if (lane == 0) {
+            const unsigned long long t_start = global_ns();
+            unsigned int spins = 0;
+            while (ld_acquire_gpu_s32(p.sk_flags + c2) < 4) {
+              if ((++spins & 255u) == 0u) {
+                if (sh->abort) break;
+                if (global_ns() - t_start > kWaitLimitNs) {
+                  sh->abort = 1;
+                  if (atomicExch(p.status, 1) != 1) { p.status[1] = 4; p.status[2] = item; p.status[3] = c2; }
+                  break;
+                }
+              }
+            }
+          }
+          __syncwarp();
+          const float* slot = p.sk_slots + (size_t)c2 * (256 * 128) + q * 32 + lane;
+          for (int c = 0; c < acc_cols; c += 16) {
+            float g[16];
+            __syncwarp();
+            tmem_ld16(taddr + c, g);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) g[i] += __ldcg(slot + (size_t)(c + i) * 128);
+            tmem_st16(taddr + c, g);
+          }
+          tmem_wait_st();
+        }
+        __syncwarp();
+      }
       if (MODE == 0) {
         const int row = it.row0 + q * 32 + lane;
         const bool row_ok = row < it.row_end;
@@ -594,6 +715,14 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   if (st < 2) return false;
   pl.stages = st;
   pl.max_ctas = user && user->max_ctas ? user->max_ctas : sms;
+  // Stream-K: deal the k-blocks of all items out evenly over the CTAs.  A single
+  // SM cannot pull much more than its 1/148 share of the HBM bandwidth (bytes in
+  // flight are bounded by its shared memory), so a grid whose last round is
+  // ragged loses that round's idle SMs.  On by default for the weight-streaming
+  // (decode) assignment, where items per SM are few.
+  const int want_sk = user ? user->stream_k : 0;
+  pl.stream_k = pl.split_k == 1 && (want_sk == 1 || (want_sk == 0 && pl.kernel == PMX_GEMM_TC_WEIGHTS_M)) ? 1 : 0;
+  if (want_sk == 1 && !pl.stream_k) return false;
   *plan = pl;
   return true;
 }
@@ -602,6 +731,8 @@ size_t gemm_tc_workspace_bytes(int64_t M, int64_t N, int epilogue, const TcPlan&
   size_t b = kStatusBytes;
   // split-K partial sums cover all N accumulator columns (SwiGLU is then applied in the final sum)
   if (plan.split_k > 1) b += (size_t)plan.split_k * M * N * sizeof(float);
+  // stream-K: one flag and one 256-column x 128-lane fp32 partial tile per CTA
+  if (plan.stream_k) b += kStreamKFlagBytes + (size_t)plan.max_ctas * 256 * 128 * sizeof(float);
   (void)epilogue;
   return b;
 }
@@ -639,6 +770,14 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   p.kb_per_split = (int)ceil_div(p.kblocks, plan.split_k);
   p.stages = plan.stages;
   p.beta = beta;
+  p.stream_k = plan.stream_k;
+  if (plan.stream_k) {
+    if (plan.max_ctas > 256) return fail(PMX_ERR_UNSUPPORTED, "grouped_linear: stream-K supports at most 256 CTAs");
+    char* base = reinterpret_cast<char*>(ws) + kStatusBytes;
+    p.sk_flags = reinterpret_cast<int*>(base);
+    p.sk_slots = reinterpret_cast<float*>(base + kStreamKFlagBytes);
+    PMX_CUDA_OK(cudaMemsetAsync(p.sk_flags, 0, kStreamKFlagBytes, s));
+  }
 
   const size_t smem = smem_bytes_for(plan, swiglu, E);
   const int grid = plan.max_ctas;

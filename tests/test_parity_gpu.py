@@ -265,6 +265,20 @@ def test_grouped_linear_tilings(F, tile):
     run_linear(F, rng, 333, 320, 256, 5, "bf16", plan=tile, bias=True)
 
 
+@pytest.mark.parametrize("plan", [dict(kernel=2, stream_k=1), dict(kernel=2, stream_k=2), dict(kernel=1, stream_k=1),
+                                  dict(kernel=2, stream_k=1, max_ctas=7), dict(kernel=2, stream_k=1, max_ctas=97),
+                                  dict(kernel=1, stream_k=1, max_ctas=5, tile_feat=64),
+                                  dict(kernel=2, stream_k=1, tile_tok=16, stages=2)])
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_grouped_linear_stream_k(F, plan, swiglu):
+    """k-blocks dealt out evenly over the CTAs: tiles cut at arbitrary k are finished by
+    their owner from the partial tiles the following CTAs leave in the workspace."""
+    rng = np.random.default_rng(len(str(plan)))
+    for M, N, K, E in ((40, 512, 1024, 8), (3, 256, 4096, 8), (300, 384, 192, 4), (64, 1024, 64, 8)):
+        run_linear(F, rng, M, N, K, E, "f16", plan=plan, bias=True, swiglu=swiglu)
+    run_linear(F, rng, 130, 256, 2048, 6, "bf16", plan=plan, swiglu=swiglu)
+
+
 def test_grouped_linear_auto_plan_and_fp32(F):
     rng = np.random.default_rng(12)
     run_linear(F, rng, 700, 256, 128, 4, "f16")          # auto -> tokens on M
