@@ -114,6 +114,7 @@ struct TcPlan {
   int split_k;
   int stages;
   int max_ctas;
+  int cta_cap;
   int stream_k;
 };
 // Fills `plan` for the tensor-core kernel or returns false when the shape is

@@ -30,6 +30,8 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -58,6 +60,7 @@ struct Params {
   int split_k, kb_per_split, kblocks;
   int stages;
   float beta;
+  int cta_cap;          // at most this many CTAs take work (the rest of the grid idles)
   int stream_k;         // 1: the k-blocks of all work items are dealt out evenly over the CTAs
   int* sk_flags;        // [grid] number of epilogue warps that have stored CTA c's partial tile
   float* sk_slots;      // [grid][256 columns][128 lanes] fp32 partial accumulators
@@ -262,13 +265,27 @@ __device__ __forceinline__ void decode_item(int item, int& e, const int* s_off, 
 struct WorkIter {
   int e;
   int next_item;
+  int grid;             // CTAs that take work: blockIdx.x >= grid idles
   long long u, u_end, units;
   __device__ __forceinline__ void init(const Params& p, int total_items) {
     e = 0;
-    next_item = blockIdx.x;
+    const int cap = min((int)gridDim.x, p.cta_cap);
+    grid = cap;
+    if (!p.stream_k && total_items > 0) {
+      // whole tiles per CTA: use the smallest grid that needs no more rounds than
+      // `cap` CTAs would, so that every round is full (896 items -> 7 rounds of
+      // 128 CTAs instead of 6 rounds of 148 plus a ragged one)
+      const int rounds = (total_items + cap - 1) / cap;
+      grid = (total_items + rounds - 1) / rounds;
+    }
+    next_item = (int)blockIdx.x < grid ? (int)blockIdx.x : total_items;
     units = (long long)total_items * p.kblocks;
-    u = (long long)blockIdx.x * units / gridDim.x;
-    u_end = (long long)(blockIdx.x + 1) * units / gridDim.x;
+    if ((int)blockIdx.x < grid) {
+      u = (long long)blockIdx.x * units / grid;
+      u_end = (long long)(blockIdx.x + 1) * units / grid;
+    } else {
+      u = u_end = 0;
+    }
   }
   __device__ __forceinline__ bool next(const Params& p, int total_items, const int* s_off,
                                        const int* s_prefix, Item& it, int& item) {
@@ -285,7 +302,7 @@ struct WorkIter {
     if (next_item >= total_items) return false;
     item = next_item;
     decode_item(item, e, s_off, s_prefix, p, it);
-    next_item += gridDim.x;
+    next_item += grid;
     return true;
   }
 };
@@ -478,7 +495,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         // owner of a tile whose remaining k-blocks went to the following CTAs:
         // add their partial tiles to the accumulator in tensor memory
         const long long item_end = ((long long)item + 1) * p.kblocks;
-        for (int c2 = blockIdx.x + 1; c2 < (int)gridDim.x && (long long)c2 * work.units / gridDim.x < item_end; ++c2) {
+        for (int c2 = blockIdx.x + 1; c2 < work.grid && (long long)c2 * work.units / work.grid < item_end; ++c2) {
+          // a CTA whose share of the units is empty has nothing to contribute
+          if ((long long)(c2 + 1) * work.units / work.grid == (long long)c2 * work.units / work.grid) continue;
           if (lane == 0) {
             const unsigned long long t_start = global_ns();
             unsigned int spins = 0;
@@ -677,6 +696,8 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   const int64_t feat_tiles = ceil_div(n_out, pl.tile_feat);
   if (user && user->split_k) {
     pl.split_k = user->split_k;
+  } else if (user && user->stream_k == 1) {
+    pl.split_k = 1;   // stream-K slices K itself
   } else {
     pl.split_k = 1;
     // experts with at least one row (estimate) x token tiles each
@@ -715,13 +736,16 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   if (st < 2) return false;
   pl.stages = st;
   pl.max_ctas = user && user->max_ctas ? user->max_ctas : sms;
-  // Stream-K: deal the k-blocks of all items out evenly over the CTAs.  A single
-  // SM cannot pull much more than its 1/148 share of the HBM bandwidth (bytes in
-  // flight are bounded by its shared memory), so a grid whose last round is
-  // ragged loses that round's idle SMs.  On by default for the weight-streaming
-  // (decode) assignment, where items per SM are few.
+  // Weight streaming is HBM-bound and measurably faster on B200 with 128 CTAs than
+  // with all 148 SMs (6.5-6.7 TB/s against 6.3); the tensor-bound assignment uses every SM.
+  pl.cta_cap = pl.max_ctas;
+  if (!(user && user->max_ctas) && pl.kernel == PMX_GEMM_TC_WEIGHTS_M && pl.cta_cap > 128) pl.cta_cap = 128;
+  // Stream-K (k-blocks of all items dealt out evenly over the CTAs) is available on
+  // request.  Measured on B200 it does not beat whole tiles on a grid sized to
+  // full rounds (see WorkIter::init): 283 vs 290 us for the Mixtral gate/up
+  // projection at 64 tokens, but 55 vs 46 us on a 1/8 tensor-parallel shard.
   const int want_sk = user ? user->stream_k : 0;
-  pl.stream_k = pl.split_k == 1 && (want_sk == 1 || (want_sk == 0 && pl.kernel == PMX_GEMM_TC_WEIGHTS_M)) ? 1 : 0;
+  pl.stream_k = pl.split_k == 1 && want_sk == 1 ? 1 : 0;
   if (want_sk == 1 && !pl.stream_k) return false;
   *plan = pl;
   return true;
@@ -755,6 +779,11 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   st = make_map(&mw, w, (uint64_t)E * N, (uint64_t)K, (uint32_t)plan.tile_feat, dtype);
   if (st != PMX_OK) return st;
 
+  if (getenv("PMX_MOE_DEBUG"))
+    fprintf(stderr, "[pmx_moe] grouped_linear M=%lld N=%lld K=%lld E=%d swiglu=%d: %s tile_feat=%d tile_tok=%d split_k=%d stages=%d grid=%d cta_cap=%d stream_k=%d\n",
+            (long long)M, (long long)N, (long long)K, E, (int)swiglu_any,
+            plan.kernel == PMX_GEMM_TC_TOKENS_M ? "tokens-on-M" : "weights-on-M", plan.tile_feat, plan.tile_tok,
+            plan.split_k, plan.stages, plan.max_ctas, plan.cta_cap, plan.stream_k);
   Params p{};
   p.off = off;
   p.bias = plan.split_k > 1 ? nullptr : bias;  // with split-K the bias joins in the final sum
@@ -771,6 +800,7 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   p.stages = plan.stages;
   p.beta = beta;
   p.stream_k = plan.stream_k;
+  p.cta_cap = plan.cta_cap;
   if (plan.stream_k) {
     if (plan.max_ctas > 256) return fail(PMX_ERR_UNSUPPORTED, "grouped_linear: stream-K supports at most 256 CTAs");
     char* base = reinterpret_cast<char*>(ws) + kStatusBytes;
