@@ -44,6 +44,8 @@ struct Ctrl {
   unsigned int ticket_done;
   unsigned int pad1[61];
   int status[4];                  // code, peer, epoch, CTA
+  unsigned int pad2[60];
+  unsigned long long stamp[8];    // %globaltimer at the phase boundaries of CTA 0 (last call)
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
 
@@ -79,6 +81,8 @@ combine_allreduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
     s_abort = 0;
   }
   __syncthreads();
+  const bool stamper = blockIdx.x == 0 && threadIdx.x == 0;
+  if (stamper) ctrl->stamp[0] = now_ns();
   const unsigned int epoch = s_epoch;
   const size_t data_off = kCtrlBytes + (epoch & 1u) * data_bytes;
   const int64_t chunks = N / V, total = Tn * chunks;
@@ -103,6 +107,7 @@ combine_allreduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
     *reinterpret_cast<uint4*>(mine + t * N + c * V) = pack16<T>(acc);
   }
   __syncthreads();
+  if (stamper) ctrl->stamp[1] = now_ns();
   // 2. last CTA publishes the epoch to every peer
   if (threadIdx.x == 0) {
     __threadfence();
@@ -112,8 +117,10 @@ combine_allreduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
       __threadfence_system();
       for (int p = 0; p < world; ++p)
         if (p != rank) st_release_sys(&reinterpret_cast<Ctrl*>(peers.base[p])->flags[rank], epoch);
+      ctrl->stamp[5] = now_ns();
     }
   }
+  if (stamper) ctrl->stamp[2] = now_ns();
   // 3. wait for every peer's epoch (thread p watches peer p)
   if (threadIdx.x < world && threadIdx.x != rank) {
     const unsigned int* flag = &ctrl->flags[threadIdx.x];
@@ -132,6 +139,7 @@ combine_allreduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
     }
   }
   __syncthreads();
+  if (stamper) ctrl->stamp[3] = now_ns();
   // 4. sum over ranks
   if (!s_abort) {
     for (int64_t i = first; i < total; i += stride) {
@@ -157,6 +165,7 @@ combine_allreduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
     }
   }
   __syncthreads();
+  if (stamper) ctrl->stamp[4] = now_ns();
   if (threadIdx.x == 0) {
     const unsigned int done = atomicAdd(&ctrl->ticket_done, 1u);
     if (done == gridDim.x - 1) {

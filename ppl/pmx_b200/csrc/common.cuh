@@ -115,6 +115,7 @@ struct TcPlan {
   int stages;
   int max_ctas;
   int cta_cap;
+  int full_rounds;
   int stream_k;
 };
 // Fills `plan` for the tensor-core kernel or returns false when the shape is

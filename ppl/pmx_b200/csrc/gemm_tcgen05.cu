@@ -61,6 +61,7 @@ struct Params {
   int stages;
   float beta;
   int cta_cap;          // at most this many CTAs take work (the rest of the grid idles)
+  int full_rounds;      // shrink the active grid so that every round of tiles is full
   int stream_k;         // 1: the k-blocks of all work items are dealt out evenly over the CTAs
   int* sk_flags;        // [grid] number of epilogue warps that have stored CTA c's partial tile
   float* sk_slots;      // [grid][256 columns][128 lanes] fp32 partial accumulators
@@ -271,7 +272,7 @@ struct WorkIter {
     e = 0;
     const int cap = min((int)gridDim.x, p.cta_cap);
     grid = cap;
-    if (!p.stream_k && total_items > 0) {
+    if (!p.stream_k && p.full_rounds && total_items > 0) {
       // whole tiles per CTA: use the smallest grid that needs no more rounds than
       // `cap` CTAs would, so that every round is full (896 items -> 7 rounds of
       // 128 CTAs instead of 6 rounds of 148 plus a ragged one)
@@ -740,6 +741,14 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   // with all 148 SMs (6.5-6.7 TB/s against 6.3); the tensor-bound assignment uses every SM.
   pl.cta_cap = pl.max_ctas;
   if (!(user && user->max_ctas) && pl.kernel == PMX_GEMM_TC_WEIGHTS_M && pl.cta_cap > 128) pl.cta_cap = 128;
+  // experiment knobs (grid sweeps): PMX_MOE_GEMM_CTAS=<n> caps the CTAs that take work,
+  // PMX_MOE_GEMM_FULL_ROUNDS=0 makes every capped CTA stride over the tiles as launched
+  if (const char* env = getenv("PMX_MOE_GEMM_CTAS")) {
+    const int n = atoi(env);
+    if (n > 0 && n <= pl.max_ctas) pl.cta_cap = n;
+  }
+  pl.full_rounds = 1;
+  if (const char* env = getenv("PMX_MOE_GEMM_FULL_ROUNDS")) pl.full_rounds = atoi(env) != 0;
   // Stream-K (k-blocks of all items dealt out evenly over the CTAs) is available on
   // request.  Measured on B200 it does not beat whole tiles on a grid sized to
   // full rounds (see WorkIter::init): 283 vs 290 us for the Mixtral gate/up
@@ -801,6 +810,7 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   p.beta = beta;
   p.stream_k = plan.stream_k;
   p.cta_cap = plan.cta_cap;
+  p.full_rounds = plan.full_rounds;
   if (plan.stream_k) {
     if (plan.max_ctas > 256) return fail(PMX_ERR_UNSUPPORTED, "grouped_linear: stream-K supports at most 256 CTAs");
     char* base = reinterpret_cast<char*>(ws) + kStatusBytes;
