@@ -233,6 +233,22 @@ def main():
         with torch.no_grad():
             return blk(x_dev)
 
+    if use_peer:
+        # the peer-memory exchange needs the ranks' buffers mapped into each other
+        # (symmetric memory); if this machine refuses, say so and use NCCL
+        try:
+            step()
+            torch.cuda.synchronize()
+            ok = torch.ones(1, device=device)
+        except Exception as exc:                      # noqa: BLE001
+            print(f"[bench] rank {rank}: peer-memory all-reduce unavailable ({exc}); using NCCL", file=sys.stderr)
+            ok = torch.zeros(1, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if ok.item() == 0:
+            use_peer = False
+            blk.peer_reduce_tokens = 0
+            blk._peer = None
+
     def sync_all():
         if world > 1:
             dist.barrier(group=group)

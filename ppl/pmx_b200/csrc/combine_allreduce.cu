@@ -6,46 +6,50 @@
 // MoeRowParallelLinear.py:57-58; the weighted combine is linear, so it can run
 // before the sum over ranks, which then moves [T,N] instead of [T*k,N]).
 //
-// One kernel per rank does both:
-//   1. combine the local rows into this rank's exchange buffer (T1, fp32 math);
-//   2. the last CTA to finish publishes the epoch number in every peer's flag
-//      word (release, system scope);
-//   3. every CTA waits (bounded) until all peers have published this epoch;
-//   4. each CTA sums its share of the rows over all ranks' buffers, reading the
-//      peers' buffers with plain 16-byte loads over NVLink, and writes `out`.
-// One-shot exchange: each rank pulls (world-1) * T*N*b bytes, which is the
-// right trade below a few MB (decode); larger messages stay with NCCL.
+// One kernel per rank does both, CTA by CTA.  All ranks launch the same grid and
+// walk the rows in the same grid-stride order, so CTA b of every rank owns the
+// same slice of the result:
+//   1. CTA b combines its slice of the local rows into this rank's exchange
+//      buffer (T1, fp32 math);
+//   2. it publishes the epoch number in flag [rank][b] of every peer (release,
+//      system scope);
+//   3. it waits (bounded) until flag [p][b] of its own control block shows this
+//      epoch for every peer p, i.e. until CTA b of every peer has done step 1;
+//   4. it sums its slice over all ranks' buffers, reading the peers' buffers
+//      with plain 16-byte loads over NVLink, and writes `out`.
+// No CTA waits for another CTA of its own GPU, so nothing depends on how many
+// CTAs are resident.  One-shot exchange: each rank pulls (world-1) * T*N*b
+// bytes, which is the right trade below a few MB (decode); larger messages stay
+// with NCCL.
 //
 // Exchange buffer of a rank (the same layout on every rank, allocated
 // symmetrically by the host side):
-//   [0, 4096)      control: flags[src] written by peers, epoch counter, tickets,
-//                  status words
-//   [4096, ...)    two data buffers used alternately (epoch parity), so a rank
+//   [0, 16384)     control: flags[src rank][CTA] written by peers, epoch counter,
+//                  exit ticket, status words, phase timestamps
+//   [16384, ...)   two data buffers used alternately (epoch parity), so a rank
 //                  may start the next call while a slower peer still reads the
 //                  previous one.
-// The grid never exceeds two 256-thread CTAs per SM, which the kernel's launch
-// bounds guarantee to fit, so all CTAs are resident and the ticket / flag waits
-// cannot starve each other.  Waits are bounded to 1 s; on
-// expiry the CTA records where it gave up in the status words and skips the sum.
+// Waits are bounded to 1 s; on expiry the CTA records where it gave up in the
+// status words and skips its sum.
 #include "common.cuh"
 
 namespace pmx {
 namespace {
 
 constexpr int kMaxWorld = 8;   // one NVSwitch domain of B200s; also the unroll depth of the peer loads
-constexpr size_t kCtrlBytes = 4096;
+constexpr int kMaxCtas = 320;  // grid limit: 2 CTAs on each of up to 160 SMs
+constexpr size_t kCtrlBytes = 16384;
 constexpr unsigned long long kWaitNs = 1000000000ull;
 
 struct Ctrl {
-  unsigned int flags[8];          // flags[src] = last epoch published by rank src
-  unsigned int pad0[64 - 8];
   unsigned int epoch;             // last completed epoch of this rank
-  unsigned int ticket_combine;
   unsigned int ticket_done;
-  unsigned int pad1[61];
+  unsigned int pad0[62];
   int status[4];                  // code, peer, epoch, CTA
-  unsigned int pad2[60];
+  unsigned int pad1[60];
   unsigned long long stamp[8];    // %globaltimer at the phase boundaries of CTA 0 (last call)
+  unsigned int pad2[48];
+  unsigned int flags[kMaxWorld][kMaxCtas];  // flags[src][b] = last epoch CTA b of rank src published
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
 
@@ -106,24 +110,18 @@ combine_allreduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
     }
     *reinterpret_cast<uint4*>(mine + t * N + c * V) = pack16<T>(acc);
   }
-  __syncthreads();
+  __syncthreads();   // the block's stores to the exchange buffer are done (CTA scope)
   if (stamper) ctrl->stamp[1] = now_ns();
-  // 2. last CTA publishes the epoch to every peer
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const unsigned int done = atomicAdd(&ctrl->ticket_combine, 1u);
-    if (done == gridDim.x - 1) {
-      ctrl->ticket_combine = 0;
-      __threadfence_system();
-      for (int p = 0; p < world; ++p)
-        if (p != rank) st_release_sys(&reinterpret_cast<Ctrl*>(peers.base[p])->flags[rank], epoch);
-      ctrl->stamp[5] = now_ns();
-    }
+  // 2. publish: my slice of this rank's buffer is complete (thread p tells peer p)
+  // (the release store orders the whole block's buffer stores before the flag: they
+  // happen-before this thread through the barrier above)
+  if (threadIdx.x < world && threadIdx.x != rank) {
+    st_release_sys(&reinterpret_cast<Ctrl*>(peers.base[threadIdx.x])->flags[rank][blockIdx.x], epoch);
   }
   if (stamper) ctrl->stamp[2] = now_ns();
-  // 3. wait for every peer's epoch (thread p watches peer p)
+  // 3. wait until the same CTA of every peer has published this epoch
   if (threadIdx.x < world && threadIdx.x != rank) {
-    const unsigned int* flag = &ctrl->flags[threadIdx.x];
+    const unsigned int* flag = &ctrl->flags[threadIdx.x][blockIdx.x];
     const unsigned long long t0 = now_ns();
     unsigned int it = 0;
     while ((int)(ld_acquire_sys(flag) - epoch) < 0) {
@@ -207,9 +205,10 @@ int launch_reduce_allreduce(const void* y, const void* w, const int64_t* inv, vo
   const size_t data_bytes = (need - kCtrlBytes) / 2;
   const int64_t items = Tn * (N / vec);
   int64_t blocks = ceil_div(items, 256);
-  // all CTAs must be resident at once (they meet at the ticket and wait on peers):
-  // the kernel is compiled for two 256-thread CTAs per SM (__launch_bounds__)
+  // the same grid on every rank (it depends only on T, N and the SM count): CTA b of
+  // each rank owns the same rows
   if (blocks > 2 * (int64_t)sm_count()) blocks = 2 * (int64_t)sm_count();
+  if (blocks > kMaxCtas) blocks = kMaxCtas;
   switch (dtype) {
     case PMX_DTYPE_F16:
       combine_allreduce_kernel<__half><<<(int)blocks, 256, 0, s>>>((const __half*)y, (const __half*)w, inv, (__half*)out, Tn, k, N, peers, rank, world, data_bytes);

@@ -31,16 +31,33 @@ __global__ void reduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
     float acc[V];
 #pragma unroll
     for (int v = 0; v < V; ++v) acc[v] = 0.f;
-    for (int j = 0; j < k; ++j) {
-      const int64_t r = inv[t * k + j];
-      const float wj = Elem<T>::to_f(w[t * k + j]);
-      if (VEC) {
-        float f[kVec<T>];
-        unpack16<T>(ld_nc16(y + r * N + c * V), f);
+    if (VEC) {
+      // rows of up to 4 slots are requested together so that their HBM latencies overlap
+      for (int j0 = 0; j0 < k; j0 += 4) {
+        uint4 raw[4];
+        float wj[4];
 #pragma unroll
-        for (int v = 0; v < V; ++v) acc[v] = fmaf(wj, f[v], acc[v]);
-      } else {
-        acc[0] = fmaf(wj, Elem<T>::to_f(y[r * N + c]), acc[0]);
+        for (int j = 0; j < 4; ++j) {
+          if (j0 + j < k) {
+            const int64_t r = inv[t * k + j0 + j];
+            wj[j] = Elem<T>::to_f(w[t * k + j0 + j]);
+            raw[j] = ld_nc16(y + r * N + c * V);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j0 + j < k) {
+            float f[kVec<T>];
+            unpack16<T>(raw[j], f);
+#pragma unroll
+            for (int v = 0; v < V; ++v) acc[v] = fmaf(wj[j], f[v], acc[v]);
+          }
+        }
+      }
+    } else {
+      for (int j = 0; j < k; ++j) {
+        const int64_t r = inv[t * k + j];
+        acc[0] = fmaf(Elem<T>::to_f(w[t * k + j]), Elem<T>::to_f(y[r * N + c]), acc[0]);
       }
     }
     if (VEC) {
