@@ -15,9 +15,13 @@
 //
 // Work items are (expert, token tile, feature tile, K slice).  The list is
 // derived on the device from expert_offset, so there is no host
-// synchronisation and the grid does not depend on the routing.  Items are
+// synchronisation and the launch does not depend on the routing.  Items are
 // ordered expert-major with the token tile fastest, so the CTAs running at
 // one time share weight tiles through L2 and each weight byte leaves HBM once.
+// The CTAs that take items are the smallest set that needs no more rounds of
+// items than the cap allows (WorkIter::init), so every round is full; with
+// stream_k the k-blocks of all items are dealt out evenly instead and tiles cut
+// at a CTA boundary are completed through partial tiles in the workspace.
 //
 // Two operand assignments (template MODE):
 //   0  tokens on MMA-M (128 rows), weight rows on MMA-N (up to 256): prefill.

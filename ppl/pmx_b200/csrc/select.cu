@@ -1,21 +1,27 @@
 // moe_select on the GPU: router top-k + softmax, per-expert histogram, prefix
 // offsets, stable permutation and the 128-bit vectorised token gather.
 //
-// Replaces MoeSelect.forward (torch_function/MoeSelect.py:36-64).  Three
-// launches, no host synchronisation, no order-dependent atomics: the
-// permutation is a pure function of the scores, so every tensor-parallel rank
-// computes the same routing bit for bit.
+// Replaces MoeSelect.forward (torch_function/MoeSelect.py:36-64).  No host
+// synchronisation and no order-dependent atomics anywhere: the permutation is a
+// pure function of the scores, so every tensor-parallel rank computes the same
+// routing bit for bit.  Three code paths share the ranking rule (higher score
+// first, lower expert index among equals):
 //
-//   route_count : one warp per token picks the k best experts (higher score
-//                 first, lower index among equals), writes the softmax of the k
-//                 kept logits and the expert ids; each block of `tpb` tokens
-//                 leaves its per-expert row count.
-//   scan        : exclusive prefix of the counts over blocks (per expert) and
-//                 over experts -> expert_offset.
+// Large batches, three launches:
+//   route_count : one warp per token picks the k best experts, writes the
+//                 softmax of the k kept logits and the expert ids; each block of
+//                 `tpb` tokens leaves its per-expert row count.
+//   scan        : exclusive prefix of the counts over blocks (one block of
+//                 threads per expert) and over experts -> expert_offset.
 //   place_gather: every block re-walks its slots in order, ranks them inside
 //                 their expert with warp match/popc, writes
 //                 invert_permutation and copies each token row once from X to
 //                 its k destinations.
+// Decode-size batches (<= 1024 tokens, <= 64 experts), one launch:
+//   select_small: every block repeats the routing of all tokens and derives the
+//                 positions of its own slots from warp ballots.
+//   route_select: the same with the router logits (x . W_gate^T) computed in the
+//                 kernel and one bounded grid-wide barrier (cooperative launch).
 #include <mutex>
 
 #include "common.cuh"
