@@ -190,10 +190,22 @@ __global__ void place_gather_kernel(const T* __restrict__ x, const int* __restri
     const uint4* src = reinterpret_cast<const uint4*>(x + t0 * H);
     uint4* dst = reinterpret_cast<uint4*>(xp);
     const int total = ntok * chunks;
-    for (int i = threadIdx.x; i < total; i += blockDim.x) {
-      const int tl = i / chunks, c = i - tl * chunks;
-      const uint4 v = __ldg(src + (int64_t)tl * chunks + c);
-      for (int j = 0; j < k; ++j) dst[(int64_t)pos[tl * k + j] * chunks + c] = v;
+    // four independent 16-byte loads in flight per thread before the stores
+    for (int i0 = threadIdx.x; i0 < total; i0 += 4 * blockDim.x) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < total) v[u] = __ldg(src + i);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < total) {
+          const int tl = i / chunks, c = i - tl * chunks;
+          for (int j = 0; j < k; ++j) dst[(int64_t)pos[tl * k + j] * chunks + c] = v[u];
+        }
+      }
     }
   } else {
     const int64_t total = (int64_t)ntok * H;
