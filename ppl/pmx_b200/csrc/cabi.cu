@@ -15,13 +15,6 @@ std::atomic<long long> g_launches{0};
 
 void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
-void set_error(const char* fmt, ...) {
-  va_list ap;
-  va_start(ap, fmt);
-  vsnprintf(g_error, sizeof(g_error), fmt, ap);
-  va_end(ap);
-}
-
 int fail(int status, const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);

@@ -11,7 +11,6 @@
 namespace pmx {
 
 // ---- error text kept per host thread for pmx_moe_last_error() ---------------
-void set_error(const char* fmt, ...);
 int fail(int status, const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
 int sm_count();  // SMs of the current device (cached per device)
