@@ -380,7 +380,7 @@ def main():
         # reduced-ffn case of the same kernel (profiles/grouped_gemm_tc_*.md); traffic is
         # >99 % weights and scales with the ffn size
         ratio = TRAFFIC_RATIO.get(roof["bound"])
-        roof.update({"traffic": work["bytes_gate_up"] * ratio if ratio else None, "kernel": "grouped_gemm_tc_kernel (gate/up projection + SwiGLU)",
+        roof.update({"traffic": work["bytes_gate_up"] * ratio if ratio else None, "kernel": "gate/up grouped GEMM with SwiGLU epilogue (grouped_gemm_tc_kernel; grouped_gemm_tc_pair_kernel for >= 1024 rows per expert)",
                      "kernel_ms": kernel_ms["gate_up"], "peak_source": peaks["source"],
                      "algorithmic_bytes": work["bytes_gate_up"], "algorithmic_flops": work["flops_gate_up"],
                      "timing": "CUDA events around K back-to-back replays of a CUDA graph holding this launch alone, same run"})

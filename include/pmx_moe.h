@@ -57,7 +57,9 @@ typedef enum pmx_gemm_kernel {
   PMX_GEMM_AUTO = 0,
   PMX_GEMM_TC_TOKENS_M = 1,  /* tcgen05: tokens on the MMA M dimension (prefill shape) */
   PMX_GEMM_TC_WEIGHTS_M = 2, /* tcgen05: weight rows on MMA M, tokens on MMA N (decode shape) */
-  PMX_GEMM_SIMT = 3          /* CUDA-core kernel, exact fp32 arithmetic (the only one for fp32) */
+  PMX_GEMM_SIMT = 3,         /* CUDA-core kernel, exact fp32 arithmetic (the only one for fp32) */
+  PMX_GEMM_TC_TOKENS_M_PAIRED = 4 /* tcgen05 cta_group::2: two CTAs (SMs) share a 256-token tile and
+                                     each loads half of the weight tile (prefill shape) */
 } pmx_gemm_kernel;
 
 /* optional tiling override for pmx_moe_grouped_linear; zero fields mean "choose" */

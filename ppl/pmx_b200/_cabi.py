@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(PKG, "libpmx_moe_b200.so")
 
 DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
 EPILOGUE_NONE, EPILOGUE_SWIGLU = 0, 1
-GEMM_AUTO, GEMM_TC_TOKENS_M, GEMM_TC_WEIGHTS_M, GEMM_SIMT = 0, 1, 2, 3
+GEMM_AUTO, GEMM_TC_TOKENS_M, GEMM_TC_WEIGHTS_M, GEMM_SIMT, GEMM_TC_TOKENS_M_PAIRED = 0, 1, 2, 3, 4
 
 
 class GemmPlan(C.Structure):

@@ -60,7 +60,18 @@ int choose_linear(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   const int want = user ? user->kernel : PMX_GEMM_AUTO;
   c->tc = false;
   if (want == PMX_GEMM_SIMT) return PMX_OK;
-  c->tc = plan_gemm_tc(M, N, K, E, dtype, epilogue, user, &c->plan);
+  if (want == PMX_GEMM_TC_TOKENS_M_PAIRED) {
+    c->tc = plan_gemm_tc_pair(M, N, K, E, dtype, epilogue, user, &c->plan);
+  } else {
+    c->tc = plan_gemm_tc(M, N, K, E, dtype, epilogue, user, &c->plan);
+    // Large experts (prefill): two SMs per 256-token tile.  Measured on B200 for the
+    // Mixtral shapes: 1453 against 1334 TFLOP/s (gate/up), 1416 against 1278 (down); with
+    // a few hundred rows per expert the larger token tile wastes more than pairing gains.
+    if (c->tc && want == PMX_GEMM_AUTO && c->plan.kernel == PMX_GEMM_TC_TOKENS_M && M / E >= 1024) {
+      TcPlan paired;
+      if (plan_gemm_tc_pair(M, N, K, E, dtype, epilogue, user, &paired)) c->plan = paired;
+    }
+  }
   if (!c->tc && want != PMX_GEMM_AUTO)
     return fail(PMX_ERR_UNSUPPORTED, "grouped_linear: the requested tensor-core plan does not cover this shape/dtype");
   return PMX_OK;
@@ -128,7 +139,7 @@ size_t pmx_moe_grouped_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, i
                                               const pmx_gemm_plan* plan) {
   LinearChoice c;
   if (choose_linear(M, N, K, E, dtype, epilogue, plan, &c) != PMX_OK) return 0;
-  if (!c.tc) return kStatusBytes;
+  if (!c.tc || c.plan.kernel == PMX_GEMM_TC_TOKENS_M_PAIRED) return kStatusBytes;
   return gemm_tc_workspace_bytes(M, N, epilogue, c.plan);
 }
 
@@ -152,8 +163,12 @@ int pmx_moe_grouped_linear(const void* x, const int64_t* expert_offset, const vo
     if (zero_outside) return launch_zero_outside(y, expert_offset, M, n_out, E, dtype, s);
     return PMX_OK;
   }
-  st = launch_gemm_tc(x, expert_offset, w, bias, y, M, N, K, E, dtype, epilogue, beta, c.plan,
-                      workspace, workspace_bytes, s);
+  if (c.plan.kernel == PMX_GEMM_TC_TOKENS_M_PAIRED)
+    st = launch_gemm_tc_pair(x, expert_offset, w, bias, y, M, N, K, E, dtype, epilogue, beta, c.plan,
+                             workspace, workspace_bytes, s);
+  else
+    st = launch_gemm_tc(x, expert_offset, w, bias, y, M, N, K, E, dtype, epilogue, beta, c.plan,
+                        workspace, workspace_bytes, s);
   if (st != PMX_OK) return st;
   // with split-K the final sum already writes zeros to rows no expert owns
   if (zero_outside && c.plan.split_k == 1) return launch_zero_outside(y, expert_offset, M, n_out, E, dtype, s);

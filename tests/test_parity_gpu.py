@@ -213,7 +213,7 @@ TC_SHAPES = [
 
 
 @pytest.mark.parametrize("M,N,K,E", TC_SHAPES)
-@pytest.mark.parametrize("kernel", [1, 2, 3])
+@pytest.mark.parametrize("kernel", [1, 2, 3, 4])
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 def test_grouped_linear_kernels(F, M, N, K, E, kernel, dtype):
     rng = np.random.default_rng(M + N + K + kernel)
@@ -221,7 +221,7 @@ def test_grouped_linear_kernels(F, M, N, K, E, kernel, dtype):
 
 
 @pytest.mark.parametrize("M,N,K,E", TC_SHAPES)
-@pytest.mark.parametrize("kernel", [1, 2, 3])
+@pytest.mark.parametrize("kernel", [1, 2, 3, 4])
 def test_grouped_linear_swiglu_fused(F, M, N, K, E, kernel):
     from ppl.pmx_b200._cabi import PmxError
     rng = np.random.default_rng(M * 3 + N + K + kernel)
@@ -256,7 +256,8 @@ def test_grouped_linear_split_k_with_swiglu_in_the_final_sum(F, kernel, split, M
     run_linear(F, rng, M, 1024, 2048, 8, "bf16", plan=plan, swiglu=True)
 
 
-@pytest.mark.parametrize("tile", [dict(kernel=1, tile_feat=32), dict(kernel=1, tile_feat=64),
+@pytest.mark.parametrize("tile", [dict(kernel=4, tile_feat=32), dict(kernel=4, tile_feat=64, stages=2), dict(kernel=4, max_ctas=6),
+                                  dict(kernel=4, tile_feat=256), dict(kernel=1, tile_feat=32), dict(kernel=1, tile_feat=64),
                                   dict(kernel=1, tile_feat=128, stages=2), dict(kernel=2, tile_tok=16),
                                   dict(kernel=2, tile_tok=64, stages=3), dict(kernel=2, tile_tok=256),
                                   dict(kernel=1, max_ctas=3), dict(kernel=2, max_ctas=1)])
@@ -281,6 +282,8 @@ def test_grouped_linear_stream_k(F, plan, swiglu):
 
 def test_grouped_linear_auto_plan_and_fp32(F):
     rng = np.random.default_rng(12)
+    run_linear(F, rng, 4500, 256, 128, 4, "bf16", bias=True)   # auto -> paired CTAs (>= 1024 rows per expert)
+    run_linear(F, rng, 4500, 512, 128, 4, "bf16", swiglu=True)
     run_linear(F, rng, 700, 256, 128, 4, "f16")          # auto -> tokens on M
     run_linear(F, rng, 24, 256, 1024, 8, "f16")          # auto -> weights on M (+ split-K)
     run_linear(F, rng, 50, 100, 36, 4, "f16")            # N, K not multiples of 8 -> CUDA-core kernel
