@@ -308,7 +308,8 @@ def main():
         # per-stage pass: every stage of the step is captured in a CUDA graph of its own and
         # replayed K times between two CUDA events (no host launch gaps inside the figure);
         # with --no-graph the stages are launched eagerly instead
-        names = ["gate", "select", "route_select", "gate_up", "down", "reduce", "allreduce", "reduce_allreduce"]
+        names = ["gate", "select", "route_select", "gate_up", "down", "reduce", "allreduce", "reduce_allreduce",
+                 "skip_rms_norm"]
         kernel_ms = {n: 0.0 for n in names}
         keep = []
 
@@ -346,6 +347,10 @@ def main():
             o = stage("reduce", lambda: OPMX.moe_reduce(y.view(shape.T, k, -1), ew, inv, k))
             if world > 1:
                 stage("allreduce", lambda: dist.all_reduce(o, group=group))
+        # the normalisation in front of the block (not part of the step): x + skip -> RMSNorm
+        norm_w = torch.ones(shape.H, device=device, dtype=dt)
+        skip_dev = torch.randn_like(x_dev)
+        stage("skip_rms_norm", lambda: OPMX.skip_rms_norm(x_dev, norm_w, skip_dev, -1, 1e-5))
         sync_all()
         for g in keep:
             g.reset()
@@ -399,7 +404,9 @@ def main():
             "layer": {"ms_floor": layer_floor_s * 1e3, "frac_of_roofline": layer_floor_s * 1e3 / ms_step,
                       "active_experts": active, "graph": graph is not None,
                       "allreduce": ("peer-memory kernel fused with the combine" if use_peer else "nccl") if world > 1 else None,
-                      "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items()}},
+                      "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items() if n != "skip_rms_norm"},
+                      "front_end": {"skip_rms_norm_ms": round(kernel_ms["skip_rms_norm"], 5),
+                                    "gbs": 4 * x_host.numel() * x_host.element_size() / (kernel_ms["skip_rms_norm"] * 1e-3) / 1e9}},
         }
         if world == 1 and not args.no_cpu_baseline:
             wu_c, w2_c = blk.wu.weight.detach().cpu(), blk.w2.weight.detach().cpu()

@@ -190,6 +190,16 @@ int pmx_swiglu(const void* x, void* y, int64_t M, int64_t D, float beta,
 int pmx_silu(const void* x, const void* gate, void* y, int64_t n, int32_t dtype,
              void* stream);
 
+/* rms_norm / skip_rms_norm -- RMSNorm.forward and SkipRMSNorm.forward
+ * (torch_function/RMSNorm.py:15-24 and :42-56), the normalisation in front of the MoE
+ * block (model_zoo/mixtral/modeling/dynamic_batching/Model.py:261), over the last axis:
+ *   s = x (+ skip), rounded to T1 and returned in skip_out when skip is given;
+ *   y = T1(float(s) * rsqrt(mean(s^2) + eps)) * weight
+ * x, skip, y, skip_out [M,H] T1, weight [H] T1; skip and skip_out may be NULL together. */
+int pmx_skip_rms_norm(const void* x, const void* skip, const void* weight, void* y,
+                      void* skip_out, int64_t M, int64_t H, float eps, int32_t dtype,
+                      void* stream);
+
 /* moe_reduce -- MoeReduce.forward, torch_function/MoeReduce.py:23-25.
  *   y [T*k,N] T1, expert_weights [T,k] T1, invert_permutation [T,k] int64
  *   out[t,:] = sum_j expert_weights[t,j] * y[invert_permutation[t,j],:]   [T,N] T1

@@ -28,7 +28,7 @@ import numpy as np
 __all__ = [
     "bf16_bits_to_f32", "f32_to_bf16_bits", "round_to_dtype", "topk_desc",
     "moe_select", "moe_grouped_linear", "swiglu", "silu_gate", "moe_reduce",
-    "moe_block", "detie_scores", "rows_with_ties",
+    "moe_block", "detie_scores", "rows_with_ties", "skip_rms_norm",
 ]
 
 
@@ -215,6 +215,20 @@ def silu_gate(x: np.ndarray, gate: np.ndarray | None = None) -> np.ndarray:
     if gate is not None:
         y = y * np.asarray(gate, dtype=np.float64)
     return y.astype(np.float32)
+
+
+def skip_rms_norm(x: np.ndarray, weight: np.ndarray, skip: np.ndarray | None = None,
+                  eps: float = 1e-5, dtype: str = "f32"):
+    """torch_function/RMSNorm.py:42-56 (SkipRMSNorm.forward; RMSNorm.forward :15-24 when
+    skip is None), over the last axis, with the reference's roundings to `dtype`:
+    SkipOut = X + SkipIn (T1); Y = T1(float(SkipOut) * rsqrt(mean(SkipOut^2) + eps)) * weight (T1).
+    Arrays are float32 holding exact up-casts.  Returns (Y, SkipOut)."""
+    x = np.asarray(x, dtype=np.float32)
+    s = x if skip is None else round_to_dtype(x + np.asarray(skip, np.float32), dtype)
+    ms = np.mean(s.astype(np.float64) ** 2, axis=-1, keepdims=True)
+    y1 = round_to_dtype((s.astype(np.float64) / np.sqrt(ms + eps)).astype(np.float32), dtype)
+    y = round_to_dtype(y1 * np.asarray(weight, np.float32), dtype)
+    return y, s
 
 
 def moe_reduce(y: np.ndarray, expert_weights: np.ndarray,

@@ -55,6 +55,7 @@ def _load() -> C.CDLL:
         "pmx_moe_grouped_linear_check": (C.c_int, [vp, C.POINTER(i32 * 4), vp]),
         "pmx_swiglu": (C.c_int, [vp, vp, i64, i64, f32, i32, vp]),
         "pmx_silu": (C.c_int, [vp, vp, vp, i64, i32, vp]),
+        "pmx_skip_rms_norm": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, f32, i32, vp]),
         "pmx_moe_reduce": (C.c_int, [vp, vp, vp, vp, i64, i32, i64, i32, vp]),
         "pmx_moe_reduce_allreduce_buffer_bytes": (sz, [i64, i64, i32]),
         "pmx_moe_reduce_allreduce": (C.c_int, [vp, vp, vp, vp, i64, i32, i64, i32, C.POINTER(vp), i32, i32, sz, vp]),

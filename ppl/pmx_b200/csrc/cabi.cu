@@ -193,6 +193,11 @@ int pmx_silu(const void* x, const void* gate, void* y, int64_t n, int32_t dtype,
   return launch_silu(x, gate, y, n, dtype, (cudaStream_t)stream);
 }
 
+int pmx_skip_rms_norm(const void* x, const void* skip, const void* weight, void* y, void* skip_out,
+                      int64_t M, int64_t H, float eps, int32_t dtype, void* stream) {
+  return launch_skip_rms_norm(x, skip, weight, y, skip_out, M, H, eps, dtype, (cudaStream_t)stream);
+}
+
 int pmx_moe_reduce(const void* y, const void* expert_weights, const int64_t* invert_permutation,
                    void* out, int64_t T, int32_t k, int64_t N, int32_t dtype, void* stream) {
   return launch_reduce(y, expert_weights, invert_permutation, out, T, k, N, dtype, (cudaStream_t)stream);

@@ -89,6 +89,8 @@ int launch_select_static(const void* x, const void* scores, void* xp, void* w, i
 
 int launch_swiglu(const void* x, void* y, int64_t M, int64_t D, float beta, int dtype, cudaStream_t s);
 int launch_silu(const void* x, const void* gate, void* y, int64_t n, int dtype, cudaStream_t s);
+int launch_skip_rms_norm(const void* x, const void* skip, const void* weight, void* y, void* skip_out,
+                         int64_t M, int64_t H, float eps, int dtype, cudaStream_t s);
 int launch_reduce(const void* y, const void* w, const int64_t* inv, void* out, int64_t T, int k,
                   int64_t N, int dtype, cudaStream_t s);
 size_t reduce_allreduce_buffer_bytes(int64_t T, int64_t N, int dtype);

@@ -129,6 +129,73 @@ __global__ void silu_kernel(const T* __restrict__ x, const T* __restrict__ gate,
   }
 }
 
+// RMSNorm with an optional skip connection (RMSNorm.py:15-24 and :42-56):
+//   s = x (+ skip), rounded to T;  y = T(float(s) * rsqrt(mean(s^2) + eps)) * weight
+// One block per row, two passes over the row (the second one hits L1/L2).  The two
+// roundings of the reference (`Y.type_as(X) * weight`) are reproduced.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+skip_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ skip, const T* __restrict__ weight,
+                     T* __restrict__ y, T* __restrict__ skip_out, int64_t M, int64_t H, float eps) {
+  constexpr int V = VEC ? kVec<T> : 1;
+  __shared__ float warp_sums[8];
+  __shared__ float s_scale;
+  const int64_t chunks = H / V;
+  for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+    const T* xr = x + row * H;
+    const T* sr = skip ? skip + row * H : nullptr;
+    T* so = skip_out + row * H;
+    float acc = 0.f;
+    for (int64_t c = threadIdx.x; c < chunks; c += blockDim.x) {
+      if (VEC) {
+        float a[kVec<T>], b[kVec<T>];
+        unpack16<T>(ld_nc16(xr + c * V), a);
+        if (sr) {
+          unpack16<T>(ld_nc16(sr + c * V), b);
+#pragma unroll
+          for (int v = 0; v < V; ++v) a[v] = Elem<T>::to_f(Elem<T>::from_f(a[v] + b[v]));
+          *reinterpret_cast<uint4*>(so + c * V) = pack16<T>(a);
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc = fmaf(a[v], a[v], acc);
+      } else {
+        float a = Elem<T>::to_f(xr[c]);
+        if (sr) {
+          a = Elem<T>::to_f(Elem<T>::from_f(a + Elem<T>::to_f(sr[c])));
+          so[c] = Elem<T>::from_f(a);
+        }
+        acc = fmaf(a, a, acc);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float tot = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += warp_sums[w];
+      s_scale = rsqrtf(tot / (float)H + eps);
+    }
+    __syncthreads();
+    const float scale = s_scale;
+    const T* src = sr ? so : xr;      // the rounded sum written above, or x itself
+    for (int64_t c = threadIdx.x; c < chunks; c += blockDim.x) {
+      if (VEC) {
+        float a[kVec<T>], wv[kVec<T>];
+        unpack16<T>(*reinterpret_cast<const uint4*>(src + c * V), a);
+        unpack16<T>(ld_nc16(weight + c * V), wv);
+#pragma unroll
+        for (int v = 0; v < V; ++v) a[v] = Elem<T>::to_f(Elem<T>::from_f(a[v] * scale)) * wv[v];
+        *reinterpret_cast<uint4*>(y + row * H + c * V) = pack16<T>(a);
+      } else {
+        const float a = Elem<T>::to_f(Elem<T>::from_f(Elem<T>::to_f(src[c]) * scale));
+        y[row * H + c] = Elem<T>::from_f(a * Elem<T>::to_f(weight[c]));
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // rows outside [off[0], off[E]) <- 0   (the zero-initialised output of
 // MoeColumnParallelLinear.py:59 / MoeRowParallelLinear.py:45)
 template <typename T>
@@ -244,6 +311,25 @@ int launch_silu(const void* x, const void* gate, void* y, int64_t n, int dtype, 
       silu_kernel<T, true><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (const T*)gate, (T*)y, n);
     else
       silu_kernel<T, false><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (const T*)gate, (T*)y, n);
+  })
+  PMX_LAUNCHED();
+  return PMX_OK;
+}
+
+int launch_skip_rms_norm(const void* x, const void* skip, const void* weight, void* y, void* skip_out,
+                         int64_t M, int64_t H, float eps, int dtype, cudaStream_t s) {
+  if (!x || !weight || !y) return fail(PMX_ERR_INVALID_ARGUMENT, "skip_rms_norm: null pointer");
+  if (skip && !skip_out) return fail(PMX_ERR_INVALID_ARGUMENT, "skip_rms_norm: skip_out is required when skip is given");
+  if (M <= 0 || H <= 0) return fail(PMX_ERR_INVALID_ARGUMENT, "skip_rms_norm: M and H must be positive");
+  int64_t blocks = M < (int64_t)sm_count() * 8 ? M : (int64_t)sm_count() * 8;
+  PMX_DISPATCH_DTYPE(dtype, "skip_rms_norm", {
+    const bool vec = H % kVec<T> == 0 && aligned16(x) && aligned16(y) && aligned16(weight) &&
+                     (!skip || (aligned16(skip) && aligned16(skip_out)));
+    T* so = skip ? (T*)skip_out : (T*)y;   // unused without skip
+    if (vec)
+      skip_rms_norm_kernel<T, true><<<(int)blocks, 256, 0, s>>>((const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
+    else
+      skip_rms_norm_kernel<T, false><<<(int)blocks, 256, 0, s>>>((const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
   })
   PMX_LAUNCHED();
   return PMX_OK;

@@ -142,7 +142,8 @@ class MoeFeedForward(nn.Module):
 def patch_reference(opmx_module) -> None:
     """Rebind the MoE entry points of an imported OPMX `torch_function` module
     (the reference resolves them through that module at call time,
-    Model.py:191-211 and ModelParallel.py:156,193) to this implementation."""
+    Model.py:191-211 and ModelParallel.py:156,193) and of the normalisation in front of
+    the block (ModelLayers.py:36-49) to this implementation."""
     for name in ("moe_select", "moe_column_parallel_linear", "moe_row_parallel_linear", "moe_reduce",
-                 "swiglu", "silu"):
+                 "swiglu", "silu", "rms_norm", "skip_rms_norm"):
         setattr(opmx_module, name, getattr(OPMX, name))

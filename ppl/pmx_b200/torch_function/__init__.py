@@ -2,7 +2,7 @@
 `pmx_llm.torch_function` (OPMX torch_function/__init__.py:17-20,37-38)."""
 from .moe import (moe_select, moe_column_parallel_linear, moe_row_parallel_linear, moe_reduce,
                   swiglu, silu, moe_grouped_linear, moe_route_select, MoeSelect, MoeColumnParallelLinear,
-                  MoeRowParallelLinear, MoeReduce, SwiGLU, SiLU)
+                  MoeRowParallelLinear, MoeReduce, SwiGLU, SiLU, rms_norm, skip_rms_norm, RMSNorm, SkipRMSNorm)
 
 __all__ = ["moe_select", "moe_column_parallel_linear", "moe_row_parallel_linear", "moe_reduce",
-           "swiglu", "silu", "moe_grouped_linear", "moe_route_select"]
+           "swiglu", "silu", "moe_grouped_linear", "moe_route_select", "rms_norm", "skip_rms_norm"]

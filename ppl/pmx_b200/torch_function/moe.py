@@ -376,3 +376,69 @@ class SiLU(torch.autograd.Function):
 def silu(X: torch.Tensor, gate: torch.Tensor = None):
     """Signature of torch_function/SiLU.py:24-25."""
     return SiLU.apply(X, gate)
+
+
+# --------------------------------------------------------------------------- normalisation in front of the block
+def _rms_norm_launch(name, X, weight, SkipIn, axis, eps):
+    _require_cuda(name, X=X, weight=weight, SkipIn=SkipIn)
+    H = X.shape[-1]
+    if axis not in (-1, X.dim() - 1):
+        raise ValueError(f"{name}: only the last axis is supported (axis={axis})")
+    if tuple(weight.shape) != (H,) or weight.dtype != X.dtype:
+        raise ValueError(f"{name}: weight must be [{H}] in X's dtype")
+    if SkipIn is not None and (SkipIn.shape != X.shape or SkipIn.dtype != X.dtype):
+        raise ValueError(f"{name}: SkipIn must match X in shape and dtype")
+    code = _dtype_code(name, X)
+    M = X.numel() // H if H else 0
+    y = torch.empty_like(X, memory_format=torch.contiguous_format)
+    skip_out = torch.empty_like(y) if SkipIn is not None else None
+    if M > 0:
+        x2, w2 = X.contiguous(), weight.contiguous()
+        s2 = SkipIn.contiguous() if SkipIn is not None else None
+        with torch.cuda.device(X.device):
+            check(lib.pmx_skip_rms_norm(ptr(x2), ptr(s2), ptr(w2), ptr(y), ptr(skip_out), M, H, float(eps), code,
+                                        stream_of(X)))
+    return y, skip_out
+
+
+class RMSNorm(torch.autograd.Function):
+    """opmx::RMSNorm without skip (torch_function/RMSNorm.py:4-24)."""
+
+    @staticmethod
+    def symbolic(g, X, weight, axis: int = -1, eps: float = 1e-5):
+        return g.op("opmx::RMSNorm", X, weight, axis_i=axis, eps_f=eps, skip_term_i=False).setTypeAs(X)
+
+    @staticmethod
+    def forward(ctx, X, weight, axis: int = -1, eps: float = 1e-5):
+        if torch.onnx.is_in_onnx_export():
+            return X
+        return _rms_norm_launch("rms_norm", X, weight, None, axis, eps)[0]
+
+
+class SkipRMSNorm(torch.autograd.Function):
+    """opmx::RMSNorm with skip_term (torch_function/RMSNorm.py:27-56)."""
+
+    @staticmethod
+    def symbolic(g, X, weight, SkipIn=None, axis: int = -1, eps: float = 1e-5):
+        args = (X, weight) if SkipIn is None else (X, weight, SkipIn)
+        Y, SkipOut = g.op("opmx::RMSNorm", *args, axis_i=axis, eps_f=eps, skip_term_i=True, outputs=2)
+        return Y.setTypeAs(X), SkipOut.setTypeAs(X)
+
+    @staticmethod
+    def forward(ctx, X, weight, SkipIn=None, axis: int = -1, eps: float = 1e-5):
+        if torch.onnx.is_in_onnx_export():
+            return X, X
+        y, skip_out = _rms_norm_launch("skip_rms_norm", X, weight, SkipIn, axis, eps)
+        return y, (X if skip_out is None else skip_out)
+
+
+def rms_norm(X: torch.Tensor, weight: torch.Tensor, axis: int = -1, eps: float = 1e-5) -> torch.Tensor:
+    """Signature of torch_function/RMSNorm.py:59-61."""
+    return RMSNorm.apply(X, weight, axis, eps)
+
+
+def skip_rms_norm(X: torch.Tensor, weight: torch.Tensor, SkipIn: torch.Tensor = None, axis: int = -1,
+                  eps: float = 1e-5):
+    """Signature of torch_function/RMSNorm.py:64-66.  -> (Y, SkipOut); SkipOut is X + SkipIn
+    (X itself when SkipIn is None), the residual stream the next layer receives."""
+    return SkipRMSNorm.apply(X, weight, SkipIn, axis, eps)

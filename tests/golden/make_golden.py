@@ -137,6 +137,22 @@ def main():
             expert_weights=f32(w), invert_permutation=inv.numpy(), out=f32(out), **meta)
         print("reduce", dtype)
 
+    # ------------------------------------------------------------ rms norm
+    g = torch.Generator().manual_seed(35)
+    for dtype in ("f32", "f16", "bf16"):
+        dt = TORCH_DT[dtype]
+        x = torch.randn(3, 11, 96, generator=g).to(dt)
+        sk = torch.randn(3, 11, 96, generator=g).to(dt)
+        w = (1 + 0.1 * torch.randn(96, generator=g)).to(dt)
+        y_skip, s_out = OPMX.skip_rms_norm(x, w, sk, -1, 1e-5)
+        y_noskip, s_same = OPMX.skip_rms_norm(x, w, None, -1, 1e-6)
+        y_plain = OPMX.rms_norm(x, w, -1, 1e-5)
+        assert torch.equal(s_same, x)
+        np.savez_compressed(os.path.join(HERE, f"rmsnorm_{dtype}.npz"), dtype=dtype, x=f32(x), skip=f32(sk),
+                            weight=f32(w), y_skip=f32(y_skip), skip_out=f32(s_out), y_noskip=f32(y_noskip),
+                            y_plain=f32(y_plain), **meta)
+        print("rmsnorm", dtype)
+
     # ------------------------------------------- whole block (Model.py:187-214)
     def block(x, wr, wu, wd, E, k, dt):
         torch.set_default_dtype(dt)

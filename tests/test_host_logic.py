@@ -123,6 +123,25 @@ def test_onnx_export_matches_the_reference_graph():
     assert col_in[0] == sel[0] and col_in[1] == sel[3] and red_in[1] == sel[1] and red_in[2] == sel[2]
 
 
+def test_rms_norm_exports_the_reference_node():
+    import ppl.pmx_b200.torch_function as F
+
+    class M(torch.nn.Module):
+        def __init__(s):
+            super().__init__()
+            s.w = torch.nn.Parameter(torch.ones(32))
+
+        def forward(s, X, S):
+            y, h = F.skip_rms_norm(X, s.w, S, -1, 1e-6)
+            return F.rms_norm(y, s.w, -1, 1e-5), h
+
+    nodes, _ = _graph_nodes(M(), (torch.randn(4, 32), torch.randn(4, 32)))
+    assert [n["kind"] for n in nodes] == ["opmx::RMSNorm", "opmx::RMSNorm"]
+    assert nodes[0]["attrs"]["skip_term"] == 1 and nodes[0]["n_inputs"] == 3 and nodes[0]["n_outputs"] == 2
+    assert nodes[1]["attrs"]["skip_term"] == 0 and nodes[1]["attrs"]["axis"] == -1
+    assert abs(nodes[0]["attrs"]["eps"] - 1e-6) < 1e-12   # RMSNorm.py:9-10,33-39
+
+
 def test_export_placeholders_have_output_shapes_and_dtypes():
     import ppl.pmx_b200.torch_function as F
     from torch.onnx._internal.torchscript_exporter import _globals

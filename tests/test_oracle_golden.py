@@ -80,6 +80,19 @@ def test_reduce_matches_reference(dtype):
     np.testing.assert_allclose(out, g["out"], **tol)
 
 
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_rms_norm_matches_reference(dtype):
+    g = load(f"rmsnorm_{dtype}.npz")
+    ulp = {"f32": 2.0 ** -22, "f16": 2.0 ** -9, "bf16": 2.0 ** -6}[dtype]      # 2 ulp: rsqrt and two roundings
+    y, s = orc.skip_rms_norm(g["x"], g["weight"], g["skip"], 1e-5, dtype)
+    assert np.array_equal(s, g["skip_out"])
+    np.testing.assert_allclose(y, g["y_skip"], rtol=ulp, atol=1e-6)
+    y, s = orc.skip_rms_norm(g["x"], g["weight"], None, 1e-6, dtype)
+    assert np.array_equal(s, g["x"])
+    np.testing.assert_allclose(y, g["y_noskip"], rtol=ulp, atol=1e-6)
+    np.testing.assert_allclose(orc.skip_rms_norm(g["x"], g["weight"], None, 1e-5, dtype)[0], g["y_plain"], rtol=ulp, atol=1e-6)
+
+
 @pytest.mark.parametrize("name", ["block_f32", "block_f16", "block_bf16", "block_f16_fine"])
 def test_block_matches_reference(name):
     g = load(name + ".npz")

@@ -351,6 +351,40 @@ def test_reduce_allreduce_kernel_with_a_single_rank(F):
         assert torch.equal(out, F.moe_reduce(yd.view(T, k, N), wd, invd, k))
 
 
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_rms_norm_golden(F, dtype):
+    g = load(f"rmsnorm_{dtype}.npz")
+    ulp = 1.5 * {"f32": 2.0 ** -22, "f16": 2.0 ** -9, "bf16": 2.0 ** -6}[dtype]   # 3 ulp: rsqrt + two roundings
+    x, sk, w = dev(g["x"], dtype), dev(g["skip"], dtype), dev(g["weight"], dtype)
+    y, s = F.skip_rms_norm(x, w, sk, -1, 1e-5)
+    assert y.shape == x.shape and s.shape == x.shape and y.dtype == x.dtype
+    assert np.array_equal(host(s), g["skip_out"])                       # the residual stream is bit-exact
+    np.testing.assert_allclose(host(y), g["y_skip"], rtol=ulp, atol=1e-6)
+    y, s = F.skip_rms_norm(x, w, None, -1, 1e-6)
+    assert s is x or torch.equal(s, x)
+    np.testing.assert_allclose(host(y), g["y_noskip"], rtol=ulp, atol=1e-6)
+    np.testing.assert_allclose(host(F.rms_norm(x, w, -1, 1e-5)), g["y_plain"], rtol=ulp, atol=1e-6)
+    oy, _ = orc.skip_rms_norm(g["x"], g["weight"], g["skip"], 1e-5, dtype)
+    np.testing.assert_allclose(host(F.skip_rms_norm(x, w, sk)[0]), oy, rtol=ulp, atol=1e-6)
+
+
+@pytest.mark.parametrize("M,H,dtype", [(1, 4096, "f16"), (64, 4096, "f16"), (300, 1000, "bf16"), (7, 50, "f32"), (2000, 2048, "bf16")])
+def test_rms_norm_shapes(F, M, H, dtype):
+    rng = np.random.default_rng(M + H)
+    x = orc.round_to_dtype(rng.standard_normal((M, H)).astype(np.float32) * 3, dtype)
+    sk = orc.round_to_dtype(rng.standard_normal((M, H)).astype(np.float32), dtype)
+    w = orc.round_to_dtype(1 + 0.2 * rng.standard_normal(H).astype(np.float32), dtype)
+    ulp = 1.5 * {"f32": 2.0 ** -22, "f16": 2.0 ** -9, "bf16": 2.0 ** -6}[dtype]   # 3 ulp: rsqrt + two roundings
+    y, s = F.skip_rms_norm(dev(x, dtype), dev(w, dtype), dev(sk, dtype), -1, 1e-5)
+    oy, os_ = orc.skip_rms_norm(x, w, sk, 1e-5, dtype)
+    assert np.array_equal(host(s), os_)
+    np.testing.assert_allclose(host(y), oy, rtol=ulp, atol=1e-6)
+    with pytest.raises(ValueError):
+        F.rms_norm(dev(x, dtype), dev(w, dtype), 0)
+    with pytest.raises(RuntimeError):
+        F.rms_norm(dev(x, dtype).cpu(), dev(w, dtype).cpu())
+
+
 # --------------------------------------------------------------------------- block
 @pytest.mark.parametrize("name", ["block_f32", "block_f16", "block_bf16", "block_f16_fine"])
 @pytest.mark.parametrize("fused", [False, True])
