@@ -131,21 +131,71 @@ __global__ void silu_kernel(const T* __restrict__ x, const T* __restrict__ gate,
 
 // RMSNorm with an optional skip connection (RMSNorm.py:15-24 and :42-56):
 //   s = x (+ skip), rounded to T;  y = T(float(s) * rsqrt(mean(s^2) + eps)) * weight
-// One block per row, two passes over the row (the second one hits L1/L2).  The two
-// roundings of the reference (`Y.type_as(X) * weight`) are reproduced.
-template <typename T, bool VEC>
+// One block per row.  Rows of up to 4 x 256 sixteen-byte chunks (8192 halves) stay in
+// registers between the sum of squares and the scaling (REG); longer or unaligned
+// rows are read a second time (from L1/L2).  The two roundings of the reference
+// (`Y.type_as(X) * weight`) are reproduced.
+__device__ __forceinline__ float block_sum_256(float acc, float* warp_sums, float* result) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+  if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += warp_sums[w];
+    *result = tot;
+  }
+  __syncthreads();
+  return *result;
+}
+
+template <typename T, bool VEC, bool REG>
 __global__ void __launch_bounds__(256)
 skip_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ skip, const T* __restrict__ weight,
                      T* __restrict__ y, T* __restrict__ skip_out, int64_t M, int64_t H, float eps) {
   constexpr int V = VEC ? kVec<T> : 1;
+  constexpr int R = 4;   // chunks per thread held in registers (REG)
   __shared__ float warp_sums[8];
-  __shared__ float s_scale;
+  __shared__ float s_total;
   const int64_t chunks = H / V;
   for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
     const T* xr = x + row * H;
     const T* sr = skip ? skip + row * H : nullptr;
     T* so = skip_out + row * H;
     float acc = 0.f;
+    if (REG) {
+      float a[R][kVec<T>];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int64_t c = threadIdx.x + (int64_t)r * blockDim.x;
+        if (c < chunks) {
+          unpack16<T>(ld_nc16(xr + c * kVec<T>), a[r]);
+          if (sr) {
+            float b[kVec<T>];
+            unpack16<T>(ld_nc16(sr + c * kVec<T>), b);
+#pragma unroll
+            for (int v = 0; v < kVec<T>; ++v) a[r][v] = Elem<T>::to_f(Elem<T>::from_f(a[r][v] + b[v]));
+            *reinterpret_cast<uint4*>(so + c * kVec<T>) = pack16<T>(a[r]);
+          }
+#pragma unroll
+          for (int v = 0; v < kVec<T>; ++v) acc = fmaf(a[r][v], a[r][v], acc);
+        }
+      }
+      const float scale = rsqrtf(block_sum_256(acc, warp_sums, &s_total) / (float)H + eps);
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int64_t c = threadIdx.x + (int64_t)r * blockDim.x;
+        if (c < chunks) {
+          float wv[kVec<T>];
+          unpack16<T>(ld_nc16(weight + c * kVec<T>), wv);
+#pragma unroll
+          for (int v = 0; v < kVec<T>; ++v) a[r][v] = Elem<T>::to_f(Elem<T>::from_f(a[r][v] * scale)) * wv[v];
+          *reinterpret_cast<uint4*>(y + row * H + c * kVec<T>) = pack16<T>(a[r]);
+        }
+      }
+      __syncthreads();
+      continue;
+    }
     for (int64_t c = threadIdx.x; c < chunks; c += blockDim.x) {
       if (VEC) {
         float a[kVec<T>], b[kVec<T>];
@@ -167,17 +217,7 @@ skip_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ skip, const 
         acc = fmaf(a, a, acc);
       }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-    if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x >> 5] = acc;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float tot = 0.f;
-      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += warp_sums[w];
-      s_scale = rsqrtf(tot / (float)H + eps);
-    }
-    __syncthreads();
-    const float scale = s_scale;
+    const float scale = rsqrtf(block_sum_256(acc, warp_sums, &s_total) / (float)H + eps);
     const T* src = sr ? so : xr;      // the rounded sum written above, or x itself
     for (int64_t c = threadIdx.x; c < chunks; c += blockDim.x) {
       if (VEC) {
@@ -326,10 +366,12 @@ int launch_skip_rms_norm(const void* x, const void* skip, const void* weight, vo
     const bool vec = H % kVec<T> == 0 && aligned16(x) && aligned16(y) && aligned16(weight) &&
                      (!skip || (aligned16(skip) && aligned16(skip_out)));
     T* so = skip ? (T*)skip_out : (T*)y;   // unused without skip
-    if (vec)
-      skip_rms_norm_kernel<T, true><<<(int)blocks, 256, 0, s>>>((const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
+    if (vec && H / kVec<T> <= 4 * 256)
+      skip_rms_norm_kernel<T, true, true><<<(int)blocks, 256, 0, s>>>((const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
+    else if (vec)
+      skip_rms_norm_kernel<T, true, false><<<(int)blocks, 256, 0, s>>>((const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
     else
-      skip_rms_norm_kernel<T, false><<<(int)blocks, 256, 0, s>>>((const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
+      skip_rms_norm_kernel<T, false, false><<<(int)blocks, 256, 0, s>>>((const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
   })
   PMX_LAUNCHED();
   return PMX_OK;
