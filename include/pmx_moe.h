@@ -119,6 +119,26 @@ int pmx_moe_route_select(const void* x, const void* w_router, void* scores,
                          void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The whole front end of the MoE block in one launch, for decode-size batches:
+ * SkipRMSNorm.forward (torch_function/RMSNorm.py:42-56, the `ffn_norm` call at
+ * model_zoo/mixtral/modeling/dynamic_batching/Model.py:261), the router gate
+ * (Linear.py:24-33, Model.py:188) and MoeSelect.forward (MoeSelect.py:36-64):
+ *   s = x (+ skip) -> skip_out (the residual stream; skip and skip_out may be NULL together)
+ *   n = T1(float(s) * rsqrt(mean(s^2) + eps)) * norm_weight      (kept on chip)
+ *   scores = n . w_router^T, then the four outputs of pmx_moe_select for (n, scores);
+ *   x_expand_permute holds rows of n.
+ * Same shape limits as pmx_moe_route_select, and additionally the normalised rows of a
+ * block's tokens must fit in shared memory (workspace_bytes() returns 0 otherwise).
+ */
+size_t pmx_moe_norm_route_select_workspace_bytes(int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype);
+int pmx_moe_norm_route_select(const void* x, const void* skip, const void* norm_weight, float eps,
+                              const void* w_router, void* skip_out, void* scores,
+                              void* x_expand_permute, void* expert_weights,
+                              int64_t* invert_permutation, int64_t* expert_offset,
+                              int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * moe_select without a workspace argument.  Has no counterpart in the OPMX
  * reference: it exists for hosts that may not allocate device memory around
  * the call -- for example an inference-engine plug-in whose enqueue hook is

@@ -48,6 +48,9 @@ def _load() -> C.CDLL:
         "pmx_moe_select": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, vp, sz, vp]),
         "pmx_moe_route_select_workspace_bytes": (sz, [i64, i64, i32, i32, i32]),
         "pmx_moe_route_select": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, vp, sz, vp]),
+        "pmx_moe_norm_route_select_workspace_bytes": (sz, [i64, i64, i32, i32, i32]),
+        "pmx_moe_norm_route_select": (C.c_int, [vp, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32,
+                                                vp, sz, vp]),
         "pmx_moe_select_static": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, vp]),
         "pmx_moe_grouped_linear_workspace_bytes": (sz, [i64, i64, i64, i32, i32, i32, plan_p]),
         "pmx_moe_grouped_linear": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, f32, i32,

@@ -127,6 +127,20 @@ int pmx_moe_route_select(const void* x, const void* w_router, void* scores, void
                              expert_offset, T, H, E, k, dtype, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+size_t pmx_moe_norm_route_select_workspace_bytes(int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype) {
+  return norm_route_select_workspace_bytes(T, H, E, k, dtype);
+}
+
+int pmx_moe_norm_route_select(const void* x, const void* skip, const void* norm_weight, float eps,
+                              const void* w_router, void* skip_out, void* scores, void* x_expand_permute,
+                              void* expert_weights, int64_t* invert_permutation, int64_t* expert_offset,
+                              int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+  return launch_norm_route_select(x, skip, norm_weight, eps, w_router, skip_out, scores, x_expand_permute,
+                                  expert_weights, invert_permutation, expert_offset, T, H, E, k, dtype,
+                                  workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
 int pmx_moe_select_static(const void* x, const void* scores, void* x_expand_permute,
                           void* expert_weights, int64_t* invert_permutation, int64_t* expert_offset,
                           int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype, void* stream) {

@@ -84,6 +84,11 @@ size_t route_select_workspace_bytes(int64_t T, int64_t H, int E, int k, int dtyp
 int launch_route_select(const void* x, const void* wr, void* scores, void* xp, void* w, int64_t* inv,
                         int64_t* off, int64_t T, int64_t H, int E, int k, int dtype, void* ws,
                         size_t ws_bytes, cudaStream_t s);
+size_t norm_route_select_workspace_bytes(int64_t T, int64_t H, int E, int k, int dtype);
+int launch_norm_route_select(const void* x, const void* skip, const void* norm_weight, float eps, const void* wr,
+                             void* skip_out, void* scores, void* xp, void* w, int64_t* inv, int64_t* off,
+                             int64_t T, int64_t H, int E, int k, int dtype, void* ws, size_t ws_bytes,
+                             cudaStream_t s);
 int launch_select_static(const void* x, const void* scores, void* xp, void* w, int64_t* inv,
                          int64_t* off, int64_t T, int64_t H, int E, int k, int dtype, cudaStream_t s);
 

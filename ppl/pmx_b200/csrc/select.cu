@@ -374,13 +374,24 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
   return v;
 }
 
-template <typename T>
+// NORM: the rows routed are RMSNorm(x (+ skip)) * norm_w (SkipRMSNorm.forward,
+// RMSNorm.py:42-56, the ffn_norm of Model.py:261): each block normalises its own tokens
+// into shared memory first, writes the residual stream (skip_out) and then computes
+// logits from, and gathers, the normalised rows.
+struct NormArgs {
+  const void* skip;      // [T,H] or null
+  const void* weight;    // [H]
+  void* skip_out;        // [T,H] (required when skip is given)
+  float eps;
+};
+
+template <typename T, bool NORM>
 __global__ void __launch_bounds__(256)
 route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, int64_t H, int E, int k,
                     int tpb, T* __restrict__ scores, T* __restrict__ xp, T* __restrict__ weights,
                     int64_t* __restrict__ inv, int64_t* __restrict__ expert_offset,
                     unsigned long long* __restrict__ masks, unsigned int* __restrict__ counter,
-                    int* __restrict__ status) {
+                    int* __restrict__ status, NormArgs norm) {
   extern __shared__ unsigned int sm_rs[];
   const int groups = (Tn + 31) / 32;
   unsigned int* ballots = sm_rs;                                        // [groups][E]
@@ -390,7 +401,10 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
   int* my_ids = reinterpret_cast<int*>(logit + tpb * E);                // [tpb][k]
   int* pos = my_ids + tpb * k;                                          // [tpb][k]
   float* partial = reinterpret_cast<float*>(pos + tpb * k);             // [warps][E]
+  // NORM: normalised rows of my tokens, 16-byte aligned behind the arrays above
+  uint4* rows = reinterpret_cast<uint4*>((reinterpret_cast<uintptr_t>(partial + 8 * E) + 15) & ~uintptr_t(15));
   __shared__ int s_abort;
+  __shared__ float s_norm_sum[8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int t0 = blockIdx.x * tpb;
   const int ntok = max(0, min(tpb, Tn - t0));
@@ -398,6 +412,47 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
   const int chunks = (int)(H / V);
   if (threadIdx.x == 0) s_abort = 0;
 
+  // A0. (NORM) normalise my tokens into shared memory
+  if (NORM) {
+    const T* nw = reinterpret_cast<const T*>(norm.weight);
+    for (int tl = 0; tl < ntok; ++tl) {
+      const uint4* xr = reinterpret_cast<const uint4*>(x + (int64_t)(t0 + tl) * H);
+      const uint4* sr = norm.skip ? reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(norm.skip) + (int64_t)(t0 + tl) * H) : nullptr;
+      uint4* so = norm.skip ? reinterpret_cast<uint4*>(reinterpret_cast<T*>(norm.skip_out) + (int64_t)(t0 + tl) * H) : nullptr;
+      uint4* row = rows + (size_t)tl * chunks;
+      float acc = 0.f;
+      for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        float a[V];
+        unpack16<T>(__ldg(xr + c), a);
+        if (sr) {
+          float b[V];
+          unpack16<T>(__ldg(sr + c), b);
+#pragma unroll
+          for (int v = 0; v < V; ++v) a[v] = Elem<T>::to_f(Elem<T>::from_f(a[v] + b[v]));
+          so[c] = pack16<T>(a);
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc = fmaf(a[v], a[v], acc);
+        row[c] = pack16<T>(a);          // the (rounded) sum, scaled in place below
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+      if (lane == 0) s_norm_sum[warp] = acc;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w = 0; w < nwarps; ++w) tot += s_norm_sum[w];
+      const float scale = rsqrtf(tot / (float)H + norm.eps);
+      for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+        float a[V], wv[V];
+        unpack16<T>(row[c], a);
+        unpack16<T>(__ldg(reinterpret_cast<const uint4*>(nw) + c), wv);
+#pragma unroll
+        for (int v = 0; v < V; ++v) a[v] = Elem<T>::to_f(Elem<T>::from_f(a[v] * scale)) * wv[v];
+        row[c] = pack16<T>(a);
+      }
+      __syncthreads();
+    }
+  }
   // A1. logits of my tokens.  The warps split the hidden dimension; every lane
   // keeps 8 experts' partial dot products, so one pass issues 9 independent
   // 16-byte loads per lane.  Partial sums meet in shared memory.
@@ -409,7 +464,7 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
       for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
         float a[V];
-        unpack16<T>(__ldg(xr + c), a);
+        unpack16<T>(NORM ? rows[(size_t)tl * chunks + c] : __ldg(xr + c), a);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           if (e0 + j < E) {
@@ -527,7 +582,7 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
   uint4* dst = reinterpret_cast<uint4*>(xp);
   for (int i = threadIdx.x; i < ntok * chunks; i += blockDim.x) {
     const int tl = i / chunks, c = i - tl * chunks;
-    const uint4 v = __ldg(src + (int64_t)tl * chunks + c);
+    const uint4 v = NORM ? rows[i] : __ldg(src + (int64_t)tl * chunks + c);
     for (int j = 0; j < k; ++j) dst[(int64_t)pos[tl * k + j] * chunks + c] = v;
   }
 }
@@ -537,7 +592,8 @@ struct RouteSelectGeometry {
   size_t smem;
 };
 
-bool route_select_geometry(int64_t T, int64_t H, int E, int k, int dtype, RouteSelectGeometry* g) {
+bool route_select_geometry(int64_t T, int64_t H, int E, int k, int dtype, RouteSelectGeometry* g,
+                           bool with_norm = false) {
   const int vec = dtype == PMX_DTYPE_F32 ? 4 : 8;
   if (T <= 0 || T > kSmallMaxTokens || E <= 0 || E > kSmallMaxExperts || k <= 0 || k > 32 || k > E || H % vec) return false;
   const int sms = sm_count();
@@ -545,7 +601,8 @@ bool route_select_geometry(int64_t T, int64_t H, int E, int k, int dtype, RouteS
   g->nblk = (int)ceil_div(T, g->tpb);
   const int groups = (int)ceil_div(T, 32);
   g->smem = ((size_t)groups * E * 2 + (E + 1) + (size_t)g->tpb * E + 2 * (size_t)g->tpb * k + 8 * (size_t)E) * 4 + 16;
-  return g->nblk <= sms;
+  if (with_norm) g->smem += 16 + (size_t)g->tpb * H * (dtype == PMX_DTYPE_F32 ? 4 : 2);
+  return g->nblk <= sms && g->smem <= 200 * 1024;
 }
 
 struct SelectGeometry {
@@ -633,35 +690,60 @@ size_t route_select_workspace_bytes(int64_t T, int64_t H, int E, int k, int dtyp
   return 64 + (size_t)T * 8;   // counter + status words, then one expert mask per token
 }
 
-int launch_route_select(const void* x, const void* wr, void* scores, void* xp, void* w, int64_t* inv,
-                        int64_t* off, int64_t T, int64_t H, int E, int k, int dtype, void* ws,
-                        size_t ws_bytes, cudaStream_t s) {
-  if (!x || !wr || !scores || !xp || !w || !inv || !off) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_route_select: null pointer");
+int launch_route_select_impl(const void* x, const void* wr, void* scores, void* xp, void* w, int64_t* inv,
+                             int64_t* off, int64_t T, int64_t H, int E, int k, int dtype, void* ws,
+                             size_t ws_bytes, cudaStream_t s, bool with_norm, NormArgs norm) {
+  const char* name = with_norm ? "moe_norm_route_select" : "moe_route_select";
+  if (!x || !wr || !scores || !xp || !w || !inv || !off) return fail(PMX_ERR_INVALID_ARGUMENT, "%s: null pointer", name);
+  if (with_norm && (!norm.weight || (norm.skip && !norm.skip_out)))
+    return fail(PMX_ERR_INVALID_ARGUMENT, "%s: norm weight missing, or skip given without skip_out", name);
   RouteSelectGeometry g;
-  if (!route_select_geometry(T, H, E, k, dtype, &g))
-    return fail(PMX_ERR_UNSUPPORTED, "moe_route_select: covers 1..%d tokens, up to %d experts, k <= 32 and 16-byte rows (T=%lld E=%d k=%d H=%lld); use a linear followed by moe_select", kSmallMaxTokens, kSmallMaxExperts, (long long)T, E, k, (long long)H);
+  if (!route_select_geometry(T, H, E, k, dtype, &g, with_norm))
+    return fail(PMX_ERR_UNSUPPORTED, "%s: covers 1..%d tokens, up to %d experts, k <= 32 and 16-byte rows (T=%lld E=%d k=%d H=%lld); use the stand-alone operators", name, kSmallMaxTokens, kSmallMaxExperts, (long long)T, E, k, (long long)H);
   const size_t need = route_select_workspace_bytes(T, H, E, k, dtype);
-  if (!ws || ws_bytes < need) return fail(PMX_ERR_WORKSPACE, "moe_route_select: workspace of %zu bytes needed, %zu given", need, ws_bytes);
-  if (!aligned16(ws) || !aligned16(x) || !aligned16(wr) || !aligned16(xp))
-    return fail(PMX_ERR_ALIGNMENT, "moe_route_select: x, w_router, x_expand_permute and the workspace must be 16-byte aligned");
+  if (!ws || ws_bytes < need) return fail(PMX_ERR_WORKSPACE, "%s: workspace of %zu bytes needed, %zu given", name, need, ws_bytes);
+  if (!aligned16(ws) || !aligned16(x) || !aligned16(wr) || !aligned16(xp) ||
+      (with_norm && (!aligned16(norm.weight) || !aligned16(norm.skip) || !aligned16(norm.skip_out))))
+    return fail(PMX_ERR_ALIGNMENT, "%s: tensors and the workspace must be 16-byte aligned", name);
   unsigned int* counter = reinterpret_cast<unsigned int*>(ws);
   int* status = reinterpret_cast<int*>(ws) + 4;
   unsigned long long* masks = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(ws) + 64);
   PMX_CUDA_OK(cudaMemsetAsync(ws, 0, 64, s));
   int Tn = (int)T;
   void* args[] = {(void*)&x, (void*)&wr, (void*)&Tn, (void*)&H, (void*)&E, (void*)&k, (void*)&g.tpb, (void*)&scores,
-                  (void*)&xp, (void*)&w, (void*)&inv, (void*)&off, (void*)&masks, (void*)&counter, (void*)&status};
+                  (void*)&xp, (void*)&w, (void*)&inv, (void*)&off, (void*)&masks, (void*)&counter, (void*)&status,
+                  (void*)&norm};
   const void* kern = nullptr;
   switch (dtype) {
-    case PMX_DTYPE_F16: kern = (const void*)route_select_kernel<__half>; break;
-    case PMX_DTYPE_BF16: kern = (const void*)route_select_kernel<__nv_bfloat16>; break;
-    case PMX_DTYPE_F32: kern = (const void*)route_select_kernel<float>; break;
-    default: return fail(PMX_ERR_UNSUPPORTED, "moe_route_select: unknown dtype %d", dtype);
+    case PMX_DTYPE_F16: kern = with_norm ? (const void*)route_select_kernel<__half, true> : (const void*)route_select_kernel<__half, false>; break;
+    case PMX_DTYPE_BF16: kern = with_norm ? (const void*)route_select_kernel<__nv_bfloat16, true> : (const void*)route_select_kernel<__nv_bfloat16, false>; break;
+    case PMX_DTYPE_F32: kern = with_norm ? (const void*)route_select_kernel<float, true> : (const void*)route_select_kernel<float, false>; break;
+    default: return fail(PMX_ERR_UNSUPPORTED, "%s: unknown dtype %d", name, dtype);
   }
   if (g.smem > 48 * 1024) PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
   PMX_CUDA_OK(cudaLaunchCooperativeKernel(kern, dim3(g.nblk), dim3(256), args, g.smem, s));
   count_launches(1);
   return PMX_OK;
+}
+
+int launch_route_select(const void* x, const void* wr, void* scores, void* xp, void* w, int64_t* inv,
+                        int64_t* off, int64_t T, int64_t H, int E, int k, int dtype, void* ws,
+                        size_t ws_bytes, cudaStream_t s) {
+  return launch_route_select_impl(x, wr, scores, xp, w, inv, off, T, H, E, k, dtype, ws, ws_bytes, s, false, NormArgs{});
+}
+
+size_t norm_route_select_workspace_bytes(int64_t T, int64_t H, int E, int k, int dtype) {
+  RouteSelectGeometry g;
+  if (!route_select_geometry(T, H, E, k, dtype, &g, true)) return 0;
+  return 64 + (size_t)T * 8;
+}
+
+int launch_norm_route_select(const void* x, const void* skip, const void* norm_weight, float eps, const void* wr,
+                             void* skip_out, void* scores, void* xp, void* w, int64_t* inv, int64_t* off,
+                             int64_t T, int64_t H, int E, int k, int dtype, void* ws, size_t ws_bytes,
+                             cudaStream_t s) {
+  NormArgs norm{skip, norm_weight, skip_out, eps};
+  return launch_route_select_impl(x, wr, scores, xp, w, inv, off, T, H, E, k, dtype, ws, ws_bytes, s, true, norm);
 }
 
 // Device address of the built-in scratch on the current device, looked up once

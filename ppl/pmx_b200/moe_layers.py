@@ -18,7 +18,7 @@ import torch.distributed as dist
 from torch import nn
 
 from . import torch_function as OPMX
-from .torch_function.moe import moe_grouped_linear, moe_route_select
+from .torch_function.moe import moe_grouped_linear, moe_route_select, moe_norm_route_select
 
 
 def _world(proc_group) -> int:
@@ -104,6 +104,19 @@ class MoeFeedForward(nn.Module):
         self.w2 = MoeRowParallelLinear(proc_group, num_experts, intermediate_dim, hidden_dim,
                                        bias_term=linear_bias_term, input_is_parallel=True)
 
+    def forward_from_residual(self, x: torch.Tensor, skip: torch.Tensor | None, norm_weight: torch.Tensor,
+                              eps: float = 1e-5):
+        """`ffn_norm` + the block: what TransformerBlock.forward does at Model.py:261-266.
+        -> (ffn, h) with h = x + skip, the residual stream handed to the next layer.  For
+        decode-size batches the norm, the router gate and the select are one launch."""
+        E, k = self.num_experts, self.num_experts_per_token
+        fused = moe_norm_route_select(x, skip, norm_weight, eps, self.gate.weight, E, k) if self.fused else None
+        if fused is None:
+            norm, h = OPMX.skip_rms_norm(x, norm_weight, skip, -1, eps)
+            return self.forward(norm), h
+        h, _, x_experts, expert_weights, invert_permutation, expert_offset = fused
+        return self._experts(x_experts, expert_weights, invert_permutation, expert_offset), h
+
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor | None = None) -> torch.Tensor:
         E, k = self.num_experts, self.num_experts_per_token
         routed = None
@@ -119,6 +132,11 @@ class MoeFeedForward(nn.Module):
             x13 = OPMX.swiglu(self.wu(x_experts, expert_offset))
             x_out = self.w2(x13, expert_offset)
             return OPMX.moe_reduce(x_out, expert_weights, invert_permutation, k)
+        return self._experts(x_experts, expert_weights, invert_permutation, expert_offset)
+
+    def _experts(self, x_experts, expert_weights, invert_permutation, expert_offset):
+        """gate/up GEMM with SwiGLU epilogue -> down GEMM -> combine (+ exchange over TP)."""
+        k = self.num_experts_per_token
         world = _world(self.proc_group)
         flat = x_experts.view(-1, self.hidden_dim)
         h = moe_grouped_linear(flat, expert_offset, self.wu.weight, self.wu.bias, swiglu=True,

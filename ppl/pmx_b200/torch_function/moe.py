@@ -137,6 +137,46 @@ def moe_route_select(X: torch.Tensor, W_router: torch.Tensor, num_experts: int, 
     return scores, xp, w, inv, off
 
 
+def moe_norm_route_select(X: torch.Tensor, SkipIn: torch.Tensor | None, norm_weight: torch.Tensor, eps: float,
+                          W_router: torch.Tensor, num_experts: int, num_experts_per_token: int):
+    """skip_rms_norm -> router gate -> moe_select in one launch for decode-size batches
+    (RMSNorm.py:42-56, Linear.py:24-33 and MoeSelect.py:36-64 as called at Model.py:261,188,191).
+    -> (SkipOut, scores, X_expand_permute, expert_weights, invert_permutation, expert_offset),
+    X_expand_permute holding rows of the normalised input; SkipOut is X itself when SkipIn is
+    None.  Returns None when the shape is outside what the fused kernel covers."""
+    _require_cuda("moe_norm_route_select", X=X, SkipIn=SkipIn, norm_weight=norm_weight, W_router=W_router)
+    k, E = int(num_experts_per_token), int(num_experts)
+    lead, H = tuple(X.shape[:-1]), X.shape[-1]
+    if tuple(W_router.shape) != (E, H) or W_router.dtype != X.dtype:
+        raise ValueError(f"W_router must be [{E}, {H}] in X's dtype")
+    if tuple(norm_weight.shape) != (H,) or norm_weight.dtype != X.dtype:
+        raise ValueError(f"norm_weight must be [{H}] in X's dtype")
+    if SkipIn is not None and (SkipIn.shape != X.shape or SkipIn.dtype != X.dtype):
+        raise ValueError("SkipIn must match X in shape and dtype")
+    T = 1
+    for d in lead:
+        T *= d
+    code = _dtype_code("moe_norm_route_select", X)
+    nbytes = lib.pmx_moe_norm_route_select_workspace_bytes(T, H, E, k, code) if T > 0 else 0
+    if nbytes == 0:
+        return None
+    dev = X.device
+    x2 = X.contiguous().view(T, H)
+    s2 = SkipIn.contiguous().view(T, H) if SkipIn is not None else None
+    skip_out = torch.empty_like(x2) if SkipIn is not None else None
+    scores = torch.empty(*lead, E, dtype=X.dtype, device=dev)
+    xp = torch.empty(*lead, k, H, dtype=X.dtype, device=dev)
+    w = torch.empty(*lead, k, dtype=X.dtype, device=dev)
+    inv = torch.empty(*lead, k, dtype=torch.int64, device=dev)
+    off = torch.empty(E + 1, dtype=torch.int64, device=dev)
+    ws = workspace(nbytes, dev)
+    with torch.cuda.device(dev):
+        check(lib.pmx_moe_norm_route_select(ptr(x2), ptr(s2), ptr(norm_weight.contiguous()), float(eps),
+                                            ptr(W_router.contiguous()), ptr(skip_out), ptr(scores), ptr(xp), ptr(w),
+                                            ptr(inv), ptr(off), T, H, E, k, code, ptr(ws), ws.numel(), stream_of(X)))
+    return (X if skip_out is None else skip_out.view_as(X)), scores, xp, w, inv, off
+
+
 # --------------------------------------------------------------------------- grouped linear
 def moe_grouped_linear(X: torch.Tensor, expert_offset: torch.Tensor, W: torch.Tensor,
                        B: torch.Tensor | None = None, *, swiglu: bool = False, beta: float = 1.0,

@@ -135,6 +135,71 @@ def test_route_select_fused_router(F, T, H, E, k, dtype):
                               torch.zeros(8, 64, device="cuda", dtype=torch.float16), 8, 2) is None
 
 
+@pytest.mark.parametrize("T,H,E,k,dtype,with_skip", [(1, 4096, 8, 2, "f16", True), (64, 4096, 8, 2, "f16", True),
+                                                      (64, 4096, 8, 2, "bf16", False), (700, 512, 64, 8, "f16", True),
+                                                      (33, 64, 5, 3, "f32", True)])
+def test_norm_route_select_fused_front_end(F, T, H, E, k, dtype, with_skip):
+    """skip_rms_norm + router gate + select in one launch: the residual stream is bit-exact,
+    the normalised rows it routes are within 3 ulp of the oracle, the scores match the gate
+    linear of those rows and the routing is bit-exact for exactly those scores."""
+    rng = np.random.default_rng(T + E + H)
+    x = orc.round_to_dtype(rng.standard_normal((T, H)).astype(np.float32) * 2, dtype)
+    sk = orc.round_to_dtype(rng.standard_normal((T, H)).astype(np.float32), dtype) if with_skip else None
+    nw = orc.round_to_dtype(1 + 0.1 * rng.standard_normal(H).astype(np.float32), dtype)
+    wr = orc.round_to_dtype((rng.standard_normal((E, H)) * 0.05).astype(np.float32), dtype)
+    out = F.moe_norm_route_select(dev(x, dtype), dev(sk, dtype) if with_skip else None, dev(nw, dtype), 1e-5,
+                                  dev(wr, dtype), E, k)
+    assert out is not None
+    h, sc, xe, ew, inv, off = out
+    torch.cuda.synchronize()
+    oy, os_ = orc.skip_rms_norm(x, nw, sk, 1e-5, dtype)
+    assert np.array_equal(host(h), os_)
+    ulp = 1.5 * {"f32": 2.0 ** -22, "f16": 2.0 ** -9, "bf16": 2.0 ** -6}[dtype]
+    rows = host(xe).reshape(-1, H)[inv.cpu().numpy().reshape(-1)].reshape(T, k, H)   # slot (t, j) -> its row
+    for j in range(k):
+        np.testing.assert_allclose(rows[:, j], oy, rtol=ulp, atol=1e-6)
+    n_gpu = rows[:, 0]                                       # the normalised rows the kernel used
+    ref_scores = (n_gpu.astype(np.float64) @ wr.astype(np.float64).T).astype(np.float32)
+    assert_close(sc, ref_scores, dtype, "router scores")
+    s32 = host(sc)
+    if not orc.rows_with_ties(s32, k).any():
+        oxe, oew, oinv, ooff = orc.moe_select(n_gpu, s32, E, k, dtype)
+        assert np.array_equal(off.cpu().numpy(), ooff) and np.array_equal(inv.cpu().numpy(), oinv)
+        assert np.array_equal(host(xe).reshape(-1, H), oxe)
+        assert_ulp(ew, oew, dtype, msg="expert_weights")
+    assert F.moe_norm_route_select(torch.zeros(2000, 64, device="cuda", dtype=torch.float16), None,
+                                   torch.ones(64, device="cuda", dtype=torch.float16), 1e-5,
+                                   torch.zeros(8, 64, device="cuda", dtype=torch.float16), 8, 2) is None
+
+
+def test_block_from_residual(F):
+    """MoeFeedForward.forward_from_residual (norm + block; fused front end for a decode batch,
+    stand-alone operators for a large one) against the oracle chain."""
+    from ppl.pmx_b200 import workloads as W
+    from ppl.pmx_b200.moe_layers import MoeFeedForward
+    for wl, kw in (("decode_t64", dict(H=512, I=1024)), ("prefill", dict(T=1500, H=256, I=512))):
+        sh = W.scaled(W.WORKLOADS[wl], **kw)
+        x, wr, _, _ = W.make_activations(sh)
+        g = torch.Generator().manual_seed(3)
+        skip = torch.randn(sh.T, sh.H, generator=g).to(x.dtype)
+        nw = (1 + 0.1 * torch.randn(sh.H, generator=g)).to(x.dtype)
+        wu, w2 = W.make_expert_weights(sh, "cuda")
+        blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, None, False).cuda().to(W.TORCH_DTYPE[sh.dtype])
+        with torch.no_grad():
+            blk.gate.weight.copy_(wr)
+            blk.wu.weight.copy_(wu)
+            blk.w2.weight.copy_(w2)
+            out, h = blk.forward_from_residual(x.cuda(), skip.cuda(), nw.cuda(), 1e-5)
+            norm, h2 = F.skip_rms_norm(x.cuda(), nw.cuda(), skip.cuda(), -1, 1e-5)
+            fused = F.moe_norm_route_select(x.cuda(), skip.cuda(), nw.cuda(), 1e-5, blk.gate.weight, sh.E, sh.k)
+            sc = fused[1] if fused is not None else torch.nn.functional.linear(norm, blk.gate.weight)
+        assert torch.equal(h, h2)
+        oy, _ = orc.skip_rms_norm(host(x), host(nw), host(skip), 1e-5, sh.dtype)
+        r = orc.moe_block(oy, host(wr), host(wu), host(w2), sh.E, sh.k, sh.dtype, scores=host(sc),
+                          round_intermediates=False)
+        assert_close(out, r["out"], sh.dtype, wl)
+
+
 def test_select_errors(F):
     x = torch.randn(4, 8, device="cuda", dtype=torch.float16)
     s = torch.randn(4, 8, device="cuda", dtype=torch.float16)
