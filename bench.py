@@ -309,7 +309,7 @@ def main():
         # replayed K times between two CUDA events (no host launch gaps inside the figure);
         # with --no-graph the stages are launched eagerly instead
         names = ["gate", "select", "route_select", "gate_up", "down", "reduce", "allreduce", "reduce_allreduce",
-                 "skip_rms_norm"]
+                 "skip_rms_norm", "norm_route_select"]
         kernel_ms = {n: 0.0 for n in names}
         keep = []
 
@@ -351,6 +351,9 @@ def main():
         norm_w = torch.ones(shape.H, device=device, dtype=dt)
         skip_dev = torch.randn_like(x_dev)
         stage("skip_rms_norm", lambda: OPMX.skip_rms_norm(x_dev, norm_w, skip_dev, -1, 1e-5))
+        if OPMX.moe_norm_route_select(x_dev, skip_dev, norm_w, 1e-5, blk.gate.weight, E, k) is not None:
+            stage("norm_route_select",
+                  lambda: OPMX.moe_norm_route_select(x_dev, skip_dev, norm_w, 1e-5, blk.gate.weight, E, k))
         sync_all()
         for g in keep:
             g.reset()
@@ -404,8 +407,10 @@ def main():
             "layer": {"ms_floor": layer_floor_s * 1e3, "frac_of_roofline": layer_floor_s * 1e3 / ms_step,
                       "active_experts": active, "graph": graph is not None,
                       "allreduce": ("peer-memory kernel fused with the combine" if use_peer else "nccl") if world > 1 else None,
-                      "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items() if n != "skip_rms_norm"},
+                      "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items()
+                                    if n not in ("skip_rms_norm", "norm_route_select")},
                       "front_end": {"skip_rms_norm_ms": round(kernel_ms["skip_rms_norm"], 5),
+                                    "norm_route_select_ms": round(kernel_ms["norm_route_select"], 5) or None,
                                     "gbs": 4 * x_host.numel() * x_host.element_size() / (kernel_ms["skip_rms_norm"] * 1e-3) / 1e9}},
         }
         if world == 1 and not args.no_cpu_baseline:

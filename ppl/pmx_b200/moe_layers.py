@@ -110,7 +110,12 @@ class MoeFeedForward(nn.Module):
         -> (ffn, h) with h = x + skip, the residual stream handed to the next layer.  For
         decode-size batches the norm, the router gate and the select are one launch."""
         E, k = self.num_experts, self.num_experts_per_token
-        fused = moe_norm_route_select(x, skip, norm_weight, eps, self.gate.weight, E, k) if self.fused else None
+        tokens = x.numel() // x.shape[-1]
+        # one token per block is where the single launch pays (measured on B200: 16.2 us against
+        # 4.2 + 14.1 us at 64 tokens, but 26.6 against 6.2 + 18.5 us at 256)
+        fused = None
+        if self.fused and tokens <= 128:
+            fused = moe_norm_route_select(x, skip, norm_weight, eps, self.gate.weight, E, k)
         if fused is None:
             norm, h = OPMX.skip_rms_norm(x, norm_weight, skip, -1, eps)
             return self.forward(norm), h
