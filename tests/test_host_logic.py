@@ -61,6 +61,21 @@ def test_workspace_sizes_and_argument_errors_without_a_gpu(lib):
     assert lib.pmx_swiglu(one, one, 4, 7, 1.0, 0, None) == -1
     assert lib.pmx_moe_grouped_linear(one, one, one, None, one, 4, 8, 0, 2, 0, 0, 1.0, 1, None, one, 256, None) == -1
     assert lib.pmx_moe_select_static(one, one, one, one, one, one, 10 ** 7, 8, 8, 2, 0, None) == -4
+    # fused front ends: decode-size batches only, otherwise "use the stand-alone operators"
+    assert lib.pmx_moe_route_select_workspace_bytes(64, 4096, 8, 2, 0) == 64 + 64 * 8
+    assert lib.pmx_moe_route_select_workspace_bytes(2000, 4096, 8, 2, 0) == 0        # too many tokens
+    assert lib.pmx_moe_route_select_workspace_bytes(64, 4096, 65, 2, 0) == 0         # too many experts
+    assert lib.pmx_moe_route_select_workspace_bytes(64, 4100, 8, 2, 0) == 0          # rows not 16-byte multiples
+    assert lib.pmx_moe_norm_route_select_workspace_bytes(64, 4096, 8, 2, 0) == 64 + 64 * 8
+    assert lib.pmx_moe_norm_route_select_workspace_bytes(1024, 16384, 8, 2, 0) == 0  # rows do not fit on chip
+    assert lib.pmx_moe_route_select(one, one, one, one, one, one, one, 5000, 64, 8, 2, 0, one, 1 << 20, None) == -2
+    assert lib.pmx_moe_norm_route_select(one, None, None, 1e-5, one, None, one, one, one, one, one, 8, 64, 8, 2, 0,
+                                         one, 1 << 20, None) == -1                    # norm weight missing
+    assert lib.pmx_skip_rms_norm(one, one, one, one, None, 4, 64, 1e-5, 0, None) == -1  # skip without skip_out
+    assert lib.pmx_moe_reduce_allreduce_buffer_bytes(64, 4096, 0) == 16384 + 2 * 64 * 4096 * 2
+    table = (C.c_void_p * 9)(*([16] * 9))
+    assert lib.pmx_moe_reduce_allreduce(one, one, one, one, 4, 2, 64, 0, table, 0, 9, 1 << 30, None) == -1  # > 8 ranks
+    assert lib.pmx_moe_reduce_allreduce(one, one, one, one, 4, 2, 64, 0, table, 0, 2, 64, None) == -4      # small buffers
 
 
 def test_operators_refuse_cpu_tensors():
