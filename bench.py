@@ -359,6 +359,17 @@ def main():
             g.reset()
         del keep
     active = int((off[1:] - off[:-1]).gt(0).sum().item())
+    # phase boundaries of the last fused combine + all-reduce call (CTA 0 of this rank), from
+    # the %globaltimer stamps the kernel leaves in its control block (byte 512, 8 x u64)
+    ar_phases = None
+    if use_peer and getattr(blk, "_peer", None) is not None:
+        try:
+            import struct
+            st = struct.unpack("8Q", bytes(blk._peer.buffer[512:576].cpu().tolist()))
+            ar_phases = {"combine_done": st[1] - st[0], "epoch_published": st[2] - st[0],
+                         "peers_seen": st[3] - st[0], "sum_done": st[4] - st[0]}
+        except Exception:                                 # noqa: BLE001  (diagnostic only)
+            ar_phases = None
 
     if rank == 0:
         peaks = load_peaks()
@@ -407,6 +418,7 @@ def main():
             "layer": {"ms_floor": layer_floor_s * 1e3, "frac_of_roofline": layer_floor_s * 1e3 / ms_step,
                       "active_experts": active, "graph": graph is not None,
                       "allreduce": ("peer-memory kernel fused with the combine" if use_peer else "nccl") if world > 1 else None,
+                      "allreduce_phases_ns": ar_phases,
                       "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items()
                                     if n not in ("skip_rms_norm", "norm_route_select")},
                       "front_end": {"skip_rms_norm_ms": round(kernel_ms["skip_rms_norm"], 5),
