@@ -9,15 +9,24 @@ N > 1) on one batch of seeded synthetic tokens.  With N > 1 (launched by
 torchrun, one rank per GPU) every expert's intermediate dimension is sharded
 over the ranks, so the total work is fixed as N grows ("strong" scaling).
 
-The line printed by rank 0:
-  value     tokens/s with the inputs resident in HBM, K replays of the captured
-            CUDA graph of the step, CUDA events on the launching stream, max over ranks
+The line printed by rank 0 (headline workload: Mixtral-8x7B decode, 64 tokens, fp16):
+  value     tokens/s with the inputs resident in HBM: regions of K replays of the captured
+            CUDA graph of the step, CUDA events on the launching stream, max over ranks;
+            the median of `repeats.regions` regions (min and max are printed too)
   e2e       the same with the step's input copied from pinned host memory and
             its output copied back inside the timed region, every step
   roofline  the dominant kernel (gate/up grouped GEMM): its launch alone captured in a
             CUDA graph and replayed K times between two CUDA events, in the same run
-  cpu_baseline  the CPU port of the reference algorithm (oracle/cpu_port.py) on
-            the host cores of this machine, a bounded sample of the same workload
+  cpu_baseline  the reference's own CPU torch path (the unmodified OPMX operators staged
+            under oracle/_ref; kind "reference") or, where that is absent, the CPU port
+            of the same algorithm (oracle/cpu_port.py; kind "port"), on the host cores of
+            this machine, a bounded sample of the same workload
+  parity    routing compared bit for bit with the oracle, sampled tokens against an fp32
+            chain, and (N > 1) the tensor-parallel result against the same kernels run
+            with the full weights on rank 0; computed outside the timed regions
+  workloads the other configurations (decode at 1..256 tokens, prefill of 8192 tokens in
+            bf16, the fine-grained 64-expert layer with and without empty experts), each
+            with its own timing, roofline, per-stage kernel times, clocks and parity
 """
 from __future__ import annotations
 
@@ -39,6 +48,11 @@ import torch.distributed as dist  # noqa: E402
 TRAFFIC_RATIO = {"hbm": 1.008, "tensor": 1.03}
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
+HEADLINE = "decode_t64"
+EXTRA_WORKLOADS = ["decode_t1", "decode_t8", "decode_t32", "decode_t128", "decode_t256", "prefill", "finegrained",
+                   "finegrained_empty"]
+ATOL, RTOL = 2e-2, 1e-2          # parity tolerance of fp16 / bf16 results against fp32 math
+STAGES = ["gate", "select", "route_select", "gate_up", "down", "reduce", "allreduce", "reduce_allreduce"]
 
 
 def load_peaks():
@@ -109,27 +123,73 @@ def physical_gpu_index(local_rank: int) -> int:
     return local_rank
 
 
+def workload_config(shape, tp):
+    return {"workload": shape.name, "tokens": shape.T, "hidden": shape.H, "experts": shape.E,
+            "experts_per_token": shape.k, "ffn": shape.I, "parallelism": f"tp{tp}",
+            "l2": "weights per rank exceed the 126 MB L2, no flush between steps"}
+
+
 # ------------------------------------------------------------------------------ CPU arm
-def cpu_pass(shape, x, w_router, wu, w2, tokens):
-    from oracle import cpu_port
-    out, _ = cpu_port.moe_block(x[:tokens], w_router, wu, w2, shape.E, shape.k)
-    return out
+class CpuArm:
+    """The MoE block on host cores: the unmodified OPMX operators when they are staged
+    under oracle/_ref (kind "reference"), else the CPU port of the same algorithm."""
 
+    def __init__(self, shape):
+        from ppl.pmx_b200 import workloads as W
+        self.shape = shape
+        self.dt = W.TORCH_DTYPE[shape.dtype]
+        self.opmx = None
+        try:
+            import oracle
+            self.opmx = oracle.import_reference()
+            self.kind = "reference"
+        except ImportError:
+            self.kind = "port"
+        torch.set_num_threads(os.cpu_count() or 1)
+        self.cores = torch.get_num_threads()
 
-def time_cpu(shape, x, w_router, wu, w2, tokens, steps, warmup, budget_s=None):
-    torch.set_num_threads(os.cpu_count() or 1)
-    with torch.inference_mode():
-        for _ in range(warmup):
-            cpu_pass(shape, x, w_router, wu, w2, tokens)
-        times = []
-        t_begin = time.perf_counter()
-        for _ in range(steps):
-            t0 = time.perf_counter()
-            cpu_pass(shape, x, w_router, wu, w2, tokens)
-            times.append(time.perf_counter() - t0)
-            if budget_s is not None and time.perf_counter() - t_begin > budget_s:
-                break
-    return times
+    def step(self, x, w_router, wu, w2):
+        sh = self.shape
+        if self.opmx is None:
+            from oracle import cpu_port
+            return cpu_port.moe_block(x, w_router, wu, w2, sh.E, sh.k)[0]
+        O = self.opmx
+        # the reference allocates the outputs of its MoE linears with the global default
+        # dtype (MoeColumnParallelLinear.py:59, MoeRowParallelLinear.py:45): run it the way
+        # its loader does (Loader.py:76-79), with the default dtype set to the model's
+        old = torch.get_default_dtype()
+        torch.set_default_dtype(self.dt)
+        try:
+            E, k, H, I = sh.E, sh.k, sh.H, sh.I
+            scores = O.linear(x, w_router, None, H, E)                              # Model.py:188
+            xe, ew, inv, off = O.moe_select(x, scores, E, k)                        # :191
+            x13 = O.moe_column_parallel_linear(xe, off, wu, None, None, E, H, 2 * I, False)   # :198
+            x13 = O.swiglu(x13)                                                     # :200
+            y = O.moe_row_parallel_linear(x13, off, w2, None, None, E, I, H, True)  # :208
+            return O.moe_reduce(y, ew, inv, k)                                      # :211
+        finally:
+            torch.set_default_dtype(old)
+
+    def time(self, x, w_router, wu, w2, tokens, steps, warmup, budget_s):
+        xs = x[:tokens]
+        with torch.inference_mode():
+            for _ in range(warmup):
+                self.step(xs, w_router, wu, w2)
+            times = []
+            t_begin = time.perf_counter()
+            for _ in range(steps):
+                t0 = time.perf_counter()
+                self.step(xs, w_router, wu, w2)
+                times.append(time.perf_counter() - t0)
+                if time.perf_counter() - t_begin > budget_s:
+                    break
+        return times
+
+    def describe(self, tokens, n):
+        src = ("unmodified OPMX operators from oracle/_ref (linear, moe_select, moe_column_parallel_linear, swiglu, "
+               "moe_row_parallel_linear, moe_reduce)") if self.kind == "reference" else "oracle/cpu_port.py"
+        return (f"{src}: first {tokens} of {self.shape.T} tokens per step, all {self.shape.E} experts' full weights, "
+                f"{n} steps, torch {torch.__version__} CPU, {self.cores} threads")
 
 
 def run_reference(args, shape, rank):
@@ -137,56 +197,420 @@ def run_reference(args, shape, rank):
     if rank != 0:
         return
     from ppl.pmx_b200 import workloads as W
-    x, w_router, scores, _ = W.make_activations(shape, detie=False)
+    x, w_router, _, _ = W.make_activations(shape, detie=False)
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     wu, w2 = W.make_expert_weights(shape, dev)
     wu, w2 = wu.cpu(), w2.cpu()
+    arm = CpuArm(shape)
     tokens = min(shape.T, 1024)
-    times = time_cpu(shape, x, w_router, wu, w2, tokens, args.steps, min(args.warmup, 2))
+    times = arm.time(x, w_router, wu, w2, tokens, args.steps, args.warmup, budget_s=240.0)
     total = sum(times)
     value = tokens * len(times) / total
-    sample = f"first {tokens} of {shape.T} tokens per step, all {shape.E} experts' full weights, {len(times)} steps"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": len(times), "warmup": min(args.warmup, 2), "ms_per_step": 1e3 * total / len(times),
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": shape.dtype,
-        "data": "synthetic", "config": workload_config(shape, 1, "cpu"),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample},
+        "data": "synthetic", "config": workload_config(shape, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": arm.cores, "kind": arm.kind, "device": "cpu",
+                         "sample": arm.describe(tokens, len(times))},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(shape, tp, where):
-    return {"workload": shape.name, "tokens": shape.T, "hidden": shape.H, "experts": shape.E,
-            "experts_per_token": shape.k, "ffn": shape.I, "parallelism": f"tp{tp}",
-            "l2": "weights per rank exceed the 126 MB L2, no flush between steps", "device": where}
-
-
 # ------------------------------------------------------------------------------ GPU arm
+class Ctx:
+    pass
+
+
+def sync_all(ctx):
+    if ctx.world > 1:
+        dist.barrier(group=ctx.group)
+    torch.cuda.synchronize()
+
+
+def timed(ctx, fn, steps):
+    """K calls of fn between two CUDA events on the current stream, barrier + synchronise on
+    both sides, max over ranks; milliseconds for the K calls."""
+    sync_all(ctx)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    sync_all(ctx)
+    ms = torch.tensor([e0.elapsed_time(e1)], device=ctx.device)
+    if ctx.world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=ctx.group)
+    return float(ms.item())
+
+
+def capture(fn):
+    """fn captured in a CUDA graph (after one run on a side stream)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = fn()
+    return g, out
+
+
+def get_block(ctx, shape, full: bool, w_router=None):
+    """The MoE block of this rank for `shape` (cached by architecture and dtype: the decode
+    workloads share one set of weights).  full=True: the whole weights, no process group."""
+    from ppl.pmx_b200 import workloads as W
+    from ppl.pmx_b200.moe_layers import MoeFeedForward
+    key = (shape.H, shape.I, shape.E, shape.k, shape.dtype, full)
+    if key in ctx.blocks:
+        return ctx.blocks[key]
+    dt = W.TORCH_DTYPE[shape.dtype]
+    tp = 1 if full else ctx.world
+    peer_tokens = 0
+    if tp > 1 and ctx.args.allreduce != "nccl" and not ctx.peer_failed:
+        peer_tokens = (4 << 20) // (shape.H * 2)          # results of up to 4 MB go through the peer kernel
+        if ctx.args.allreduce == "peer":
+            peer_tokens = max(peer_tokens, 8192)
+    blk = MoeFeedForward(shape.H, shape.I, shape.E, shape.k, None if full else ctx.group, False,
+                         peer_reduce_tokens=peer_tokens, peer_algorithm=ctx.args.peer_algo).to(ctx.device, dt)
+    wu, w2 = W.make_expert_weights(shape, ctx.device, tp_rank=0 if full else ctx.rank, tp_size=tp)
+    if w_router is None:
+        _, w_router, _, _ = W.make_activations(shape, detie=False)
+    with torch.no_grad():
+        blk.gate.weight.copy_(w_router)
+        blk.wu.weight.copy_(wu)
+        blk.w2.weight.copy_(w2)
+    del wu, w2
+    ctx.blocks[key] = blk
+    return blk
+
+
+def uses_peer(blk, shape):
+    return blk._peer is not None and blk._peer.fits(shape.T, shape.H, blk.wu.weight.dtype)
+
+
+def routing_of(blk, x_dev, shape):
+    """(scores, x_experts, expert_weights, invert_permutation, expert_offset) exactly as the block computes them."""
+    import ppl.pmx_b200.torch_function as OPMX
+    r = OPMX.moe_route_select(x_dev, blk.gate.weight, shape.E, shape.k)
+    if r is not None:
+        return r
+    scores = OPMX.router_gate(x_dev, blk.gate.weight)
+    return (scores,) + tuple(OPMX.moe_select(x_dev, scores, shape.E, shape.k))
+
+
+def parity_check(ctx, shape, blk, x_dev, out):
+    """Untimed.  Routing bit for bit against the oracle (on the scores the kernel produced),
+    `samples` tokens of the result against an fp32 chain over the full weights, and for N > 1
+    the tensor-parallel result against the same kernels with the full weights on rank 0 plus
+    identical routing on every rank."""
+    import numpy as np
+    from oracle import moe_oracle as orc
+    E, k, T, H, I = shape.E, shape.k, shape.T, shape.H, shape.I
+    with torch.no_grad():
+        scores, _, ew, inv, off = routing_of(blk, x_dev, shape)
+    torch.cuda.synchronize()
+    rec = {"tolerance": f"max-abs {ATOL} / rel {RTOL} against fp32 math"}
+    ranks_same = None
+    if ctx.world > 1:
+        # the routing is replicated: every rank must hold the same integers
+        mine = torch.cat([off.view(-1), inv.view(-1)])
+        allr = [torch.empty_like(mine) for _ in range(ctx.world)]
+        dist.all_gather(allr, mine, group=ctx.group)
+        outs = [torch.empty_like(out) for _ in range(ctx.world)]
+        dist.all_gather(outs, out.contiguous(), group=ctx.group)
+        ranks_same = all(torch.equal(a, allr[0]) for a in allr)
+        rec["routing_identical_on_all_ranks"] = ranks_same
+        rec["output_identical_on_all_ranks"] = all(torch.equal(o, outs[0]) for o in outs)
+    if ctx.rank != 0:
+        return None
+    s32 = scores.float().cpu().numpy().reshape(T, E)
+    _, oew, oinv, ooff = orc.moe_select(np.zeros((T, 1), np.float32), s32, E, k, shape.dtype)
+    rec["expert_offset_exact"] = bool(np.array_equal(off.cpu().numpy(), ooff))
+    rec["invert_permutation_exact"] = bool(np.array_equal(inv.cpu().numpy().reshape(T, k), oinv))
+    rec["rows_with_tied_scores"] = int(orc.rows_with_ties(s32, k).sum())
+    rec["empty_experts"] = int((np.diff(ooff) == 0).sum())
+    # sampled tokens against fp32 math over the full weights
+    full = blk if ctx.world == 1 else get_block(ctx, shape, full=True, w_router=blk.gate.weight.detach())
+    rng = np.random.default_rng(0)
+    sample = rng.choice(T, size=min(32, T), replace=False)
+    expert_of_row = np.searchsorted(ooff, np.arange(T * k), side="right") - 1
+    max_abs, max_rel, ok = 0.0, 0.0, True
+    with torch.no_grad():
+        for t in sample:
+            acc = torch.zeros(H, device=ctx.device, dtype=torch.float32)
+            xt = x_dev[t].float()
+            for j in range(k):
+                e = int(expert_of_row[oinv[t, j]])
+                gu = full.wu.weight[e].float() @ xt
+                h = gu[I:] * gu[:I] * torch.sigmoid(gu[:I])
+                acc += float(oew[t, j]) * (full.w2.weight[e].float() @ h)
+            got = out[t].float()
+            err = (got - acc).abs()
+            max_abs = max(max_abs, float(err.max()))
+            max_rel = max(max_rel, float((err / acc.abs().clamp_min(1.0)).max()))
+            ok &= bool((err <= ATOL + RTOL * acc.abs()).all())
+    rec.update({"sampled_tokens": int(len(sample)), "max_abs_err": max_abs, "max_rel_err": max_rel,
+                "sampled_within_tolerance": ok})
+    good = rec["expert_offset_exact"] and rec["invert_permutation_exact"] and ok
+    if ctx.world > 1:
+        with torch.no_grad():
+            one = full(x_dev)
+        torch.cuda.synchronize()
+        d = (out.float() - one.float()).abs()
+        same = bool((d <= ATOL + RTOL * one.float().abs()).all())
+        rec["tp_vs_tp1"] = {"max_abs_diff": float(d.max()), "within_tolerance": same,
+                            "note": "tensor-parallel result of this run against the same kernels on rank 0 with the "
+                                    "full weights (the partial sums are rounded and added in another order)"}
+        good = good and same and bool(ranks_same)
+    rec["ok"] = bool(good)
+    return rec
+
+
+def measure(ctx, shape, steps, warmup, regions, headline):
+    """Times one workload; returns its record on rank 0 (None elsewhere)."""
+    import ppl.pmx_b200.torch_function as OPMX
+    from ppl.pmx_b200 import _cabi, workloads as W
+    from ppl.pmx_b200.torch_function.moe import moe_grouped_linear
+    args = ctx.args
+    dt = W.TORCH_DTYPE[shape.dtype]
+    x_host, w_router, _, _ = W.make_activations(shape, detie=False)
+    x_host = x_host.pin_memory()
+    out_host = torch.empty(shape.T, shape.H, dtype=dt).pin_memory()
+    blk = get_block(ctx, shape, full=False, w_router=w_router)
+    x_dev = x_host.to(ctx.device)
+    E, k = shape.E, shape.k
+
+    def step():
+        with torch.no_grad():
+            return blk(x_dev)
+
+    if ctx.world > 1 and blk.peer_reduce_tokens > 0 and blk._peer is None:
+        # the peer-memory exchange needs the ranks' buffers mapped into each other
+        # (symmetric memory); if this machine refuses, say so and use NCCL
+        try:
+            step()
+            torch.cuda.synchronize()
+            ok = torch.ones(1, device=ctx.device)
+        except Exception as exc:                      # noqa: BLE001
+            print(f"[bench] rank {ctx.rank}: peer-memory all-reduce unavailable ({exc}); using NCCL", file=sys.stderr)
+            ok = torch.zeros(1, device=ctx.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=ctx.group)
+        if ok.item() == 0:
+            ctx.peer_failed = True
+            for b in ctx.blocks.values():
+                b.peer_reduce_tokens, b._peer = 0, None
+    use_peer = uses_peer(blk, shape) if ctx.world > 1 else False
+
+    for _ in range(warmup):
+        out = step()
+    torch.cuda.synchronize()
+    launches_before = _cabi.lib.pmx_moe_kernel_launches()
+    out = step()
+    torch.cuda.synchronize()
+    launches_per_step = _cabi.lib.pmx_moe_kernel_launches() - launches_before
+    blk.check()                                       # no bounded wait ran out so far
+    graph = None
+    if not args.no_graph:
+        graph, out = capture(step)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+            return out
+        return step()
+
+    def e2e_step():
+        x_dev.copy_(x_host, non_blocking=True)
+        o = run_step()
+        out_host.copy_(o, non_blocking=True)
+
+    sampler = ClockSampler(physical_gpu_index(ctx.local_rank))
+    kernel_ms = {n: 0.0 for n in STAGES + ["skip_rms_norm", "norm_route_select"]}
+    with sampler:
+        region_ms = [timed(ctx, run_step, steps) for _ in range(regions)]
+        ms_e2e = timed(ctx, e2e_step, steps) if headline else None
+
+        # per-stage pass: every stage of the step is captured in a CUDA graph of its own and
+        # replayed K times between two CUDA events (no host launch gaps inside the figure);
+        # with --no-graph the stages are launched eagerly instead
+        keep = []
+
+        def stage(name, fn):
+            with torch.no_grad():
+                r = fn()                                   # eager: produces the next stage's inputs
+                if args.no_graph:
+                    run = fn
+                else:
+                    g, _ = capture(fn)
+                    keep.append(g)
+                    run = g.replay
+                kernel_ms[name] = timed(ctx, run, steps) / steps
+            return r
+
+        sync_all(ctx)
+        plan = ctx.gemm_plan
+        if OPMX.moe_route_select(x_dev, blk.gate.weight, E, k) is not None:
+            _, xe, ew, inv, off = stage("route_select", lambda: OPMX.moe_route_select(x_dev, blk.gate.weight, E, k))
+        else:
+            logits = stage("gate", lambda: OPMX.router_gate(x_dev, blk.gate.weight))
+            xe, ew, inv, off = stage("select", lambda: OPMX.moe_select(x_dev, logits, E, k))
+        h = stage("gate_up", lambda: moe_grouped_linear(xe.view(-1, shape.H), off, blk.wu.weight, None,
+                                                        swiglu=True, zero_outside=False, plan=plan))
+        y = stage("down", lambda: moe_grouped_linear(h, off, blk.w2.weight, None, zero_outside=False, plan=plan))
+        if use_peer:
+            stage("reduce_allreduce", lambda: blk._peer.combine_allreduce(y, ew, inv, k))
+        else:
+            o = stage("reduce", lambda: OPMX.moe_reduce(y.view(shape.T, k, -1), ew, inv, k))
+            if ctx.world > 1:
+                stage("allreduce", lambda: dist.all_reduce(o, group=ctx.group))
+        if headline:
+            # the normalisation in front of the block (not part of the step): x + skip -> RMSNorm
+            norm_w = torch.ones(shape.H, device=ctx.device, dtype=dt)
+            skip_dev = torch.randn_like(x_dev)
+            stage("skip_rms_norm", lambda: OPMX.skip_rms_norm(x_dev, norm_w, skip_dev, -1, 1e-5))
+            if OPMX.moe_norm_route_select(x_dev, skip_dev, norm_w, 1e-5, blk.gate.weight, E, k) is not None:
+                stage("norm_route_select",
+                      lambda: OPMX.moe_norm_route_select(x_dev, skip_dev, norm_w, 1e-5, blk.gate.weight, E, k))
+        sync_all(ctx)
+        for g in keep:
+            g.reset()
+        del keep
+    active = int((off[1:] - off[:-1]).gt(0).sum().item())
+    # phase boundaries inside the fused combine + all-reduce (one extra call with stamps on)
+    ar_phases = None
+    if use_peer:
+        try:
+            blk._peer.flags = _cabi.ALLREDUCE_FLAG_STAMPS
+            for _ in range(3):
+                step()
+            ar_phases = blk._peer.phases_ns()
+        except Exception:                                 # noqa: BLE001  (diagnostic only)
+            ar_phases = None
+        finally:
+            blk._peer.flags = 0
+    sync_all(ctx)
+    out = run_step()
+    torch.cuda.synchronize()
+    blk.check()
+    parity = parity_check(ctx, shape, blk, x_dev, out)
+    sync_all(ctx)
+    if graph is not None:
+        graph.reset()
+        del graph
+    if ctx.rank != 0:
+        return None
+
+    peaks = ctx.peaks
+    work = W.algorithmic_work(shape, ctx.world, active)
+    ms_med = statistics.median(region_ms)
+    ms_step = ms_med / steps
+    clocks = sampler.summary()
+    # tensor peak: the burst figure when the timed region ran at (nearly) full SM clock,
+    # the sustained one when the power cap had pulled the clock down
+    burst = bool(clocks["sm_mhz"] and clocks["sm_max_mhz"] and clocks["sm_mhz"] >= 0.9 * clocks["sm_max_mhz"])
+    tensor_peak = peaks["bf16_tflops"] if burst else peaks["bf16_tflops_sustained"]
+    ridge = tensor_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)
+
+    def roofline_of(stage_name, bytes_key, flops_key):
+        t = kernel_ms[stage_name] * 1e-3
+        if t <= 0:
+            return None
+        if work[flops_key] / work[bytes_key] < ridge:
+            a = work[bytes_key] / t / 1e9
+            return {"bound": "hbm", "achieved": a, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": a / peaks["hbm_gbs"]}
+        a = work[flops_key] / t / 1e12
+        return {"bound": "tensor", "achieved": a, "peak": tensor_peak, "unit": "TFLOP/s", "frac": a / tensor_peak,
+                "peak_kind": "burst" if burst else "sustained"}
+
+    roof = roofline_of("gate_up", "bytes_gate_up", "flops_gate_up")
+    ratio = TRAFFIC_RATIO.get(roof["bound"])
+    # DRAM traffic of the launch = algorithmic bytes x the ratio ncu measured on a
+    # reduced-ffn case of the same kernel (profiles/grouped_gemm_tc_*.md); traffic is
+    # >99 % weights and scales with the ffn size
+    roof.update({"traffic": work["bytes_gate_up"] * ratio if ratio else None,
+                 "kernel": "gate/up grouped GEMM with SwiGLU epilogue (grouped_gemm_tc_kernel; "
+                           "grouped_gemm_tc_pair_kernel for >= 1024 rows per expert)",
+                 "kernel_ms": kernel_ms["gate_up"], "peak_source": peaks["source"],
+                 "algorithmic_bytes": work["bytes_gate_up"], "algorithmic_flops": work["flops_gate_up"],
+                 "timing": "CUDA events around K back-to-back replays of a CUDA graph holding this launch alone, same run"})
+    down = roofline_of("down", "bytes_down", "flops_down")
+    layer_floor_s = max(work["bytes"] / (peaks["hbm_gbs"] * 1e9), work["flops"] / (tensor_peak * 1e12))
+    rec = {
+        "workload": shape.name, "dtype": shape.dtype, "config": workload_config(shape, ctx.world),
+        "steps": steps, "ms_per_step": ms_step, "tokens_per_s": shape.T / (ms_step * 1e-3),
+        "repeats": {"regions": regions, "steps_per_region": steps, "ms_per_step_median": ms_step,
+                    "ms_per_step_min": min(region_ms) / steps, "ms_per_step_max": max(region_ms) / steps},
+        "gpu_launches_per_step": int(launches_per_step),
+        "clocks": clocks, "roofline": roof,
+        "roofline_down": {k2: down[k2] for k2 in ("bound", "achieved", "unit", "frac")} if down else None,
+        "layer": {"ms_floor": layer_floor_s * 1e3, "frac_of_roofline": layer_floor_s * 1e3 / ms_step,
+                  "active_experts": active, "graph": not args.no_graph,
+                  "allreduce": ((f"peer-memory kernel fused with the combine ({args.peer_algo})" if use_peer else "nccl")
+                                if ctx.world > 1 else None),
+                  "allreduce_phases_ns": ar_phases,
+                  "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items() if n in STAGES and v > 0}},
+        "parity": parity,
+    }
+    if headline:
+        rec["e2e_ms_total"] = ms_e2e
+        rec["h2d"] = x_host.numel() * x_host.element_size()
+        rec["d2h"] = out_host.numel() * out_host.element_size()
+        rec["layer"]["front_end"] = {
+            "skip_rms_norm_ms": round(kernel_ms["skip_rms_norm"], 5),
+            "norm_route_select_ms": round(kernel_ms["norm_route_select"], 5) or None,
+            "gbs": (4 * x_host.numel() * x_host.element_size() / (kernel_ms["skip_rms_norm"] * 1e-3) / 1e9
+                    if kernel_ms["skip_rms_norm"] > 0 else None)}
+    return rec
+
+
+def parse_plan(text):
+    from ppl.pmx_b200._cabi import GemmPlan
+    if not text:
+        return None
+    return GemmPlan(**{k: int(v) for k, v in (item.split("=") for item in text.split(","))})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_t64")
+    ap.add_argument("--workload", default=HEADLINE, help="the workload of the headline figures")
+    ap.add_argument("--extra", default=None,
+                    help="comma-separated workloads reported in the `workloads` array ('' for none; default: all "
+                         "the other configurations when the headline is the default one)")
+    ap.add_argument("--regions", type=int, default=5, help="timed regions of K steps per workload (median reported)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true", help="ordinary launches instead of programmatic dependent launch")
     ap.add_argument("--allreduce", default="auto", choices=["auto", "peer", "nccl"],
                     help="N > 1: fused combine + all-reduce kernel over NVLink peer memory, or moe_reduce + NCCL "
                          "(auto: peer when the [T,H] result is at most 4 MB)")
+    ap.add_argument("--peer-algo", default="auto", choices=["auto", "push", "pull"])
+    ap.add_argument("--gemm-plan", default="", help="pmx_gemm_plan fields for the gate_up / down STAGE timings, "
+                                                    "e.g. balance=2,cta_cap=128 (the step itself uses the default plan)")
     ap.add_argument("--ffn-div", type=int, default=1,
                     help="divide the ffn size by this (small cases for profiler captures; traffic and flops scale with it)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     from ppl.pmx_b200 import workloads as W
-    shape = W.WORKLOADS[args.workload]
-    if args.ffn_div != 1:
-        shape = W.scaled(shape, I=shape.I // args.ffn_div, name=f"{shape.name}_ffn_div{args.ffn_div}")
+
+    def shape_of(name):
+        sh = W.WORKLOADS[name]
+        if args.ffn_div != 1:
+            sh = W.scaled(sh, I=sh.I // args.ffn_div, name=f"{sh.name}_ffn_div{args.ffn_div}")
+        return sh
+
+    shape = shape_of(args.workload)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -201,251 +625,78 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
     torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    group = None
+    ctx = Ctx()
+    ctx.args, ctx.world, ctx.rank, ctx.local_rank = args, world, rank, local_rank
+    ctx.device = torch.device("cuda", local_rank)
+    ctx.group, ctx.blocks, ctx.peer_failed, ctx.peaks = None, {}, False, load_peaks()
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-        group = dist.new_group(list(range(world)))
-
-    import ppl.pmx_b200.torch_function as OPMX
+        dist.init_process_group("nccl", device_id=ctx.device)
+        ctx.group = dist.new_group(list(range(world)))
     from ppl.pmx_b200 import _cabi
-    from ppl.pmx_b200.moe_layers import MoeFeedForward
-    from ppl.pmx_b200.torch_function.moe import moe_grouped_linear
+    if args.no_pdl:
+        _cabi.lib.pmx_moe_set_programmatic_launch(0)
+    ctx.gemm_plan = parse_plan(args.gemm_plan)
 
-    dt = W.TORCH_DTYPE[shape.dtype]
-    x_host, w_router, _, _ = W.make_activations(shape, detie=False)
-    x_host = x_host.pin_memory()
-    out_host = torch.empty(shape.T, shape.H, dtype=dt).pin_memory()
-    result_bytes = shape.T * shape.H * torch.empty((), dtype=dt).element_size()
-    use_peer = world > 1 and (args.allreduce == "peer" or (args.allreduce == "auto" and result_bytes <= (4 << 20)))
-    blk = MoeFeedForward(shape.H, shape.I, shape.E, shape.k, group, False,
-                         peer_reduce_tokens=shape.T if use_peer else 0).to(device, dt)
-    wu, w2 = W.make_expert_weights(shape, device, tp_rank=rank, tp_size=world)
-    with torch.no_grad():
-        blk.gate.weight.copy_(w_router)
-        blk.wu.weight.copy_(wu)
-        blk.w2.weight.copy_(w2)
-    del wu, w2
-    x_dev = x_host.to(device)
-    E, k = shape.E, shape.k
-
-    def step():
-        with torch.no_grad():
-            return blk(x_dev)
-
-    if use_peer:
-        # the peer-memory exchange needs the ranks' buffers mapped into each other
-        # (symmetric memory); if this machine refuses, say so and use NCCL
+    head = measure(ctx, shape, args.steps, args.warmup, args.regions, headline=True)
+    extra_names = (EXTRA_WORKLOADS if args.workload == HEADLINE else []) if args.extra is None else \
+        [n for n in args.extra.split(",") if n]
+    extras = []
+    for name in extra_names:
+        sh = shape_of(name)
+        # fewer steps for the long steps (prefill: ~4.5 ms each), at least 10
+        k_steps = max(10, min(args.steps, int(200 / max(1.0, 0.002 * sh.T))))
         try:
-            step()
-            torch.cuda.synchronize()
-            ok = torch.ones(1, device=device)
+            rec = measure(ctx, sh, k_steps, max(3, min(args.warmup, 5)), args.regions, headline=False)
         except Exception as exc:                      # noqa: BLE001
-            print(f"[bench] rank {rank}: peer-memory all-reduce unavailable ({exc}); using NCCL", file=sys.stderr)
-            ok = torch.zeros(1, device=device)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
-        if ok.item() == 0:
-            use_peer = False
-            blk.peer_reduce_tokens = 0
-            blk._peer = None
-
-    def sync_all():
-        if world > 1:
-            dist.barrier(group=group)
-        torch.cuda.synchronize()
-
-    # warm-up (eager), then capture one step
-    for _ in range(args.warmup):
-        out = step()
-    torch.cuda.synchronize()
-    launches_before = _cabi.lib.pmx_moe_kernel_launches()
-    out = step()
-    torch.cuda.synchronize()
-    launches_per_step = _cabi.lib.pmx_moe_kernel_launches() - launches_before
-    graph = None
-    if not args.no_graph:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            out = step()
-        torch.cuda.current_stream().wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            out = step()
-        for _ in range(3):
-            graph.replay()
-        torch.cuda.synchronize()
-
-    def run_step():
-        if graph is not None:
-            graph.replay()
-            return out
-        return step()
-
-    def timed(fn, steps):
-        sync_all()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        sync_all()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=device)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX, group=group)
-        return float(ms.item())
-
-    def e2e_step():
-        x_dev.copy_(x_host, non_blocking=True)
-        o = run_step()
-        out_host.copy_(o, non_blocking=True)
-
-    sampler = ClockSampler(physical_gpu_index(local_rank))
-    with sampler:
-        ms_total = timed(run_step, args.steps)
-        ms_e2e = timed(e2e_step, args.steps)
-
-        # per-stage pass: every stage of the step is captured in a CUDA graph of its own and
-        # replayed K times between two CUDA events (no host launch gaps inside the figure);
-        # with --no-graph the stages are launched eagerly instead
-        names = ["gate", "select", "route_select", "gate_up", "down", "reduce", "allreduce", "reduce_allreduce",
-                 "skip_rms_norm", "norm_route_select"]
-        kernel_ms = {n: 0.0 for n in names}
-        keep = []
-
-        def stage(name, fn):
-            with torch.no_grad():
-                r = fn()                                   # eager: produces the next stage's inputs
-                if args.no_graph:
-                    run = fn
-                else:
-                    side = torch.cuda.Stream()
-                    side.wait_stream(torch.cuda.current_stream())
-                    with torch.cuda.stream(side):
-                        fn()
-                    torch.cuda.current_stream().wait_stream(side)
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g):
-                        fn()
-                    keep.append(g)
-                    run = g.replay
-                kernel_ms[name] = timed(run, args.steps) / args.steps
-            return r
-
-        sync_all()
-        if OPMX.moe_route_select(x_dev, blk.gate.weight, E, k) is not None:
-            _, xe, ew, inv, off = stage("route_select", lambda: OPMX.moe_route_select(x_dev, blk.gate.weight, E, k))
-        else:
-            logits = stage("gate", lambda: torch.nn.functional.linear(x_dev, blk.gate.weight))
-            xe, ew, inv, off = stage("select", lambda: OPMX.moe_select(x_dev, logits, E, k))
-        h = stage("gate_up", lambda: moe_grouped_linear(xe.view(-1, shape.H), off, blk.wu.weight, None,
-                                                        swiglu=True, zero_outside=False))
-        y = stage("down", lambda: moe_grouped_linear(h, off, blk.w2.weight, None, zero_outside=False))
-        if use_peer:
-            stage("reduce_allreduce", lambda: blk._peer.combine_allreduce(y, ew, inv, k))
-        else:
-            o = stage("reduce", lambda: OPMX.moe_reduce(y.view(shape.T, k, -1), ew, inv, k))
+            rec = {"workload": sh.name, "error": f"{type(exc).__name__}: {exc}"}
             if world > 1:
-                stage("allreduce", lambda: dist.all_reduce(o, group=group))
-        # the normalisation in front of the block (not part of the step): x + skip -> RMSNorm
-        norm_w = torch.ones(shape.H, device=device, dtype=dt)
-        skip_dev = torch.randn_like(x_dev)
-        stage("skip_rms_norm", lambda: OPMX.skip_rms_norm(x_dev, norm_w, skip_dev, -1, 1e-5))
-        if OPMX.moe_norm_route_select(x_dev, skip_dev, norm_w, 1e-5, blk.gate.weight, E, k) is not None:
-            stage("norm_route_select",
-                  lambda: OPMX.moe_norm_route_select(x_dev, skip_dev, norm_w, 1e-5, blk.gate.weight, E, k))
-        sync_all()
-        for g in keep:
-            g.reset()
-        del keep
-    active = int((off[1:] - off[:-1]).gt(0).sum().item())
-    # phase boundaries of the last fused combine + all-reduce call (CTA 0 of this rank), from
-    # the %globaltimer stamps the kernel leaves in its control block (byte 512, 8 x u64)
-    ar_phases = None
-    if use_peer and getattr(blk, "_peer", None) is not None:
-        try:
-            import struct
-            st = struct.unpack("8Q", bytes(blk._peer.buffer[512:576].cpu().tolist()))
-            ar_phases = {"combine_done": st[1] - st[0], "epoch_published": st[2] - st[0],
-                         "peers_seen": st[3] - st[0], "sum_done": st[4] - st[0]}
-        except Exception:                                 # noqa: BLE001  (diagnostic only)
-            ar_phases = None
+                raise
+        if rank == 0:
+            extras.append(rec)
 
     if rank == 0:
-        peaks = load_peaks()
-        work = W.algorithmic_work(shape, world, active)
-        ms_step = ms_total / args.steps
-        value = shape.T / (ms_step * 1e-3)
-        e2e_value = shape.T / (ms_e2e / args.steps * 1e-3)
-        # dominant kernel: the gate/up grouped GEMM
-        t_gu = kernel_ms["gate_up"] * 1e-3
-        ai = work["flops_gate_up"] / work["bytes_gate_up"]
-        clocks = sampler.summary()
-        # tensor peak: the burst figure when the timed region ran at (nearly) full SM clock,
-        # the sustained one when the power cap had pulled the clock down
-        burst = bool(clocks["sm_mhz"] and clocks["sm_max_mhz"] and clocks["sm_mhz"] >= 0.9 * clocks["sm_max_mhz"])
-        tensor_peak = peaks["bf16_tflops"] if burst else peaks["bf16_tflops_sustained"]
-        tensor_peak_kind = "burst" if burst else "sustained"
-        ridge = tensor_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)
-        if ai < ridge:
-            achieved = work["bytes_gate_up"] / t_gu / 1e9
-            roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / peaks["hbm_gbs"]}
-        else:
-            achieved = work["flops_gate_up"] / t_gu / 1e12
-            roof = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak,
-                    "unit": "TFLOP/s", "frac": achieved / tensor_peak, "peak_kind": tensor_peak_kind}
-        # DRAM traffic of the launch = algorithmic bytes x the ratio ncu measured on a
-        # reduced-ffn case of the same kernel (profiles/grouped_gemm_tc_*.md); traffic is
-        # >99 % weights and scales with the ffn size
-        ratio = TRAFFIC_RATIO.get(roof["bound"])
-        roof.update({"traffic": work["bytes_gate_up"] * ratio if ratio else None, "kernel": "gate/up grouped GEMM with SwiGLU epilogue (grouped_gemm_tc_kernel; grouped_gemm_tc_pair_kernel for >= 1024 rows per expert)",
-                     "kernel_ms": kernel_ms["gate_up"], "peak_source": peaks["source"],
-                     "algorithmic_bytes": work["bytes_gate_up"], "algorithmic_flops": work["flops_gate_up"],
-                     "timing": "CUDA events around K back-to-back replays of a CUDA graph holding this launch alone, same run"})
-        # whole-layer figures against the layer's own roofline
-        layer_floor_s = max(work["bytes"] / (peaks["hbm_gbs"] * 1e9), work["flops"] / (tensor_peak * 1e12))
+        ms_step = head["ms_per_step"]
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": METRIC, "value": head["tokens_per_s"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": shape.dtype, "data": "synthetic",
-            "config": workload_config(shape, world, "B200"),
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * x_host.element_size(),
-                    "d2h_bytes_per_step": out_host.numel() * out_host.element_size()},
-            "gpu_launches": int(launches_per_step) * args.steps,
-            "clocks": clocks,
-            "roofline": roof,
-            "layer": {"ms_floor": layer_floor_s * 1e3, "frac_of_roofline": layer_floor_s * 1e3 / ms_step,
-                      "active_experts": active, "graph": graph is not None,
-                      "allreduce": ("peer-memory kernel fused with the combine" if use_peer else "nccl") if world > 1 else None,
-                      "allreduce_phases_ns": ar_phases,
-                      "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items()
-                                    if n not in ("skip_rms_norm", "norm_route_select")},
-                      "front_end": {"skip_rms_norm_ms": round(kernel_ms["skip_rms_norm"], 5),
-                                    "norm_route_select_ms": round(kernel_ms["norm_route_select"], 5) or None,
-                                    "gbs": 4 * x_host.numel() * x_host.element_size() / (kernel_ms["skip_rms_norm"] * 1e-3) / 1e9}},
+            "config": head["config"],
+            "repeats": head["repeats"],
+            "e2e": {"value": shape.T / (head["e2e_ms_total"] / args.steps * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": head["h2d"], "d2h_bytes_per_step": head["d2h"]},
+            "gpu_launches": head["gpu_launches_per_step"] * args.steps,
+            "programmatic_dependent_launch": not args.no_pdl,
+            "clocks": head["clocks"],
+            "roofline": head["roofline"],
+            "roofline_down": head["roofline_down"],
+            "layer": head["layer"],
+            "parity": head["parity"],
+            "workloads": extras,
         }
         if world == 1 and not args.no_cpu_baseline:
+            blk = get_block(ctx, shape, full=False)
+            x_host, w_router, _, _ = W.make_activations(shape, detie=False)
             wu_c, w2_c = blk.wu.weight.detach().cpu(), blk.w2.weight.detach().cpu()
+            arm = CpuArm(shape)
             tokens = min(shape.T, 1024)
-            times = time_cpu(shape, x_host, w_router, wu_c, w2_c, tokens, 20, 1, budget_s=15.0)
-            line["cpu_baseline"] = {
-                "value": tokens * len(times) / sum(times), "unit": UNIT, "cores": torch.get_num_threads(),
-                "kind": "port",
-                "sample": f"first {tokens} of {shape.T} tokens, full expert weights, {len(times)} passes after 1 warm-up"}
+            times = arm.time(x_host, w_router, wu_c, w2_c, tokens, 20, 1, budget_s=15.0)
+            line["cpu_baseline"] = {"value": tokens * len(times) / sum(times), "unit": UNIT, "cores": arm.cores,
+                                    "kind": arm.kind, "sample": arm.describe(tokens, len(times))}
         print(json.dumps(line), flush=True)
     # Tear-down.  A CUDA graph that captured NCCL kernels must be gone before the
-    # communicator is destroyed; a watchdog ends the process if the tear-down
-    # itself stalls (the result line is already out).
+    # communicator is destroyed; a watchdog ends the process with an error if the
+    # tear-down itself stalls (the result line is already out).
     sys.stdout.flush()
     if world > 1:
-        watchdog = threading.Timer(30.0, lambda: os._exit(0))
+        def stalled():
+            sys.stderr.write("[bench] tear-down of the process group stalled for 60 s; exiting with status 3\n")
+            sys.stderr.flush()
+            os._exit(3)
+        watchdog = threading.Timer(60.0, stalled)
         watchdog.daemon = True
         watchdog.start()
-        sync_all()
-        if graph is not None:
-            graph.reset()
-            del graph
+        sync_all(ctx)
+        ctx.blocks.clear()
         torch.cuda.synchronize()
         dist.destroy_process_group()
         watchdog.cancel()

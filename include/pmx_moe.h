@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define PMX_MOE_ABI_VERSION 1
+#define PMX_MOE_ABI_VERSION 2
 
 /* element type of activations and weights */
 typedef enum pmx_dtype {
@@ -71,7 +71,14 @@ typedef struct pmx_gemm_plan {
   int32_t stages;       /* shared-memory pipeline depth */
   int32_t max_ctas;     /* cap on the persistent grid (0 = number of SMs) */
   int32_t stream_k;     /* 0 = choose, 1 = deal k-blocks evenly over the CTAs (partial tiles
-                           are exchanged through the workspace), 2 = whole tiles per CTA */
+                           are exchanged through the workspace; needs the SMs to itself, see
+                           pmx_moe_grouped_linear), 2 = whole tiles per CTA */
+  int32_t cta_cap;      /* at most this many CTAs of the grid take work items (0 = choose) */
+  int32_t full_rounds;  /* 0 = choose, 1 = shrink the working grid on the device so that every
+                           round of tiles is full, 2 = every CTA up to cta_cap strides over the tiles */
+  int32_t balance;      /* PMX_GEMM_TC_WEIGHTS_M only: 0 = choose, 1 = deal the feature rows evenly
+                           over the CTAs in units of 8 rows (every SM streams the same number of
+                           weight bytes), 2 = whole 128-row tiles */
 } pmx_gemm_plan;
 
 int pmx_moe_abi_version(void);
@@ -80,6 +87,13 @@ const char* pmx_moe_status_string(int status);
 /* Number of kernels this library has launched (or recorded into a CUDA graph
  * under capture) in this process so far; for benchmark accounting. */
 long long pmx_moe_kernel_launches(void);
+/* Programmatic dependent launch: by default the kernels of this library are
+ * launched with programmatic stream serialisation, so that a kernel's set-up (and,
+ * for the expert GEMMs, its first weight tiles) overlaps the tail of the kernel in
+ * front of it on the stream; every kernel waits for its predecessors before it reads
+ * their results or writes anything.  on = 0 switches to ordinary launches for the
+ * whole process.  Returns the previous setting. */
+int pmx_moe_set_programmatic_launch(int on);
 
 /*
  * moe_select -- replaces MoeSelect.forward, torch_function/MoeSelect.py:36-64.
@@ -108,8 +122,14 @@ int pmx_moe_select(const void* x, const void* scores, void* x_expand_permute,
  *   from exactly those scores.
  * Covers 1 <= T <= 1024, E <= 64, k <= 32, H*sizeof(T1) a multiple of 16;
  * pmx_moe_route_select_workspace_bytes returns 0 for other shapes (use a linear
- * and pmx_moe_select then).  The launch is cooperative (its blocks meet at one
- * bounded grid-wide barrier).
+ * and pmx_moe_select then).  The blocks of the launch (at most one per SM) meet at
+ * one grid-wide barrier whose two counter words are the first 8 bytes of the
+ * workspace: the first 64 bytes of the workspace must be ZERO before the first call
+ * that uses it; every call that completes leaves them zero again, so a workspace can
+ * be kept and reused without clearing (calls that share a workspace must not overlap
+ * on the GPU).  The barrier wait is bounded (1 s); if it runs out the outputs are
+ * undefined, pmx_moe_route_select_check reports it and the caller clears the first
+ * 64 bytes before the next call.
  */
 size_t pmx_moe_route_select_workspace_bytes(int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype);
 int pmx_moe_route_select(const void* x, const void* w_router, void* scores,
@@ -127,9 +147,12 @@ int pmx_moe_route_select(const void* x, const void* w_router, void* scores,
  *   n = T1(float(s) * rsqrt(mean(s^2) + eps)) * norm_weight      (kept on chip)
  *   scores = n . w_router^T, then the four outputs of pmx_moe_select for (n, scores);
  *   x_expand_permute holds rows of n.
- * Same shape limits as pmx_moe_route_select, and additionally the normalised rows of a
+ * Same shape limits and workspace contract as pmx_moe_route_select, and additionally the normalised rows of a
  * block's tokens must fit in shared memory (workspace_bytes() returns 0 otherwise).
  */
+/* Synchronises `stream`; PMX_ERR_DEVICE_CHECK if the grid barrier of a
+ * pmx_moe_route_select / pmx_moe_norm_route_select call on this workspace gave up. */
+int pmx_moe_route_select_check(const void* workspace, void* stream);
 size_t pmx_moe_norm_route_select_workspace_bytes(int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype);
 int pmx_moe_norm_route_select(const void* x, const void* skip, const void* norm_weight, float eps,
                               const void* w_router, void* skip_out, void* scores,
@@ -154,9 +177,11 @@ int pmx_moe_norm_route_select(const void* x, const void* skip, const void* norm_
  *     PMX_MOE_SELECT_STATIC_SCRATCH_BYTES (1 MiB: e.g. T*k up to 131072 slots
  *     with 8 experts); larger problems get PMX_ERR_WORKSPACE and a message
  *     naming the size, and should use pmx_moe_select.
- *   - The first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress, with the caller's device current) and caches it;
- *     make that first call before starting any stream capture.
+ *   - Every call looks up the array's device address for the current device
+ *     (cudaGetSymbolAddress, a host-side lookup).  The very first use of the
+ *     library on a device may make the CUDA runtime load the library's device
+ *     image (which holds the array); make that first call before starting any
+ *     stream capture.
  *   - All calls on a device share the one array and it keeps whatever the last
  *     call left there.  Nothing in it needs clearing between calls (every byte
  *     a call reads it has written itself first), but two calls whose kernels
@@ -179,6 +204,11 @@ int pmx_moe_select_static(const void* x, const void* scores,
  *   y [M,N] T1, or [M,N/2] T1 with PMX_EPILOGUE_SWIGLU (SwiGLU.forward,
  *   torch_function/SwiGLU.py:15-16, applied to the accumulator: rows [0,N/2) of
  *   w[e] are the gate projection, rows [N/2,N) the up projection).
+ * With E == 1, expert_offset may be NULL: the one "expert" then owns all M rows,
+ * which makes the call a dense linear y = x . w^T (+ bias) -- Linear.forward
+ * (torch_function/Linear.py:24-33), and the local product of
+ * ColumnParallelLinear.forward / RowParallelLinear.forward
+ * (torch_function/ColumnParallelLinear.py:43, RowParallelLinear.py:41).
  * zero_outside != 0 also writes zeros to rows outside [expert_offset[0],
  * expert_offset[E]) as the reference's zero-initialised output has them.
  * Collectives (all-reduce / all-gather of the reference ops) stay with the caller.
@@ -228,6 +258,15 @@ int pmx_moe_reduce(const void* y, const void* expert_weights,
                    const int64_t* invert_permutation, void* out, int64_t T,
                    int32_t k, int64_t N, int32_t dtype, void* stream);
 
+/* how pmx_moe_reduce_allreduce moves the partial results between the ranks */
+typedef enum pmx_allreduce_algorithm {
+  PMX_ALLREDUCE_AUTO = 0,
+  PMX_ALLREDUCE_PULL = 1, /* one hop: every rank publishes a per-CTA flag and reads all peers' buffers */
+  PMX_ALLREDUCE_PUSH = 2  /* two hops (reduce at an owner rank, then broadcast) of 8-byte words that
+                             carry their own flag; no fence, no separate flag (the default) */
+} pmx_allreduce_algorithm;
+#define PMX_ALLREDUCE_FLAG_STAMPS 1 /* CTA 0 records %globaltimer at its phase boundaries */
+
 /*
  * moe_reduce fused with the tensor-parallel all-reduce over NVLink peer memory:
  *   out[t,:] = sum over ranks r of  sum_j expert_weights[t,j] * y_r[invert_permutation[t,j],:]
@@ -237,23 +276,45 @@ int pmx_moe_reduce(const void* y, const void* expert_weights,
  * after the weighted combine (same sum, another order; [T,N] crosses NVLink
  * instead of [T*k,N]).  Every rank of the group calls it once per step with its
  * own partial y_r; all ranks must pass identical expert_weights and
- * invert_permutation (the routing is replicated).
+ * invert_permutation (the routing is replicated), the same T, algorithm and
+ * buffer_bytes.  All ranks receive bit-identical results.
  *   peer_buffers: host array of `world` device pointers, entry r = rank r's
- *   exchange buffer of pmx_moe_reduce_allreduce_buffer_bytes(T_max,N,dtype)
+ *   exchange buffer of buffer_bytes >= pmx_moe_reduce_allreduce_buffer_bytes(T_max,N,dtype)
  *   bytes, mapped into this process (CUDA IPC / symmetric memory), zeroed once
- *   before the first call and followed by a barrier of the group.  All ranks
- *   use the same T_max and N for the size.
- * One-shot exchange (each rank reads world-1 buffers): meant for decode-size
- * messages; use NCCL above a few MB.  Waits on peers are bounded (1 s);
- * pmx_moe_reduce_allreduce_check reads the record a failed wait left behind.
+ *   before the first call and followed by a barrier of the group.  buffer_bytes
+ *   (not T) fixes the layout inside the buffer, so calls with different T <= T_max
+ *   may follow each other on the same buffers.
+ * Meant for decode-size messages; use NCCL above a few MB.  Waits on peers are
+ * bounded by wait_limit_ns (<= 0: one second).  A wait that runs out leaves zeros
+ * in the rows it covered and a record that pmx_moe_reduce_allreduce_check reports
+ * (and clears); the exchange buffers of all ranks must be zeroed again (and the
+ * group synchronised) before the next call.  Call the check at step boundaries.
  */
 size_t pmx_moe_reduce_allreduce_buffer_bytes(int64_t T, int64_t N, int32_t dtype);
 int pmx_moe_reduce_allreduce(const void* y, const void* expert_weights,
                              const int64_t* invert_permutation, void* out,
                              int64_t T, int32_t k, int64_t N, int32_t dtype,
                              void* const* peer_buffers, int32_t rank,
-                             int32_t world, size_t buffer_bytes, void* stream);
-int pmx_moe_reduce_allreduce_check(const void* my_buffer, int32_t out[4], void* stream);
+                             int32_t world, size_t buffer_bytes, int32_t algorithm,
+                             int32_t flags, int64_t wait_limit_ns, void* stream);
+/* Synchronises `stream`; returns PMX_ERR_DEVICE_CHECK (out = code, peer, epoch, CTA)
+ * if a wait ran out since the last check, and clears the record. */
+int pmx_moe_reduce_allreduce_check(void* my_buffer, int32_t out[4], void* stream);
+/* %globaltimer values CTA 0 recorded in the last call made with PMX_ALLREDUCE_FLAG_STAMPS:
+ * out[0] start; PUSH: [1] partials sent, [2] owned sums published, [3] all sums received;
+ * PULL: [1] combined, [2] flag published, [3] peers seen, [4] summed.  Synchronises `stream`. */
+int pmx_moe_reduce_allreduce_phases(const void* my_buffer, uint64_t out[8], void* stream);
+/*
+ * The same exchange with all `world` ranks played by ONE cooperative launch on ONE
+ * GPU (rank = blockIdx.y), for testing the protocol where only one device is
+ * available: y, expert_weights, invert_permutation, out and buffers are host arrays
+ * of `world` device pointers, all on the current device.
+ */
+int pmx_moe_reduce_allreduce_emulated(const void* const* y, const void* const* expert_weights,
+                                      const int64_t* const* invert_permutation, void* const* out,
+                                      int64_t T, int32_t k, int64_t N, int32_t dtype,
+                                      void* const* buffers, int32_t world, size_t buffer_bytes,
+                                      int32_t algorithm, int64_t wait_limit_ns, void* stream);
 
 #ifdef __cplusplus
 }

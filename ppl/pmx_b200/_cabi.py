@@ -15,6 +15,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libpmx_moe_b200.so")
 
 DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+ABI_VERSION = 2
 EPILOGUE_NONE, EPILOGUE_SWIGLU = 0, 1
 GEMM_AUTO, GEMM_TC_TOKENS_M, GEMM_TC_WEIGHTS_M, GEMM_SIMT, GEMM_TC_TOKENS_M_PAIRED = 0, 1, 2, 3, 4
 
@@ -22,7 +23,8 @@ GEMM_AUTO, GEMM_TC_TOKENS_M, GEMM_TC_WEIGHTS_M, GEMM_SIMT, GEMM_TC_TOKENS_M_PAIR
 class GemmPlan(C.Structure):
     """Mirror of pmx_gemm_plan."""
     _fields_ = [("kernel", C.c_int32), ("tile_feat", C.c_int32), ("tile_tok", C.c_int32),
-                ("split_k", C.c_int32), ("stages", C.c_int32), ("max_ctas", C.c_int32), ("stream_k", C.c_int32)]
+                ("split_k", C.c_int32), ("stages", C.c_int32), ("max_ctas", C.c_int32), ("stream_k", C.c_int32),
+                ("cta_cap", C.c_int32), ("full_rounds", C.c_int32), ("balance", C.c_int32)]
 
 
 class PmxError(RuntimeError):
@@ -48,6 +50,8 @@ def _load() -> C.CDLL:
         "pmx_moe_select": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, vp, sz, vp]),
         "pmx_moe_route_select_workspace_bytes": (sz, [i64, i64, i32, i32, i32]),
         "pmx_moe_route_select": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, vp, sz, vp]),
+        "pmx_moe_route_select_check": (C.c_int, [vp, vp]),
+        "pmx_moe_set_programmatic_launch": (C.c_int, [C.c_int]),
         "pmx_moe_norm_route_select_workspace_bytes": (sz, [i64, i64, i32, i32, i32]),
         "pmx_moe_norm_route_select": (C.c_int, [vp, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32,
                                                 vp, sz, vp]),
@@ -61,13 +65,17 @@ def _load() -> C.CDLL:
         "pmx_skip_rms_norm": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, f32, i32, vp]),
         "pmx_moe_reduce": (C.c_int, [vp, vp, vp, vp, i64, i32, i64, i32, vp]),
         "pmx_moe_reduce_allreduce_buffer_bytes": (sz, [i64, i64, i32]),
-        "pmx_moe_reduce_allreduce": (C.c_int, [vp, vp, vp, vp, i64, i32, i64, i32, C.POINTER(vp), i32, i32, sz, vp]),
+        "pmx_moe_reduce_allreduce": (C.c_int, [vp, vp, vp, vp, i64, i32, i64, i32, C.POINTER(vp), i32, i32, sz,
+                                               i32, i32, i64, vp]),
         "pmx_moe_reduce_allreduce_check": (C.c_int, [vp, C.POINTER(i32 * 4), vp]),
+        "pmx_moe_reduce_allreduce_phases": (C.c_int, [vp, C.POINTER(C.c_uint64 * 8), vp]),
+        "pmx_moe_reduce_allreduce_emulated": (C.c_int, [C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), i64, i32,
+                                                        i64, i32, C.POINTER(vp), i32, sz, i32, i64, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = res, args
-    if lib.pmx_moe_abi_version() != 1:
+    if lib.pmx_moe_abi_version() != ABI_VERSION:
         raise ImportError("libpmx_moe_b200.so has an unexpected ABI version; rebuild it")
     return lib
 
@@ -86,6 +94,26 @@ def ptr(t: torch.Tensor | None) -> C.c_void_p:
 
 def stream_of(t: torch.Tensor) -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+ALLREDUCE_AUTO, ALLREDUCE_PULL, ALLREDUCE_PUSH = 0, 1, 2
+ALLREDUCE_FLAG_STAMPS = 1
+
+_barrier_ws: dict = {}
+
+
+def barrier_workspace(nbytes: int, device) -> torch.Tensor:
+    """The workspace of the one-launch router + select kernels: its grid barrier words
+    must be zero before the first call and every completed call leaves them zero, so
+    ONE buffer per device is allocated (zeroed) on first use and kept.  Calls that
+    share it must not overlap on the GPU: callers that drive several streams of one
+    device concurrently pass a workspace of their own to the operators instead."""
+    dev = torch.device(device)
+    t = _barrier_ws.get(dev.index)
+    if t is None or t.numel() < nbytes:
+        t = torch.zeros(max(int(nbytes), 64 + 8 * 1024), dtype=torch.uint8, device=dev)
+        _barrier_ws[dev.index] = t
+    return t
 
 
 def workspace(nbytes: int, device) -> torch.Tensor:

@@ -11,6 +11,23 @@ namespace pmx {
 namespace {
 thread_local char g_error[512] = "";
 std::atomic<long long> g_launches{0};
+std::atomic<int> g_pdl{1};
+}
+
+int launch_pdl(const void* kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, void** args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_pdl.load(std::memory_order_relaxed) ? 1 : 0;
+  PMX_CUDA_OK(cudaLaunchKernelExC(&cfg, kern, args));
+  count_launches(1);
+  return PMX_OK;
 }
 
 void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
@@ -90,6 +107,10 @@ const char* pmx_moe_last_error(void) { return g_error; }
 
 long long pmx_moe_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
+int pmx_moe_set_programmatic_launch(int on) {
+  return g_pdl.exchange(on ? 1 : 0, std::memory_order_relaxed);
+}
+
 const char* pmx_moe_status_string(int status) {
   switch (status) {
     case PMX_OK: return "ok";
@@ -127,6 +148,17 @@ int pmx_moe_route_select(const void* x, const void* w_router, void* scores, void
                              expert_offset, T, H, E, k, dtype, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+int pmx_moe_route_select_check(const void* workspace, void* stream) {
+  if (!workspace) return fail(PMX_ERR_INVALID_ARGUMENT, "route_select_check: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  int words[8] = {0};
+  PMX_CUDA_OK(cudaMemcpyAsync(words, workspace, sizeof(words), cudaMemcpyDeviceToHost, s));
+  PMX_CUDA_OK(cudaStreamSynchronize(s));
+  if (words[4] != 0)
+    return fail(PMX_ERR_DEVICE_CHECK, "route_select: the grid-wide barrier gave up waiting (code %d, %d blocks had arrived)", words[4], words[0]);
+  return PMX_OK;
+}
+
 size_t pmx_moe_norm_route_select_workspace_bytes(int64_t T, int64_t H, int32_t E, int32_t k, int32_t dtype) {
   return norm_route_select_workspace_bytes(T, H, E, k, dtype);
 }
@@ -162,7 +194,10 @@ int pmx_moe_grouped_linear(const void* x, const int64_t* expert_offset, const vo
                            int32_t dtype, int32_t epilogue, float beta, int32_t zero_outside,
                            const pmx_gemm_plan* plan, void* workspace, size_t workspace_bytes,
                            void* stream) {
-  if (!x || !expert_offset || !w || !y) return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear: null pointer");
+  if (!x || !w || !y) return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear: null pointer");
+  if (!expert_offset && E != 1)
+    return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear: expert_offset may be null only for a single expert (E=%d)", E);
+  if (!expert_offset) zero_outside = 0;   // the one expert owns every row
   LinearChoice c;
   int st = choose_linear(M, N, K, E, dtype, epilogue, plan, &c);
   if (st != PMX_OK) return st;
@@ -225,14 +260,28 @@ size_t pmx_moe_reduce_allreduce_buffer_bytes(int64_t T, int64_t N, int32_t dtype
 int pmx_moe_reduce_allreduce(const void* y, const void* expert_weights, const int64_t* invert_permutation,
                              void* out, int64_t T, int32_t k, int64_t N, int32_t dtype,
                              void* const* peer_buffers, int32_t rank, int32_t world,
-                             size_t buffer_bytes, void* stream) {
+                             size_t buffer_bytes, int32_t algorithm, int32_t flags, int64_t wait_limit_ns,
+                             void* stream) {
   return launch_reduce_allreduce(y, expert_weights, invert_permutation, out, T, k, N, dtype, peer_buffers,
-                                 rank, world, buffer_bytes, (cudaStream_t)stream);
+                                 rank, world, buffer_bytes, algorithm, flags, wait_limit_ns, (cudaStream_t)stream);
 }
 
-int pmx_moe_reduce_allreduce_check(const void* my_buffer, int32_t out[4], void* stream) {
+int pmx_moe_reduce_allreduce_emulated(const void* const* y, const void* const* expert_weights,
+                                      const int64_t* const* invert_permutation, void* const* out, int64_t T,
+                                      int32_t k, int64_t N, int32_t dtype, void* const* buffers, int32_t world,
+                                      size_t buffer_bytes, int32_t algorithm, int64_t wait_limit_ns, void* stream) {
+  return launch_reduce_allreduce_emulated(y, expert_weights, invert_permutation, out, T, k, N, dtype, buffers,
+                                          world, buffer_bytes, algorithm, wait_limit_ns, (cudaStream_t)stream);
+}
+
+int pmx_moe_reduce_allreduce_check(void* my_buffer, int32_t out[4], void* stream) {
   if (!my_buffer || !out) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_reduce_allreduce_check: null pointer");
   return reduce_allreduce_check(my_buffer, out, (cudaStream_t)stream);
+}
+
+int pmx_moe_reduce_allreduce_phases(const void* my_buffer, uint64_t out[8], void* stream) {
+  if (!my_buffer || !out) return fail(PMX_ERR_INVALID_ARGUMENT, "moe_reduce_allreduce_phases: null pointer");
+  return reduce_allreduce_phases(my_buffer, reinterpret_cast<unsigned long long*>(out), (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <tuple>
+
 #include "../../../include/pmx_moe.h"
 
 namespace pmx {
@@ -21,6 +23,35 @@ void count_launches(int n);  // adds to the process-wide kernel-launch counter
     int _s = ::pmx::check_cuda((expr), #expr);            \
     if (_s != PMX_OK) return _s;                          \
   } while (0)
+
+// Launches `kern` with programmatic stream serialisation (programmatic dependent
+// launch): the grid may be scheduled while the kernel in front of it on the stream
+// is still running, as soon as all of that kernel's CTAs have executed
+// pdl_launch_dependents() (or exited).  Kernels launched this way call pdl_wait()
+// before their first access to memory another kernel may have written, and write
+// nothing to global memory before it.  Counts the launch.  With the process-wide
+// switch off (pmx_moe_set_programmatic_launch(0)) it is an ordinary launch.
+int launch_pdl(const void* kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, void** args);
+
+// launch_pdl for a kernel given as a function pointer, with its arguments by value
+// (converted to the kernel's parameter types).
+template <typename... KArgs, typename... Args>
+int launch_pdl_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  static_assert(sizeof...(KArgs) == sizeof...(Args), "argument count does not match the kernel");
+  std::tuple<KArgs...> vals(static_cast<KArgs>(args)...);
+  void* ptrs[sizeof...(KArgs)];
+  int i = 0;
+  std::apply([&](auto&... v) { ((ptrs[i++] = (void*)&v), ...); }, vals);
+  return launch_pdl((const void*)kern, grid, block, smem, s, ptrs);
+}
+
+#ifdef __CUDACC__
+// Blocks until the grids this one depends on have completed and their memory is
+// visible (a no-op in a grid launched without programmatic serialisation).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the dependent grid be scheduled once every CTA of this grid has said so.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 // after every kernel launch: count it, then surface a launch error
 #define PMX_LAUNCHED()                       \
@@ -63,6 +94,11 @@ __device__ __forceinline__ uint4 pack16(const float (&f)[kVec<T>]) {
   return v;
 }
 
+// expert_offset[e]; a null table stands for ONE expert that owns all M rows (a dense linear)
+__device__ __forceinline__ long long offset_at(const int64_t* off, int e, long long M) {
+  return off ? (long long)off[e] : (e == 0 ? 0ll : M);
+}
+
 __device__ __forceinline__ uint4 ld_nc16(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
 }
@@ -101,8 +137,14 @@ int launch_reduce(const void* y, const void* w, const int64_t* inv, void* out, i
 size_t reduce_allreduce_buffer_bytes(int64_t T, int64_t N, int dtype);
 int launch_reduce_allreduce(const void* y, const void* w, const int64_t* inv, void* out, int64_t T,
                             int k, int64_t N, int dtype, void* const* peer_buffers, int rank,
-                            int world, size_t buffer_bytes, cudaStream_t s);
-int reduce_allreduce_check(const void* my_buffer, int out[4], cudaStream_t s);
+                            int world, size_t buffer_bytes, int algo, int flags, long long wait_limit_ns,
+                            cudaStream_t s);
+int launch_reduce_allreduce_emulated(const void* const* y, const void* const* w, const int64_t* const* inv,
+                                     void* const* out, int64_t T, int k, int64_t N, int dtype,
+                                     void* const* buffers, int world, size_t buffer_bytes, int algo,
+                                     long long wait_limit_ns, cudaStream_t s);
+int reduce_allreduce_check(void* my_buffer, int out[4], cudaStream_t s);
+int reduce_allreduce_phases(const void* my_buffer, unsigned long long out[8], cudaStream_t s);
 int launch_zero_outside(void* y, const int64_t* off, int64_t M, int64_t n_out, int E, int dtype,
                         cudaStream_t s);
 int launch_splitk_finish(const float* partial, const int64_t* off, const void* bias, void* y,
@@ -123,6 +165,7 @@ struct TcPlan {
   int cta_cap;
   int full_rounds;
   int stream_k;
+  int balanced;    // weight rows on MMA-M: feature rows dealt evenly over the CTAs in 8-row units
 };
 // Fills `plan` for the tensor-core kernel or returns false when the shape is
 // outside what it covers (the caller then uses the CUDA-core kernel).

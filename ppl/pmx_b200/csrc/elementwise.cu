@@ -68,6 +68,8 @@ template <typename T, bool VEC>
 __global__ void reduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
                               const int64_t* __restrict__ inv, T* __restrict__ out, int64_t Tn,
                               int k, int64_t N) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = VEC ? kVec<T> : 1;
   const int64_t chunks = N / V;
   const int64_t total = Tn * chunks;
@@ -83,6 +85,8 @@ __global__ void reduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
 template <typename T, bool VEC>
 __global__ void swiglu_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int64_t D,
                               float beta) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = VEC ? kVec<T> : 1;
   const int64_t half = D / 2, chunks = half / V, total = M * chunks;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -106,6 +110,8 @@ __global__ void swiglu_kernel(const T* __restrict__ x, T* __restrict__ y, int64_
 template <typename T, bool VEC>
 __global__ void silu_kernel(const T* __restrict__ x, const T* __restrict__ gate, T* __restrict__ y,
                             int64_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = VEC ? kVec<T> : 1;
   const int64_t total = n / V;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -153,6 +159,8 @@ template <typename T, bool VEC, bool REG>
 __global__ void __launch_bounds__(256)
 skip_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ skip, const T* __restrict__ weight,
                      T* __restrict__ y, T* __restrict__ skip_out, int64_t M, int64_t H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = VEC ? kVec<T> : 1;
   constexpr int R = 4;   // chunks per thread held in registers (REG)
   __shared__ float warp_sums[8];
@@ -241,6 +249,8 @@ skip_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ skip, const 
 template <typename T>
 __global__ void zero_outside_kernel(T* __restrict__ y, const int64_t* __restrict__ off, int64_t M,
                                     int64_t n_out, int E) {
+  pdl_launch_dependents();
+  pdl_wait();
   int64_t lo = off[0], hi = off[E];
   lo = lo < 0 ? 0 : (lo > M ? M : lo);
   hi = hi < lo ? lo : (hi > M ? M : hi);
@@ -261,9 +271,11 @@ __global__ void splitk_finish_kernel(const float* __restrict__ partial,
                                      const int64_t* __restrict__ off, const T* __restrict__ bias,
                                      T* __restrict__ y, int64_t M, int64_t n_out, int E, int split,
                                      float beta) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t n_in = SWIGLU ? 2 * n_out : n_out;
   const int64_t chunks = n_out / 4, total = M * chunks;
-  const int64_t lo = off[0], hi = off[E];
+  const int64_t lo = offset_at(off, 0, M), hi = offset_at(off, E, M);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t m = i / chunks, c = (i - m * chunks) * 4;
@@ -280,7 +292,7 @@ __global__ void splitk_finish_kernel(const float* __restrict__ partial,
       }
       if (bias) {
         int e = 0;
-        while (e + 1 < E && off[e + 1] <= m) ++e;
+        while (e + 1 < E && offset_at(off, e + 1, M) <= m) ++e;
         const T* b = bias + (int64_t)e * n_in + c;
         acc.x += Elem<T>::to_f(b[0]); acc.y += Elem<T>::to_f(b[1]);
         acc.z += Elem<T>::to_f(b[2]); acc.w += Elem<T>::to_f(b[3]);
@@ -300,6 +312,14 @@ __global__ void splitk_finish_kernel(const float* __restrict__ partial,
   }
 }
 
+// launch with programmatic stream serialisation (the kernels above wait for their
+// predecessors first thing); counts the launch and returns on error
+#define PMX_PDL_LAUNCH(kern, grid, block, smem, s, ...)                                        \
+  do {                                                                                         \
+    const int _st = launch_pdl_k(kern, dim3(grid), dim3(block), smem, s, __VA_ARGS__);         \
+    if (_st != PMX_OK) return _st;                                                             \
+  } while (0)
+
 #define PMX_DISPATCH_DTYPE(dtype, what, ...)                                       \
   switch (dtype) {                                                                 \
     case PMX_DTYPE_F16: { using T = __half; __VA_ARGS__ } break;                   \
@@ -318,11 +338,10 @@ int launch_reduce(const void* y, const void* w, const int64_t* inv, void* out, i
     const bool vec = N % kVec<T> == 0 && aligned16(y) && aligned16(out);
     const int64_t items = Tn * (vec ? N / kVec<T> : N);
     if (vec)
-      reduce_kernel<T, true><<<grid_for(items), kThreads, 0, s>>>((const T*)y, (const T*)w, inv, (T*)out, Tn, k, N);
+      PMX_PDL_LAUNCH((reduce_kernel<T, true>), grid_for(items), kThreads, 0, s, (const T*)y, (const T*)w, inv, (T*)out, Tn, k, N);
     else
-      reduce_kernel<T, false><<<grid_for(items), kThreads, 0, s>>>((const T*)y, (const T*)w, inv, (T*)out, Tn, k, N);
+      PMX_PDL_LAUNCH((reduce_kernel<T, false>), grid_for(items), kThreads, 0, s, (const T*)y, (const T*)w, inv, (T*)out, Tn, k, N);
   })
-  PMX_LAUNCHED();
   return PMX_OK;
 }
 
@@ -333,11 +352,10 @@ int launch_swiglu(const void* x, void* y, int64_t M, int64_t D, float beta, int 
     const bool vec = (D / 2) % kVec<T> == 0 && aligned16(x) && aligned16(y);
     const int64_t items = M * (vec ? D / 2 / kVec<T> : D / 2);
     if (vec)
-      swiglu_kernel<T, true><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (T*)y, M, D, beta);
+      PMX_PDL_LAUNCH((swiglu_kernel<T, true>), grid_for(items), kThreads, 0, s, (const T*)x, (T*)y, M, D, beta);
     else
-      swiglu_kernel<T, false><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (T*)y, M, D, beta);
+      PMX_PDL_LAUNCH((swiglu_kernel<T, false>), grid_for(items), kThreads, 0, s, (const T*)x, (T*)y, M, D, beta);
   })
-  PMX_LAUNCHED();
   return PMX_OK;
 }
 
@@ -348,11 +366,10 @@ int launch_silu(const void* x, const void* gate, void* y, int64_t n, int dtype, 
     const bool vec = n % kVec<T> == 0 && aligned16(x) && aligned16(y) && (!gate || aligned16(gate));
     const int64_t items = vec ? n / kVec<T> : n;
     if (vec)
-      silu_kernel<T, true><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (const T*)gate, (T*)y, n);
+      PMX_PDL_LAUNCH((silu_kernel<T, true>), grid_for(items), kThreads, 0, s, (const T*)x, (const T*)gate, (T*)y, n);
     else
-      silu_kernel<T, false><<<grid_for(items), kThreads, 0, s>>>((const T*)x, (const T*)gate, (T*)y, n);
+      PMX_PDL_LAUNCH((silu_kernel<T, false>), grid_for(items), kThreads, 0, s, (const T*)x, (const T*)gate, (T*)y, n);
   })
-  PMX_LAUNCHED();
   return PMX_OK;
 }
 
@@ -367,22 +384,20 @@ int launch_skip_rms_norm(const void* x, const void* skip, const void* weight, vo
                      (!skip || (aligned16(skip) && aligned16(skip_out)));
     T* so = skip ? (T*)skip_out : (T*)y;   // unused without skip
     if (vec && H / kVec<T> <= 4 * 256)
-      skip_rms_norm_kernel<T, true, true><<<(int)blocks, 256, 0, s>>>((const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
+      PMX_PDL_LAUNCH((skip_rms_norm_kernel<T, true, true>), (int)blocks, 256, 0, s, (const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
     else if (vec)
-      skip_rms_norm_kernel<T, true, false><<<(int)blocks, 256, 0, s>>>((const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
+      PMX_PDL_LAUNCH((skip_rms_norm_kernel<T, true, false>), (int)blocks, 256, 0, s, (const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
     else
-      skip_rms_norm_kernel<T, false, false><<<(int)blocks, 256, 0, s>>>((const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
+      PMX_PDL_LAUNCH((skip_rms_norm_kernel<T, false, false>), (int)blocks, 256, 0, s, (const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
   })
-  PMX_LAUNCHED();
   return PMX_OK;
 }
 
 int launch_zero_outside(void* y, const int64_t* off, int64_t M, int64_t n_out, int E, int dtype,
                         cudaStream_t s) {
   PMX_DISPATCH_DTYPE(dtype, "grouped_linear", {
-    zero_outside_kernel<T><<<sm_count(), kThreads, 0, s>>>((T*)y, off, M, n_out, E);
+    PMX_PDL_LAUNCH((zero_outside_kernel<T>), sm_count(), kThreads, 0, s, (T*)y, off, M, n_out, E);
   })
-  PMX_LAUNCHED();
   return PMX_OK;
 }
 
@@ -392,11 +407,10 @@ int launch_splitk_finish(const float* partial, const int64_t* off, const void* b
   if (n_out % 4) return fail(PMX_ERR_UNSUPPORTED, "grouped_linear: split-K needs N %% 4 == 0");
   PMX_DISPATCH_DTYPE(dtype, "grouped_linear", {
     if (swiglu)
-      splitk_finish_kernel<T, true><<<grid_for(M * n_out / 4), kThreads, 0, s>>>(partial, off, (const T*)bias, (T*)y, M, n_out, E, split, beta);
+      PMX_PDL_LAUNCH((splitk_finish_kernel<T, true>), grid_for(M * n_out / 4), kThreads, 0, s, partial, off, (const T*)bias, (T*)y, M, n_out, E, split, beta);
     else
-      splitk_finish_kernel<T, false><<<grid_for(M * n_out / 4), kThreads, 0, s>>>(partial, off, (const T*)bias, (T*)y, M, n_out, E, split, beta);
+      PMX_PDL_LAUNCH((splitk_finish_kernel<T, false>), grid_for(M * n_out / 4), kThreads, 0, s, partial, off, (const T*)bias, (T*)y, M, n_out, E, split, beta);
   })
-  PMX_LAUNCHED();
   return PMX_OK;
 }
 

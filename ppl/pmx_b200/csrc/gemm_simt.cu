@@ -29,7 +29,7 @@ grouped_gemm_simt_kernel(const T* __restrict__ x, const int64_t* __restrict__ of
     int e = 0;
     s_expert = -1;
     for (; e < E; ++e) {
-      int64_t r0 = off[e], r1 = off[e + 1];
+      int64_t r0 = offset_at(off, e, M), r1 = offset_at(off, e + 1, M);
       r0 = r0 < 0 ? 0 : r0;
       r1 = r1 > M ? M : r1;
       const int64_t tiles = r1 > r0 ? (r1 - r0 + BM - 1) / BM : 0;

@@ -34,8 +34,6 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
-#include <cstdio>
-#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -48,7 +46,8 @@ namespace {
 template <typename T, int MODE, bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
-                       const __grid_constant__ CUtensorMap map_w, const Params p) {
+                       const __grid_constant__ CUtensorMap map_w,
+                       const __grid_constant__ SmallBoxMaps map_ws, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tt = p.tile_tok, ft = p.tile_feat;
@@ -62,13 +61,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   // ---- set-up ---------------------------------------------------------------
-  // CTA 0 clears the status words (a failed wait is recorded no earlier than
-  // its 2 s limit, long after this store)
-  if (blockIdx.x == 0 && threadIdx.x < 4) p.status[threadIdx.x] = 0;
-  for (int e = threadIdx.x; e <= p.E; e += blockDim.x) {
-    long long o = p.off[e];
-    s_off[e] = (int)(o < 0 ? 0 : (o > p.M ? p.M : o));
-  }
+  // Everything up to pdl_wait() touches no memory another kernel writes, so under
+  // programmatic dependent launch it overlaps the tail of the kernel in front.
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.stages; ++i) {
       mbar_init(&sh->full[i], 1);
@@ -80,6 +75,24 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     }
     sh->abort = 0;
     fence_barrier_init();
+    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&map_w);
+    if (MODE == 1 && p.balanced) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) prefetch_tensormap(&map_ws.m[i]);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  pdl_wait();
+  // CTA 0 clears the status words (a failed wait is recorded no earlier than
+  // its 2 s limit, long after this store)
+  if (blockIdx.x == 0 && threadIdx.x < 4) p.status[threadIdx.x] = 0;
+  for (int e = threadIdx.x; e <= p.E; e += blockDim.x) {
+    long long o = offset_at(p.off, e, p.M);
+    s_off[e] = (int)(o < 0 ? 0 : (o > p.M ? p.M : o));
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -91,10 +104,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       acc += ((rows + tt - 1) / tt) * p.feat_tiles * p.split_k;
     }
     s_prefix[p.E] = acc;
-  }
-  if (warp == 1) {
-    tmem_alloc(&sh->tmem_base, kTmemCols);
-    tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
@@ -118,13 +127,33 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           ok = wait_barrier(&sh->empty[stage], phase ^ 1u, sh, p.status, 0, item);
           if (!ok) break;
-          mbar_expect_tx(&sh->full[stage], stage_bytes);
           const uint32_t dst = smem_base + stage * stage_bytes;
-          tma_load_2d(dst, &map_x, &sh->full[stage], kb * kBlockK, it.row0);
-          tma_load_2d(dst + tok_bytes, &map_w, &sh->full[stage], kb * kBlockK, wrow);
-          if (SWIGLU)
-            tma_load_2d(dst + tok_bytes + ft * 128, &map_w, &sh->full[stage], kb * kBlockK,
-                        wrow + p.N / 2);
+          if (MODE == 1 && p.balanced && it.fn != ft) {
+            // a range of it.fn < 128 feature rows: boxes of 64, 32, 16 and 8 rows (each at
+            // most once); the rows of the stage behind them keep stale data that only
+            // reaches accumulator lanes nobody stores
+            mbar_expect_tx(&sh->full[stage], tok_bytes + (SWIGLU ? 2u : 1u) * (uint32_t)it.fn * 128u);
+            tma_load_2d(dst, &map_x, &sh->full[stage], kb * kBlockK, it.row0);
+            int done = 0;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const int rows = 64 >> b;
+              if (it.fn - done >= rows) {
+                tma_load_2d(dst + tok_bytes + done * 128, &map_ws.m[b], &sh->full[stage], kb * kBlockK, wrow + done);
+                if (SWIGLU)
+                  tma_load_2d(dst + tok_bytes + (ft + done) * 128, &map_ws.m[b], &sh->full[stage], kb * kBlockK,
+                              wrow + p.N / 2 + done);
+                done += rows;
+              }
+            }
+          } else {
+            mbar_expect_tx(&sh->full[stage], stage_bytes);
+            tma_load_2d(dst, &map_x, &sh->full[stage], kb * kBlockK, it.row0);
+            tma_load_2d(dst + tok_bytes, &map_w, &sh->full[stage], kb * kBlockK, wrow);
+            if (SWIGLU)
+              tma_load_2d(dst + tok_bytes + ft * 128, &map_w, &sh->full[stage], kb * kBlockK,
+                          wrow + p.N / 2);
+          }
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
       }
@@ -300,14 +329,14 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         }
       } else {
         const int f = it.f0 + q * 32 + lane;  // output feature of this thread
-        const bool f_ok = f < p.n_out;
+        const bool f_ok = f < p.n_out && q * 32 + lane < it.fn;
         float bg = 0.f, bu = 0.f;
         if (bias && f_ok) {
           bg = Elem<T>::to_f(bias[(int64_t)it.e * p.N + f]);
           if (SWIGLU) bu = Elem<T>::to_f(bias[(int64_t)it.e * p.N + p.n_out + f]);
         }
         for (int c = 0; c < tt; c += 16) {
-          if (it.row0 + c >= it.row_end) break;  // same for the whole warp
+          if (it.row0 + c >= it.row_end || q * 32 >= it.fn) break;  // same for the whole warp
           float g[16], u[16];
           __syncwarp();
           tmem_ld16(taddr + c, g);
@@ -350,13 +379,12 @@ size_t smem_bytes_for(const TcPlan& plan, bool swiglu, int E) {
 }
 
 template <typename T, int MODE, bool SWIGLU>
-int launch_inst(const CUtensorMap& mx, const CUtensorMap& mw, const Params& p, int grid, size_t smem,
-                cudaStream_t s) {
+int launch_inst(const CUtensorMap& mx, const CUtensorMap& mw, const SmallBoxMaps& mws, const Params& p, int grid,
+                size_t smem, cudaStream_t s) {
   auto kern = grouped_gemm_tc_kernel<T, MODE, SWIGLU>;
   PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, kThreads, smem, s>>>(mx, mw, p);
-  PMX_LAUNCHED();
-  return PMX_OK;
+  void* args[] = {(void*)&mx, (void*)&mw, (void*)&mws, (void*)&p};
+  return launch_pdl((const void*)kern, dim3(grid), dim3(kThreads), smem, s, args);
 }
 
 int pow2_at_least(int64_t v, int lo, int hi) {
@@ -393,9 +421,13 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   }
   const int kblocks = (int)ceil_div(K, kBlockK);
   const int64_t feat_tiles = ceil_div(n_out, pl.tile_feat);
+  const int want_sk = user ? user->stream_k : 0;
+  // Weight rows on MMA-M: deal the feature rows of all panels out evenly (8-row units)
+  // instead of whole 128-row tiles, unless the caller asks for whole tiles or stream-K.
+  pl.balanced = pl.kernel == PMX_GEMM_TC_WEIGHTS_M && want_sk != 1 && !(user && user->balance == 2) ? 1 : 0;
   if (user && user->split_k) {
     pl.split_k = user->split_k;
-  } else if (user && user->stream_k == 1) {
+  } else if (want_sk == 1) {
     pl.split_k = 1;   // stream-K slices K itself
   } else {
     pl.split_k = 1;
@@ -403,14 +435,17 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
     const int64_t act = M < E ? M : E;
     const int64_t tok_tiles = act * (int64_t)ceil_div((int64_t)(avg_rows < 1 ? 1 : avg_rows), pl.tile_tok);
     const int64_t items = tok_tiles * feat_tiles;
-    if (2 * items <= sms) {
-      // fewer work items than half the SMs (one token, or a thin tensor-parallel
-      // shard): slice K.  With SwiGLU the kernel then produces plain [gate | up]
-      // partial sums (twice the feature tiles) and the activation moves into the
-      // final sum.  Measured on B200: with more items than that the extra
-      // partial-sum traffic and launch cost more than the better balance gains.
-      const int64_t base = swiglu ? tok_tiles * ceil_div(N, pl.tile_feat) : items;
-      int64_t want = ceil_div(2 * sms, base);
+    // balanced: 8-row units are the grain, so K is sliced only when there are fewer
+    // than two units per SM; whole tiles: when there are fewer tiles than half the SMs
+    // (one token, or a thin tensor-parallel shard).  With SwiGLU the kernel then
+    // produces plain [gate | up] partial sums (twice the feature tiles) and the
+    // activation moves into the final sum.  Measured on B200: with more items than
+    // that the extra partial-sum traffic and launch cost more than the better balance gains.
+    const bool slice = pl.balanced ? tok_tiles * (n_out / 8) < 2 * (int64_t)sms : 2 * items <= sms;
+    if (slice) {
+      const int64_t base = pl.balanced ? (tok_tiles * (N / 8) + 15) / 16
+                                       : (swiglu ? tok_tiles * ceil_div(N, pl.tile_feat) : items);
+      int64_t want = ceil_div(2 * sms, base > 0 ? base : 1);
       const int64_t cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
       if (want > cap) want = cap;
       if (want > 16) want = 16;
@@ -435,25 +470,24 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   if (st < 2) return false;
   pl.stages = st;
   pl.max_ctas = user && user->max_ctas ? user->max_ctas : sms;
-  // Weight streaming is HBM-bound and measurably faster on B200 with 128 CTAs than
-  // with all 148 SMs (6.5-6.7 TB/s against 6.3); the tensor-bound assignment uses every SM.
+  // Whole 128-row weight tiles stream measurably faster on B200 with 128 CTAs than with
+  // all 148 SMs (6.5-6.7 TB/s against 6.3: a ragged last round of tiles costs a full
+  // one); evenly dealt rows and the tensor-bound assignment use every SM.
   pl.cta_cap = pl.max_ctas;
-  if (!(user && user->max_ctas) && pl.kernel == PMX_GEMM_TC_WEIGHTS_M && pl.cta_cap > 128) pl.cta_cap = 128;
-  // experiment knobs (grid sweeps): PMX_MOE_GEMM_CTAS=<n> caps the CTAs that take work,
-  // PMX_MOE_GEMM_FULL_ROUNDS=0 makes every capped CTA stride over the tiles as launched
-  if (const char* env = getenv("PMX_MOE_GEMM_CTAS")) {
-    const int n = atoi(env);
-    if (n > 0 && n <= pl.max_ctas) pl.cta_cap = n;
-  }
-  pl.full_rounds = 1;
-  if (const char* env = getenv("PMX_MOE_GEMM_FULL_ROUNDS")) pl.full_rounds = atoi(env) != 0;
+  if (!(user && user->max_ctas) && pl.kernel == PMX_GEMM_TC_WEIGHTS_M && !pl.balanced && pl.cta_cap > 128) pl.cta_cap = 128;
+  if (user && user->cta_cap > 0 && user->cta_cap <= pl.max_ctas) pl.cta_cap = user->cta_cap;
+  pl.full_rounds = !(user && user->full_rounds == 2);
   // Stream-K (k-blocks of all items dealt out evenly over the CTAs) is available on
   // request.  Measured on B200 it does not beat whole tiles on a grid sized to
   // full rounds (see WorkIter::init): 283 vs 290 us for the Mixtral gate/up
   // projection at 64 tokens, but 55 vs 46 us on a 1/8 tensor-parallel shard.
-  const int want_sk = user ? user->stream_k : 0;
   pl.stream_k = pl.split_k == 1 && want_sk == 1 ? 1 : 0;
   if (want_sk == 1 && !pl.stream_k) return false;
+  // Stream-K: the owner of a cut tile waits for CTAs with higher indices, so all CTAs of
+  // the launch have to be resident together: one per SM and the SMs not shared with other
+  // kernels.  A ring so small that two CTAs fit on one SM is refused (the second would
+  // block in the tensor-memory allocation until the first exits).
+  if (pl.stream_k && fixed + stage * (size_t)pl.stages <= 114 * 1024) return false;
   *plan = pl;
   return true;
 }
@@ -486,11 +520,13 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   st = make_map(&mw, w, (uint64_t)E * N, (uint64_t)K, (uint32_t)plan.tile_feat, dtype);
   if (st != PMX_OK) return st;
 
-  if (getenv("PMX_MOE_DEBUG"))
-    fprintf(stderr, "[pmx_moe] grouped_linear M=%lld N=%lld K=%lld E=%d swiglu=%d: %s tile_feat=%d tile_tok=%d split_k=%d stages=%d grid=%d cta_cap=%d stream_k=%d\n",
-            (long long)M, (long long)N, (long long)K, E, (int)swiglu_any,
-            plan.kernel == PMX_GEMM_TC_TOKENS_M ? "tokens-on-M" : "weights-on-M", plan.tile_feat, plan.tile_tok,
-            plan.split_k, plan.stages, plan.max_ctas, plan.cta_cap, plan.stream_k);
+  SmallBoxMaps mws{};
+  if (plan.balanced) {
+    for (int b = 0; b < 4; ++b) {
+      st = make_map(&mws.m[b], w, (uint64_t)E * N, (uint64_t)K, (uint32_t)(64 >> b), dtype);
+      if (st != PMX_OK) return st;
+    }
+  }
   Params p{};
   p.off = off;
   p.bias = plan.split_k > 1 ? nullptr : bias;  // with split-K the bias joins in the final sum
@@ -500,7 +536,9 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   p.n_out = (int)n_out;
   p.tile_tok = plan.tile_tok;
   p.tile_feat = plan.tile_feat;
-  p.feat_tiles = (int)ceil_div(n_out, plan.tile_feat);
+  p.feat_tiles = plan.balanced ? 1 : (int)ceil_div(n_out, plan.tile_feat);
+  p.balanced = plan.balanced;
+  p.units_per_panel = (int)(n_out / 8);
   p.kblocks = (int)ceil_div(K, kBlockK);
   p.split_k = plan.split_k;
   p.kb_per_split = (int)ceil_div(p.kblocks, plan.split_k);
@@ -521,7 +559,7 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   const int grid = plan.max_ctas;
   const bool bf = dtype == PMX_DTYPE_BF16;
   const int mode = plan.kernel == PMX_GEMM_TC_TOKENS_M ? 0 : 1;
-#define PMX_TC_LAUNCH(TT, MD, SW) st = launch_inst<TT, MD, SW>(mx, mw, p, grid, smem, s)
+#define PMX_TC_LAUNCH(TT, MD, SW) st = launch_inst<TT, MD, SW>(mx, mw, mws, p, grid, smem, s)
   if (mode == 0) {
     if (swiglu) { if (bf) PMX_TC_LAUNCH(__nv_bfloat16, 0, true); else PMX_TC_LAUNCH(__half, 0, true); }
     else        { if (bf) PMX_TC_LAUNCH(__nv_bfloat16, 0, false); else PMX_TC_LAUNCH(__half, 0, false); }

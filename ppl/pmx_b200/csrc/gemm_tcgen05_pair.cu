@@ -23,8 +23,6 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
-#include <cstdio>
-#include <cstdlib>
 #include <type_traits>
 
 #include "common.cuh"
@@ -105,11 +103,9 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x,
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
 
-  if (blockIdx.x == 0 && threadIdx.x < 4) p.status[threadIdx.x] = 0;
-  for (int e = threadIdx.x; e <= p.E; e += blockDim.x) {
-    long long o = p.off[e];
-    s_off[e] = (int)(o < 0 ? 0 : (o > p.M ? p.M : o));
-  }
+  // set-up that touches nothing another kernel writes: under programmatic dependent
+  // launch it overlaps the tail of the kernel in front
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int i = 0; i < p.stages; ++i) {
       mbar_init(&sh->full[i], 1);    // used in the leader only: its producer's expect_tx arrival
@@ -121,6 +117,18 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x,
     }
     sh->abort = 0;
     fence_barrier_init();
+    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&map_w);
+  }
+  if (warp == 1) {
+    tmem_alloc2(&sh->tmem_base, kTmemCols);
+    tmem_relinquish2();
+  }
+  pdl_wait();
+  if (blockIdx.x == 0 && threadIdx.x < 4) p.status[threadIdx.x] = 0;
+  for (int e = threadIdx.x; e <= p.E; e += blockDim.x) {
+    long long o = offset_at(p.off, e, p.M);
+    s_off[e] = (int)(o < 0 ? 0 : (o > p.M ? p.M : o));
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -132,10 +140,6 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x,
       acc += ((rows + 255) / 256) * p.feat_tiles;   // the pair's token tile is 256 rows
     }
     s_prefix[p.E] = acc;
-  }
-  if (warp == 1) {
-    tmem_alloc2(&sh->tmem_base, kTmemCols);
-    tmem_relinquish2();
   }
   tc_fence_before();
   __syncthreads();
@@ -277,9 +281,9 @@ int launch_pair_inst(const CUtensorMap& mx, const CUtensorMap& mw, const Params&
                      cudaStream_t s) {
   auto kern = grouped_gemm_tc_pair_kernel<T, SWIGLU>;
   PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<grid, kThreads, smem, s>>>(mx, mw, p);   // cluster shape is part of the kernel (__cluster_dims__)
-  PMX_LAUNCHED();
-  return PMX_OK;
+  void* args[] = {(void*)&mx, (void*)&mw, (void*)&p};
+  // the cluster shape is part of the kernel (__cluster_dims__)
+  return launch_pdl((const void*)kern, dim3(grid), dim3(kThreads), smem, s, args);
 }
 
 }  // namespace
@@ -335,9 +339,6 @@ int launch_gemm_tc_pair(const void* x, const int64_t* off, const void* w, const 
   if (st != PMX_OK) return st;
   st = make_map(&mw, w, (uint64_t)E * N, (uint64_t)K, (uint32_t)(wrows / 2), dtype);
   if (st != PMX_OK) return st;
-  if (getenv("PMX_MOE_DEBUG"))
-    fprintf(stderr, "[pmx_moe] grouped_linear M=%lld N=%lld K=%lld E=%d swiglu=%d: paired CTAs tile 256x%d stages=%d grid=%d\n",
-            (long long)M, (long long)N, (long long)K, E, (int)swiglu, wrows, plan.stages, plan.max_ctas);
   Params p{};
   p.off = off;
   p.bias = bias;

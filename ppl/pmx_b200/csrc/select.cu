@@ -21,9 +21,7 @@
 //   select_small: every block repeats the routing of all tokens and derives the
 //                 positions of its own slots from warp ballots.
 //   route_select: the same with the router logits (x . W_gate^T) computed in the
-//                 kernel and one bounded grid-wide barrier (cooperative launch).
-#include <mutex>
-
+//                 kernel and one bounded, self-resetting grid-wide barrier.
 #include "common.cuh"
 
 namespace pmx {
@@ -49,6 +47,8 @@ template <typename T>
 __global__ void route_count_kernel(const T* __restrict__ scores, int64_t T_tokens, int E, int k,
                                    int tpb, T* __restrict__ weights, int* __restrict__ ids,
                                    int* __restrict__ block_counts) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ int hist[];  // [E]
   for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
   __syncthreads();
@@ -102,6 +102,8 @@ __global__ void route_count_kernel(const T* __restrict__ scores, int64_t T_token
 // totals into expert_offset.
 __global__ void scan_kernel(int* __restrict__ block_counts, int nblk, int E, int* __restrict__ totals,
                             unsigned int* __restrict__ ticket, int64_t* __restrict__ expert_offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ int warp_sum[32];
   __shared__ int carry;
   __shared__ bool last;
@@ -155,6 +157,8 @@ __global__ void place_gather_kernel(const T* __restrict__ x, const int* __restri
                                     const int64_t* __restrict__ expert_offset, int64_t T_tokens,
                                     int64_t H, int E, int k, int tpb, T* __restrict__ xp,
                                     int64_t* __restrict__ inv) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ int sm[];
   int* cursor = sm;      // [E] next row of each expert for this block
   int* pos = sm + E;     // [tpb*k] destination row of each slot of this block
@@ -234,6 +238,8 @@ __global__ void __launch_bounds__(256)
 select_small_kernel(const T* __restrict__ x, const T* __restrict__ scores, int Tn, int64_t H, int E,
                     int k, int tpb, T* __restrict__ xp, T* __restrict__ weights,
                     int64_t* __restrict__ inv, int64_t* __restrict__ expert_offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ unsigned int sm_small[];
   const int groups = (Tn + 31) / 32;
   unsigned int* ballots = sm_small;                                     // [groups][E]
@@ -353,25 +359,27 @@ int run_select_small(const void* x, const void* scores, void* xp, void* w, int64
   const bool vec = (H * sizeof(T)) % 16 == 0 && aligned16(x) && aligned16(xp);
   auto kern = vec ? select_small_kernel<T, true> : select_small_kernel<T, false>;
   if (smem > 48 * 1024) PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<nblk, 256, smem, s>>>(reinterpret_cast<const T*>(x), reinterpret_cast<const T*>(scores), (int)Tn, H, E, k, tpb,
-                               reinterpret_cast<T*>(xp), reinterpret_cast<T*>(w), inv, off);
-  PMX_LAUNCHED();
-  return PMX_OK;
+  return launch_pdl_k(kern, dim3(nblk), dim3(256), smem, s, reinterpret_cast<const T*>(x),
+                      reinterpret_cast<const T*>(scores), (int)Tn, H, E, k, tpb, reinterpret_cast<T*>(xp),
+                      reinterpret_cast<T*>(w), inv, off);
 }
 
-// ---- router gate + select in one cooperative launch ---------------------------
+// ---- router gate + select in one launch ---------------------------------------
 // For decode-size batches the router logits (Linear.forward, Linear.py:24-33,
 // called at Model.py:188) are computed by the same kernel that routes: each
 // block computes the E logits of its own tokens (fp32 accumulation, one rounding
 // to T1 -- the scores the reference would hand to moe_select), picks their top-k
 // and publishes one 64-bit expert mask per token; after a grid-wide barrier
-// (bounded spin on a counter; the launch is cooperative, so all blocks are
-// resident) every block derives the stable positions of its own slots from the
-// masks of all tokens and gathers its rows.
+// (bounded spin on a generation word; the grid has at most one block per SM, so
+// all blocks are resident together) every block derives the stable positions of its own slots from the
+// masks of all tokens and gathers its rows.  The grid has at most one block per SM.
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
   unsigned int v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // NORM: the rows routed are RMSNorm(x (+ skip)) * norm_w (SkipRMSNorm.forward,
@@ -391,7 +399,7 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
                     int tpb, T* __restrict__ scores, T* __restrict__ xp, T* __restrict__ weights,
                     int64_t* __restrict__ inv, int64_t* __restrict__ expert_offset,
                     unsigned long long* __restrict__ masks, unsigned int* __restrict__ counter,
-                    int* __restrict__ status, NormArgs norm) {
+                    int* __restrict__ status, NormArgs norm, unsigned long long wait_ns) {
   extern __shared__ unsigned int sm_rs[];
   const int groups = (Tn + 31) / 32;
   unsigned int* ballots = sm_rs;                                        // [groups][E]
@@ -411,6 +419,8 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
   constexpr int V = kVec<T>;
   const int chunks = (int)(H / V);
   if (threadIdx.x == 0) s_abort = 0;
+  pdl_launch_dependents();
+  pdl_wait();   // x (and skip) come from the kernel in front of this one
 
   // A0. (NORM) normalise my tokens into shared memory
   if (NORM) {
@@ -515,22 +525,31 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
       weights[(int64_t)t * k + j] = Elem<T>::from_f(expf(row[my_ids[tl * k + j]] - vmax) / denom);
     masks[t] = mask;
   }
-  // grid-wide barrier: everybody's masks are in global memory
+  // grid-wide barrier: everybody's masks are in global memory.  Sense-reversing and
+  // self-resetting (the last block to arrive clears the count and advances the
+  // generation), so the two words only have to be zero once, before the first call.
   __syncthreads();
   if (threadIdx.x == 0) {
+    unsigned int* generation = counter + 1;
+    const unsigned int gen0 = ld_acquire_gpu(generation);   // cannot advance before this block arrives
     __threadfence();
-    atomicAdd(counter, 1u);
-    unsigned long long t_start = 0;
-    unsigned int it = 0;
-    while (ld_acquire_gpu(counter) < gridDim.x) {
-      if ((++it & 1023u) == 0u) {
-        unsigned long long now;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-        if (t_start == 0) t_start = now;
-        if (now - t_start > 1000000000ull) {   // 1 s: give up, record it
-          s_abort = 1;
-          atomicCAS(status, 0, 2);
-          break;
+    if (atomicAdd(counter, 1u) == gridDim.x - 1) {
+      *reinterpret_cast<volatile unsigned int*>(counter) = 0u;
+      __threadfence();
+      st_release_gpu(generation, gen0 + 1u);
+    } else {
+      unsigned long long t_start = 0;
+      unsigned int it = 0;
+      while (ld_acquire_gpu(generation) == gen0) {
+        if ((++it & 1023u) == 0u) {
+          unsigned long long now;
+          asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+          if (t_start == 0) t_start = now;
+          if (now - t_start > wait_ns) {   // give up, record it
+            s_abort = 1;
+            atomicCAS(status, 0, 2);
+            break;
+          }
         }
       }
     }
@@ -635,24 +654,19 @@ int run_select(const void* x, const void* scores, void* xp, void* w, int64_t* in
   int* ids = reinterpret_cast<int*>(ws);
   int* counts = reinterpret_cast<int*>(reinterpret_cast<char*>(ws) + g.ids_bytes);
   const int route_threads = 32 * (g.tpb < 8 ? g.tpb : 8);
-  route_count_kernel<T><<<g.nblk, route_threads, E * sizeof(int), s>>>(
-      reinterpret_cast<const T*>(scores), Tn, E, k, g.tpb, reinterpret_cast<T*>(w), ids, counts);
-  PMX_LAUNCHED();
+  int st = launch_pdl_k(route_count_kernel<T>, dim3(g.nblk), dim3(route_threads), E * sizeof(int), s,
+                        reinterpret_cast<const T*>(scores), Tn, E, k, g.tpb, reinterpret_cast<T*>(w), ids, counts);
+  if (st != PMX_OK) return st;
   int* totals = counts + (int64_t)g.nblk * E;
   unsigned int* ticket = reinterpret_cast<unsigned int*>(totals + E);
   PMX_CUDA_OK(cudaMemsetAsync(ticket, 0, sizeof(unsigned int), s));
-  scan_kernel<<<E, 256, 0, s>>>(counts, g.nblk, E, totals, ticket, off);
-  PMX_LAUNCHED();
+  st = launch_pdl_k(scan_kernel, dim3(E), dim3(256), 0, s, counts, g.nblk, E, totals, ticket, off);
+  if (st != PMX_OK) return st;
   const size_t sm_bytes = (size_t)(E + g.tpb * k) * sizeof(int);
   const bool vec = (H * sizeof(T)) % 16 == 0 && aligned16(x) && aligned16(xp);
-  if (vec)
-    place_gather_kernel<T, true><<<g.nblk, 256, sm_bytes, s>>>(
-        reinterpret_cast<const T*>(x), ids, counts, off, Tn, H, E, k, g.tpb, reinterpret_cast<T*>(xp), inv);
-  else
-    place_gather_kernel<T, false><<<g.nblk, 256, sm_bytes, s>>>(
-        reinterpret_cast<const T*>(x), ids, counts, off, Tn, H, E, k, g.tpb, reinterpret_cast<T*>(xp), inv);
-  PMX_LAUNCHED();
-  return PMX_OK;
+  auto place = vec ? place_gather_kernel<T, true> : place_gather_kernel<T, false>;
+  return launch_pdl_k(place, dim3(g.nblk), dim3(256), sm_bytes, s, reinterpret_cast<const T*>(x), ids, counts, off, Tn,
+                      H, E, k, g.tpb, reinterpret_cast<T*>(xp), inv);
 }
 
 }  // namespace
@@ -708,11 +722,11 @@ int launch_route_select_impl(const void* x, const void* wr, void* scores, void* 
   unsigned int* counter = reinterpret_cast<unsigned int*>(ws);
   int* status = reinterpret_cast<int*>(ws) + 4;
   unsigned long long* masks = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(ws) + 64);
-  PMX_CUDA_OK(cudaMemsetAsync(ws, 0, 64, s));
   int Tn = (int)T;
+  unsigned long long wait_ns = 1000000000ull;   // 1 s
   void* args[] = {(void*)&x, (void*)&wr, (void*)&Tn, (void*)&H, (void*)&E, (void*)&k, (void*)&g.tpb, (void*)&scores,
                   (void*)&xp, (void*)&w, (void*)&inv, (void*)&off, (void*)&masks, (void*)&counter, (void*)&status,
-                  (void*)&norm};
+                  (void*)&norm, (void*)&wait_ns};
   const void* kern = nullptr;
   switch (dtype) {
     case PMX_DTYPE_F16: kern = with_norm ? (const void*)route_select_kernel<__half, true> : (const void*)route_select_kernel<__half, false>; break;
@@ -721,9 +735,9 @@ int launch_route_select_impl(const void* x, const void* wr, void* scores, void* 
     default: return fail(PMX_ERR_UNSUPPORTED, "%s: unknown dtype %d", name, dtype);
   }
   if (g.smem > 48 * 1024) PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem));
-  PMX_CUDA_OK(cudaLaunchCooperativeKernel(kern, dim3(g.nblk), dim3(256), args, g.smem, s));
-  count_launches(1);
-  return PMX_OK;
+  // at most one block per SM (route_select_geometry), so the whole grid is resident
+  // once the kernels in front of it have drained; the barrier wait is bounded anyway
+  return launch_pdl(kern, dim3(g.nblk), dim3(256), g.smem, s, args);
 }
 
 int launch_route_select(const void* x, const void* wr, void* scores, void* xp, void* w, int64_t* inv,
@@ -746,22 +760,14 @@ int launch_norm_route_select(const void* x, const void* skip, const void* norm_w
   return launch_route_select_impl(x, wr, scores, xp, w, inv, off, T, H, E, k, dtype, ws, ws_bytes, s, true, norm);
 }
 
-// Device address of the built-in scratch on the current device, looked up once
-// per device (with that device current) and cached.
+// Device address of the built-in scratch on the current device.  Looked up on every
+// call (a host-side table lookup once the module is loaded), so that the address is
+// never stale after cudaDeviceReset or a change of context on the device.
 int select_static_scratch(void** out) {
-  static std::mutex mu;
-  static void* cached[64] = {nullptr};
-  int dev = -1;
-  PMX_CUDA_OK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return fail(PMX_ERR_UNSUPPORTED, "moe_select_static: device index %d out of range", dev);
-  std::lock_guard<std::mutex> lock(mu);
-  if (!cached[dev]) {
-    void* p = nullptr;
-    PMX_CUDA_OK(cudaGetSymbolAddress(&p, g_select_static_scratch));
-    if (!p) return fail(PMX_ERR_CUDA, "moe_select_static: cudaGetSymbolAddress returned a null address");
-    cached[dev] = p;
-  }
-  *out = cached[dev];
+  void* p = nullptr;
+  PMX_CUDA_OK(cudaGetSymbolAddress(&p, g_select_static_scratch));
+  if (!p) return fail(PMX_ERR_CUDA, "moe_select_static: cudaGetSymbolAddress returned a null address");
+  *out = p;
   return PMX_OK;
 }
 

@@ -30,6 +30,17 @@ struct Params {
   int stream_k;         // 1: the k-blocks of all work items are dealt out evenly over the CTAs
   int* sk_flags;        // [grid] number of epilogue warps that have stored CTA c's partial tile
   float* sk_slots;      // [grid][256 columns][128 lanes] fp32 partial accumulators
+  int balanced;         // weight rows on MMA-M only: the output features of all (expert, token tile,
+                        // K slice) panels are dealt out evenly over the working CTAs in units of 8
+                        // rows, so that every SM streams the same number of weight bytes
+                        // (feat_tiles is 1 then: a work "item" of the prefix table is a panel)
+  int units_per_panel;  // n_out / 8
+};
+
+// tensor maps over the weights with boxes of 64, 32, 16 and 8 rows: a range of feature
+// rows that is not a whole 128-row tile is fetched as at most four of these
+struct SmallBoxMaps {
+  CUtensorMap m[4];
 };
 
 // ----------------------------------------------------------------------------- PTX wrappers
@@ -72,6 +83,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)),
@@ -198,6 +212,7 @@ __device__ __forceinline__ bool wait_barrier(uint64_t* bar, uint32_t parity, Sha
 
 struct Item {
   int e, row0, row_end, f0, kb0, kb1, ks;
+  int fn;   // feature rows of the item (balanced mode; tile_feat otherwise)
 };
 
 // Maps a work-item index to its tile.  `e` carries over between calls (items
@@ -215,6 +230,7 @@ __device__ __forceinline__ void decode_item(int item, int& e, const int* s_off, 
   it.row0 = s_off[e] + tok * p.tile_tok;
   it.row_end = s_off[e + 1];
   it.f0 = ft * p.tile_feat;
+  it.fn = p.tile_feat;
   it.kb0 = it.ks * p.kb_per_split;
   it.kb1 = min(p.kblocks, it.kb0 + p.kb_per_split);
 }
@@ -234,6 +250,20 @@ struct WorkIter {
     e = 0;
     const int cap = min((int)gridDim.x, p.cta_cap);
     grid = cap;
+    if (p.balanced) {
+      // u counts 8-row units of output features over all panels
+      units = (long long)total_items * p.units_per_panel;
+      // very small problems: at least two units per working CTA
+      if (units < 2ll * grid) grid = (int)(units / 2 > 0 ? units / 2 : 1);
+      next_item = 0;
+      if ((int)blockIdx.x < grid) {
+        u = (long long)blockIdx.x * units / grid;
+        u_end = (long long)(blockIdx.x + 1) * units / grid;
+      } else {
+        u = u_end = 0;
+      }
+      return;
+    }
     if (!p.stream_k && p.full_rounds && total_items > 0) {
       // whole tiles per CTA: use the smallest grid that needs no more rounds than
       // `cap` CTAs would, so that every round is full (896 items -> 7 rounds of
@@ -252,6 +282,34 @@ struct WorkIter {
   }
   __device__ __forceinline__ bool next(const Params& p, int total_items, const int* s_off,
                                        const int* s_prefix, Item& it, int& item) {
+    if (p.balanced) {
+      if (u >= u_end) return false;
+      const int upp = p.units_per_panel;
+      const int panel = (int)(u / upp);
+      const int within = (int)(u - (long long)panel * upp);
+      while (panel >= s_prefix[e + 1]) ++e;
+      const int local = panel - s_prefix[e];
+      const int rows = s_off[e + 1] - s_off[e];
+      const int ntt = (rows + p.tile_tok - 1) / p.tile_tok;
+      const int tok = local % ntt;
+      it.ks = local / ntt;
+      it.e = e;
+      it.row0 = s_off[e] + tok * p.tile_tok;
+      it.row_end = s_off[e + 1];
+      it.kb0 = it.ks * p.kb_per_split;
+      it.kb1 = min(p.kblocks, it.kb0 + p.kb_per_split);
+      // my units of this panel, cut into pieces of at most 16 units (128 rows) of
+      // nearly equal size
+      const long long panel_end = (long long)(panel + 1) * upp;
+      const int seg = (int)((u_end < panel_end ? u_end : panel_end) - u);
+      const int pieces = (seg + 15) / 16;
+      const int take = (seg + pieces - 1) / pieces;
+      it.f0 = within * 8;
+      it.fn = take * 8;
+      item = panel;
+      u += take;
+      return true;
+    }
     if (p.stream_k) {
       if (u >= u_end) return false;
       item = (int)(u / p.kblocks);

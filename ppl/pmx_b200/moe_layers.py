@@ -13,6 +13,8 @@ order and moves k times fewer bytes over NVLink.
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 import torch.distributed as dist
 from torch import nn
@@ -21,8 +23,82 @@ from . import torch_function as OPMX
 from .torch_function.moe import moe_grouped_linear, moe_route_select, moe_norm_route_select
 
 
+# set to True to wrap the stages of MoeFeedForward in NVTX ranges (visible in a profiler
+# timeline; a few host microseconds per eager call, nothing in a replayed CUDA graph)
+NVTX = False
+
+
+def _range(name: str):
+    return torch.cuda.nvtx.range(name) if NVTX else contextlib.nullcontext()
+
+
 def _world(proc_group) -> int:
     return 1 if proc_group is None else proc_group.size()
+
+
+class Linear(nn.Module):
+    """weight [out_features, in_features] (ModelLayers.py:51-69)."""
+
+    def __init__(self, in_features: int, out_features: int, bias_term: bool = True) -> None:
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.weight = nn.Parameter(torch.ones(out_features, in_features))
+        if bias_term:
+            self.bias = nn.Parameter(torch.zeros(out_features))
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, X: torch.Tensor):
+        return OPMX.linear(X, self.weight, self.bias, self.in_features, self.out_features)
+
+
+class ColumnParallelLinear(nn.Module):
+    """weight [out_features/tp, in_features] (ModelParallel.py:61-92)."""
+
+    def __init__(self, proc_group, in_features: int, out_features: int, bias_term: bool = True,
+                 gather_output: bool = True) -> None:
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.gather_output = gather_output
+        self.proc_group = proc_group
+        world_size = _world(proc_group)
+        assert out_features % world_size == 0, "{} is not divisible by {}".format(out_features, world_size)
+        self.out_features_per_partition = out_features // world_size
+        self.weight = nn.Parameter(torch.ones(self.out_features_per_partition, in_features))
+        if bias_term:
+            self.bias = nn.Parameter(torch.zeros(self.out_features_per_partition))
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, X: torch.Tensor):
+        return OPMX.column_parallel_linear(X, self.weight, self.bias, self.proc_group, self.in_features,
+                                           self.out_features, self.gather_output)
+
+
+class RowParallelLinear(nn.Module):
+    """weight [out_features, in_features/tp] (ModelParallel.py:95-124)."""
+
+    def __init__(self, proc_group, in_features: int, out_features: int, bias_term: bool = True,
+                 input_is_parallel: bool = False) -> None:
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.input_is_parallel = input_is_parallel
+        self.proc_group = proc_group
+        world_size = _world(proc_group)
+        assert in_features % world_size == 0, "{} is not divisible by {}".format(in_features, world_size)
+        self.in_features_per_partition = in_features // world_size
+        self.weight = nn.Parameter(torch.ones(out_features, self.in_features_per_partition))
+        if bias_term:
+            self.bias = nn.Parameter(torch.zeros(out_features))
+        else:
+            self.register_parameter("bias", None)
+
+    def forward(self, X: torch.Tensor):
+        return OPMX.row_parallel_linear(X, self.weight, self.bias, self.proc_group, self.in_features,
+                                        self.out_features, self.input_is_parallel)
 
 
 class MoeColumnParallelLinear(nn.Module):
@@ -87,7 +163,7 @@ class MoeFeedForward(nn.Module):
 
     def __init__(self, hidden_dim: int, intermediate_dim: int, num_experts: int,
                  num_experts_per_token: int, proc_group=None, linear_bias_term: bool = False,
-                 fused: bool = True, peer_reduce_tokens: int = 0) -> None:
+                 fused: bool = True, peer_reduce_tokens: int = 0, peer_algorithm: str = "auto") -> None:
         super().__init__()
         self.num_experts = num_experts
         self.num_experts_per_token = num_experts_per_token
@@ -97,8 +173,10 @@ class MoeFeedForward(nn.Module):
         # peer_reduce_tokens > 0: for up to that many tokens the combine and the
         # all-reduce run as one kernel over NVLink peer memory (set up on first use)
         self.peer_reduce_tokens = peer_reduce_tokens
+        self.peer_algorithm = peer_algorithm
         self._peer = None
-        self.gate = nn.Linear(hidden_dim, num_experts, bias=False)
+        self._last_workspaces = ()     # status words of the last step's expert GEMMs, for check()
+        self.gate = Linear(hidden_dim, num_experts, bias_term=False)
         self.wu = MoeColumnParallelLinear(proc_group, num_experts, hidden_dim, 2 * intermediate_dim,
                                           bias_term=linear_bias_term, gather_output=False)
         self.w2 = MoeRowParallelLinear(proc_group, num_experts, intermediate_dim, hidden_dim,
@@ -125,14 +203,15 @@ class MoeFeedForward(nn.Module):
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor | None = None) -> torch.Tensor:
         E, k = self.num_experts, self.num_experts_per_token
         routed = None
-        if router_logits is None and self.fused:
-            routed = moe_route_select(x, self.gate.weight, E, k)     # decode-size batches: one launch
-        if routed is not None:
-            _, x_experts, expert_weights, invert_permutation, expert_offset = routed
-        else:
-            if router_logits is None:
-                router_logits = torch.nn.functional.linear(x, self.gate.weight)
-            x_experts, expert_weights, invert_permutation, expert_offset = OPMX.moe_select(x, router_logits, E, k)
+        with _range("moe.route_select"):
+            if router_logits is None and self.fused:
+                routed = moe_route_select(x, self.gate.weight, E, k)     # decode-size batches: one launch
+            if routed is not None:
+                _, x_experts, expert_weights, invert_permutation, expert_offset = routed
+            else:
+                if router_logits is None:
+                    router_logits = OPMX.router_gate(x, self.gate.weight)
+                x_experts, expert_weights, invert_permutation, expert_offset = OPMX.moe_select(x, router_logits, E, k)
         if not self.fused:
             x13 = OPMX.swiglu(self.wu(x_experts, expert_offset))
             x_out = self.w2(x13, expert_offset)
@@ -144,29 +223,61 @@ class MoeFeedForward(nn.Module):
         k = self.num_experts_per_token
         world = _world(self.proc_group)
         flat = x_experts.view(-1, self.hidden_dim)
-        h = moe_grouped_linear(flat, expert_offset, self.wu.weight, self.wu.bias, swiglu=True,
-                               zero_outside=False)
+        with _range("moe.gate_up_swiglu"):
+            h, ws1 = moe_grouped_linear(flat, expert_offset, self.wu.weight, self.wu.bias, swiglu=True,
+                                        zero_outside=False, return_workspace=True)
         bias2 = self.w2.bias
         if bias2 is not None and world > 1 and dist.get_rank(group=self.proc_group) != 0:
             bias2 = None
-        y = moe_grouped_linear(h, expert_offset, self.w2.weight, bias2, zero_outside=False)
-        if world > 1 and self.peer_reduce_tokens > 0:
-            if self._peer is None:
-                from .peer_reduce import PeerCombine
-                self._peer = PeerCombine(self.proc_group, self.peer_reduce_tokens, self.hidden_dim, y.dtype, y.device)
-            if self._peer.fits(expert_weights.numel() // k, self.hidden_dim, y.dtype):
-                return self._peer.combine_allreduce(y, expert_weights, invert_permutation, k)
-        out = OPMX.moe_reduce(y.view(*expert_weights.shape, -1), expert_weights, invert_permutation, k)
-        if world > 1:
-            dist.all_reduce(out, group=self.proc_group)
+        with _range("moe.down"):
+            y, ws2 = moe_grouped_linear(h, expert_offset, self.w2.weight, bias2, zero_outside=False,
+                                        return_workspace=True)
+        self._last_workspaces = (ws1, ws2)
+        with _range("moe.combine_allreduce"):
+            if world > 1 and self.peer_reduce_tokens > 0:
+                if self._peer is None:
+                    from .peer_reduce import PeerCombine
+                    self._peer = PeerCombine(self.proc_group, self.peer_reduce_tokens, self.hidden_dim, y.dtype,
+                                             y.device, algorithm=self.peer_algorithm)
+                if self._peer.fits(expert_weights.numel() // k, self.hidden_dim, y.dtype):
+                    return self._peer.combine_allreduce(y, expert_weights, invert_permutation, k)
+            out = OPMX.moe_reduce(y.view(*expert_weights.shape, -1), expert_weights, invert_permutation, k)
+            if world > 1:
+                dist.all_reduce(out, group=self.proc_group)
         return out
 
+    def check(self) -> None:
+        """Synchronises the device and raises (PmxError, status -6) if a kernel of the last
+        step recorded a bounded wait that ran out: a pipeline barrier inside an expert GEMM,
+        the grid barrier of the one-launch router + select, or a wait for a peer in the fused
+        combine + all-reduce.  Without this call such a failure leaves undefined (GEMMs,
+        select) or zero (all-reduce) rows behind silently; call it at step boundaries, or
+        every N steps.  Not for use inside a CUDA graph capture."""
+        from .torch_function.moe import grouped_linear_check, route_select_check
+        for ws in self._last_workspaces:
+            if ws is not None:
+                grouped_linear_check(ws)
+        route_select_check(device=self.gate.weight.device)
+        if self._peer is not None:
+            self._peer.check()
 
-def patch_reference(opmx_module) -> None:
-    """Rebind the MoE entry points of an imported OPMX `torch_function` module
-    (the reference resolves them through that module at call time,
-    Model.py:191-211 and ModelParallel.py:156,193) and of the normalisation in front of
-    the block (ModelLayers.py:36-49) to this implementation."""
-    for name in ("moe_select", "moe_column_parallel_linear", "moe_row_parallel_linear", "moe_reduce",
-                 "swiglu", "silu", "rms_norm", "skip_rms_norm"):
+
+PATCHED_NAMES = ("moe_select", "moe_column_parallel_linear", "moe_row_parallel_linear", "moe_reduce",
+                 "swiglu", "silu", "rms_norm", "skip_rms_norm",
+                 "linear", "column_parallel_linear", "row_parallel_linear")
+
+
+def patch_reference(opmx_module, names=PATCHED_NAMES) -> dict:
+    """Rebind operators of an imported OPMX `torch_function` module to this implementation:
+    the MoE entry points (the reference resolves them through that module at call time,
+    Model.py:191-211 and ModelParallel.py:156,193), the normalisation in front of the block
+    (ModelLayers.py:36-49) and the dense linears around it (ModelLayers.py:69,
+    ModelParallel.py:89,121).  Returns {name: original function} so the caller can undo it
+    (`for n, f in saved.items(): setattr(opmx_module, n, f)`)."""
+    saved = {}
+    for name in names:
+        if name not in PATCHED_NAMES:
+            raise ValueError(f"{name} is not an operator this package replaces")
+        saved[name] = getattr(opmx_module, name)
         setattr(opmx_module, name, getattr(OPMX, name))
+    return saved

@@ -103,13 +103,42 @@ def moe_select(X: torch.Tensor, scores: torch.Tensor, num_experts: int, num_expe
     return MoeSelect.apply(X, scores, num_experts, num_experts_per_token)
 
 
-def moe_route_select(X: torch.Tensor, W_router: torch.Tensor, num_experts: int, num_experts_per_token: int):
+def _route_select_workspace(nbytes: int, dev, given):
+    if given is None:
+        return _cabi.barrier_workspace(nbytes, dev)
+    if given.device != dev or given.numel() * given.element_size() < nbytes:
+        raise ValueError(f"workspace must hold {nbytes} bytes on {dev} (first 64 bytes zero before its first use)")
+    return given
+
+
+def route_select_check(workspace: torch.Tensor | None = None, device=None) -> None:
+    """Synchronises and raises if the grid barrier of an earlier moe_route_select /
+    moe_norm_route_select call on this workspace (default: the device's own) gave up;
+    the barrier words are cleared so that the next call starts clean."""
+    if workspace is not None:
+        ws = workspace
+    else:
+        index = torch.device(device).index if device is not None else None
+        ws = _cabi._barrier_ws.get(torch.cuda.current_device() if index is None else index)
+    if ws is None:
+        return
+    with torch.cuda.device(ws.device):
+        status = lib.pmx_moe_route_select_check(ptr(ws), stream_of(ws))
+        if status != 0:
+            text = lib.pmx_moe_last_error().decode()
+            ws[:64].zero_()
+            raise _cabi.PmxError(status, text)
+
+
+def moe_route_select(X: torch.Tensor, W_router: torch.Tensor, num_experts: int, num_experts_per_token: int,
+                     workspace: torch.Tensor | None = None):
     """Router gate and moe_select in one launch for decode-size batches:
     scores = X @ W_router.T (Linear.py:24-33 as called at Model.py:188), then
     MoeSelect (MoeSelect.py:36-64) on those scores.
     -> (scores [*,E], X_expand_permute, expert_weights, invert_permutation, expert_offset),
     or None when the shape is outside what the fused kernel covers (more than 1024
-    tokens, more than 64 experts, ...): call a linear and moe_select then."""
+    tokens, more than 64 experts, ...): call a linear and moe_select then.
+    `workspace`: see _cabi.barrier_workspace (default: one kept buffer per device)."""
     _require_cuda("moe_route_select", X=X, W_router=W_router)
     k, E = int(num_experts_per_token), int(num_experts)
     lead, H = tuple(X.shape[:-1]), X.shape[-1]
@@ -130,7 +159,7 @@ def moe_route_select(X: torch.Tensor, W_router: torch.Tensor, num_experts: int, 
     w = torch.empty(*lead, k, dtype=X.dtype, device=dev)
     inv = torch.empty(*lead, k, dtype=torch.int64, device=dev)
     off = torch.empty(E + 1, dtype=torch.int64, device=dev)
-    ws = workspace(nbytes, dev)
+    ws = _route_select_workspace(nbytes, dev, workspace)
     with torch.cuda.device(dev):
         check(lib.pmx_moe_route_select(ptr(x2), ptr(wr), ptr(scores), ptr(xp), ptr(w), ptr(inv), ptr(off), T, H,
                                        E, k, code, ptr(ws), ws.numel(), stream_of(X)))
@@ -138,7 +167,8 @@ def moe_route_select(X: torch.Tensor, W_router: torch.Tensor, num_experts: int, 
 
 
 def moe_norm_route_select(X: torch.Tensor, SkipIn: torch.Tensor | None, norm_weight: torch.Tensor, eps: float,
-                          W_router: torch.Tensor, num_experts: int, num_experts_per_token: int):
+                          W_router: torch.Tensor, num_experts: int, num_experts_per_token: int,
+                          workspace: torch.Tensor | None = None):
     """skip_rms_norm -> router gate -> moe_select in one launch for decode-size batches
     (RMSNorm.py:42-56, Linear.py:24-33 and MoeSelect.py:36-64 as called at Model.py:261,188,191).
     -> (SkipOut, scores, X_expand_permute, expert_weights, invert_permutation, expert_offset),
@@ -169,7 +199,7 @@ def moe_norm_route_select(X: torch.Tensor, SkipIn: torch.Tensor | None, norm_wei
     w = torch.empty(*lead, k, dtype=X.dtype, device=dev)
     inv = torch.empty(*lead, k, dtype=torch.int64, device=dev)
     off = torch.empty(E + 1, dtype=torch.int64, device=dev)
-    ws = workspace(nbytes, dev)
+    ws = _route_select_workspace(nbytes, dev, workspace)
     with torch.cuda.device(dev):
         check(lib.pmx_moe_norm_route_select(ptr(x2), ptr(s2), ptr(norm_weight.contiguous()), float(eps),
                                             ptr(W_router.contiguous()), ptr(skip_out), ptr(scores), ptr(xp), ptr(w),
@@ -186,6 +216,7 @@ def moe_grouped_linear(X: torch.Tensor, expert_offset: torch.Tensor, W: torch.Te
 
     X [*,K], W [E,N,K], B [E,N] or None -> Y [*,N]; with swiglu=True W holds the
     gate rows then the up rows and Y is [*,N/2] = up * gate * sigmoid(beta*gate).
+    expert_offset=None (E == 1 only): the one expert owns all rows, a dense linear.
     The shared core of moe_column_parallel_linear and moe_row_parallel_linear
     (the loops at MoeColumnParallelLinear.py:61-67 and MoeRowParallelLinear.py:47-53).
     """
@@ -212,7 +243,9 @@ def moe_grouped_linear(X: torch.Tensor, expert_offset: torch.Tensor, W: torch.Te
     x2 = X.contiguous().view(M, K)
     w = W.contiguous()
     b = B.contiguous() if B is not None else None
-    off = _offsets_on(expert_offset, dev, E)
+    if expert_offset is None and E != 1:
+        raise ValueError("expert_offset may be None only for a single expert")
+    off = _offsets_on(expert_offset, dev, E) if expert_offset is not None else None
     epi = _cabi.EPILOGUE_SWIGLU if swiglu else _cabi.EPILOGUE_NONE
     plan_ref = C.byref(plan) if plan is not None else None
     nbytes = lib.pmx_moe_grouped_linear_workspace_bytes(M, N, K, E, code, epi, plan_ref)

@@ -19,7 +19,11 @@ def test_reference_arm_prints_one_contract_line():
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and d["metric"] == "moe_layer_tokens_per_s" and d["unit"] == "tokens/s"
     assert d["higher_is_better"] is True and d["value"] > 0 and d["steps"] == 2
-    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["sample"]
+    import oracle
+    # the unmodified reference operators when they are staged, the port otherwise
+    assert d["cpu_baseline"]["kind"] == ("reference" if oracle.ref_path() else "port")
+    assert d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["sample"]
+    assert d["warmup"] == 3 and d["config"]["parallelism"] == "tp1"
     assert d["e2e"] == {"value": d["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert d["config"]["workload"] == "small_f32"
 

@@ -44,7 +44,7 @@ def test_full_size_routing_is_bit_exact_and_round_trips(F, wl):
     np.testing.assert_allclose(host(back), host(xd), atol=ATOL, rtol=RTOL)
 
 
-@pytest.mark.parametrize("wl", ["decode_t64", "prefill"])
+@pytest.mark.parametrize("wl", ["decode_t64", "prefill", "finegrained", "finegrained_empty"])
 def test_full_size_expert_gemms_on_sampled_rows(F, wl):
     """Both grouped GEMMs of the Mixtral layer at full size: sampled rows of every expert
     against fp32 matmuls on the same device, and linearity of the down projection."""

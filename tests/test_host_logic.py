@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol(lib):
     raw = C.CDLL(os.path.join(ROOT, "ppl", "pmx_b200", "libpmx_moe_b200.so"))
     for n in names:
         assert hasattr(raw, n), f"{n} declared in pmx_moe.h but not exported"
-    assert lib.pmx_moe_abi_version() == 1
+    assert lib.pmx_moe_abi_version() == 2
     assert lib.pmx_moe_status_string(-4) == b"workspace missing or too small"
 
 
@@ -40,9 +40,12 @@ def test_workspace_sizes_and_argument_errors_without_a_gpu(lib):
     n = lib.pmx_moe_select_workspace_bytes(8192, 8, 2)
     assert n >= 8192 * 2 * 4 and n % 16 == 0
     # Mixtral down projection: 64 tokens -> enough work items, status words only;
-    # one token (2 rows) -> K is sliced: fp32 partial sums + status words
+    # one token (2 rows): the feature rows are dealt out in 8-row units, still enough
+    # units for every SM; with whole 128-row tiles K is sliced: fp32 partial sums + status words
     assert lib.pmx_moe_grouped_linear_workspace_bytes(128, 4096, 14336, 8, 0, 0, None) == 256
-    ws = lib.pmx_moe_grouped_linear_workspace_bytes(2, 4096, 14336, 8, 0, 0, None)
+    assert lib.pmx_moe_grouped_linear_workspace_bytes(2, 4096, 14336, 8, 0, 0, None) == 256
+    whole = GemmPlan(balance=2)
+    ws = lib.pmx_moe_grouped_linear_workspace_bytes(2, 4096, 14336, 8, 0, 0, C.byref(whole))
     assert ws > 256 and (ws - 256) % (2 * 4096 * 4) == 0
     assert lib.pmx_moe_grouped_linear_workspace_bytes(128, 4096, 14336, 8, 2, 0, None) == 256   # fp32 -> CUDA cores
     assert lib.pmx_moe_grouped_linear_workspace_bytes(128, 4097, 64, 8, 0, 1, None) == 0        # odd N with SwiGLU
@@ -72,10 +75,13 @@ def test_workspace_sizes_and_argument_errors_without_a_gpu(lib):
     assert lib.pmx_moe_norm_route_select(one, None, None, 1e-5, one, None, one, one, one, one, one, 8, 64, 8, 2, 0,
                                          one, 1 << 20, None) == -1                    # norm weight missing
     assert lib.pmx_skip_rms_norm(one, one, one, one, None, 4, 64, 1e-5, 0, None) == -1  # skip without skip_out
-    assert lib.pmx_moe_reduce_allreduce_buffer_bytes(64, 4096, 0) == 16384 + 2 * 64 * 4096 * 2
+    # exchange buffer: 16 KB of control + two areas of one 32-byte slot per 16-byte item (+ 8 warps of slack)
+    assert lib.pmx_moe_reduce_allreduce_buffer_bytes(64, 4096, 0) == 16384 + 2 * (64 * 4096 // 8 + 256) * 32
     table = (C.c_void_p * 9)(*([16] * 9))
-    assert lib.pmx_moe_reduce_allreduce(one, one, one, one, 4, 2, 64, 0, table, 0, 9, 1 << 30, None) == -1  # > 8 ranks
-    assert lib.pmx_moe_reduce_allreduce(one, one, one, one, 4, 2, 64, 0, table, 0, 2, 64, None) == -4      # small buffers
+    assert lib.pmx_moe_reduce_allreduce(one, one, one, one, 4, 2, 64, 0, table, 0, 9, 1 << 30, 0, 0, 0, None) == -1  # > 8 ranks
+    assert lib.pmx_moe_reduce_allreduce(one, one, one, one, 4, 2, 64, 0, table, 0, 2, 64, 0, 0, 0, None) == -4      # small buffers
+    assert lib.pmx_moe_reduce_allreduce(one, one, one, one, 4, 2, 64, 0, table, 0, 2, 1 << 30, 7, 0, 0, None) == -1  # unknown algorithm
+    assert lib.pmx_moe_set_programmatic_launch(1) in (0, 1)
 
 
 def test_operators_refuse_cpu_tensors():
@@ -220,3 +226,32 @@ def test_workloads_detie_and_algorithmic_work():
     _, _, sc, _ = W.make_activations(fg)
     _, _, _, off = orc.moe_select(np.zeros((fg.T, 1), np.float32), sc.float().numpy(), fg.E, fg.k)
     assert int((np.diff(off) == 0).sum()) == 8
+
+
+def test_patch_reference_rebinds_exactly_the_replaced_operators():
+    """patch_reference() swaps the operators this package replaces into an imported OPMX
+    `torch_function` module (the staged, unmodified reference), leaves every other
+    attribute alone, and its return value undoes it."""
+    import oracle
+    if oracle.ref_path() is None:
+        pytest.skip("the OPMX reference is not staged (python oracle/make_ref.py)")
+    import ppl.pmx_b200.torch_function as F
+    from ppl.pmx_b200.moe_layers import patch_reference, PATCHED_NAMES
+    opmx = oracle.import_reference()
+    before = dict(vars(opmx))
+    saved = patch_reference(opmx)
+    try:
+        assert set(saved) == set(PATCHED_NAMES) == {
+            "moe_select", "moe_column_parallel_linear", "moe_row_parallel_linear", "moe_reduce", "swiglu", "silu",
+            "rms_norm", "skip_rms_norm", "linear", "column_parallel_linear", "row_parallel_linear"}
+        for name, value in vars(opmx).items():
+            if name in PATCHED_NAMES:
+                assert value is getattr(F, name) and value is not before[name]
+            else:
+                assert value is before[name], f"{name} must not be touched"
+        with pytest.raises(ValueError):
+            patch_reference(opmx, names=("multi_head_attention",))
+    finally:
+        for name, fn in saved.items():
+            setattr(opmx, name, fn)
+    assert all(getattr(opmx, n) is before[n] for n in PATCHED_NAMES)

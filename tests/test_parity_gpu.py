@@ -334,7 +334,7 @@ def test_grouped_linear_tilings(F, tile):
 @pytest.mark.parametrize("plan", [dict(kernel=2, stream_k=1), dict(kernel=2, stream_k=2), dict(kernel=1, stream_k=1),
                                   dict(kernel=2, stream_k=1, max_ctas=7), dict(kernel=2, stream_k=1, max_ctas=97),
                                   dict(kernel=1, stream_k=1, max_ctas=5, tile_feat=64),
-                                  dict(kernel=2, stream_k=1, tile_tok=16, stages=2)])
+                                  dict(kernel=2, stream_k=1, tile_tok=16, stages=8)])
 @pytest.mark.parametrize("swiglu", [False, True])
 def test_grouped_linear_stream_k(F, plan, swiglu):
     """k-blocks dealt out evenly over the CTAs: tiles cut at arbitrary k are finished by
@@ -343,6 +343,28 @@ def test_grouped_linear_stream_k(F, plan, swiglu):
     for M, N, K, E in ((40, 512, 1024, 8), (3, 256, 4096, 8), (300, 384, 192, 4), (64, 1024, 64, 8)):
         run_linear(F, rng, M, N, K, E, "f16", plan=plan, bias=True, swiglu=swiglu)
     run_linear(F, rng, 130, 256, 2048, 6, "bf16", plan=plan, swiglu=swiglu)
+
+
+def test_grouped_linear_stream_k_needs_one_cta_per_sm(F):
+    """A stream-K plan whose shared-memory ring is so small that two CTAs would share an
+    SM is refused (its CTAs wait for one another and must all be resident)."""
+    from ppl.pmx_b200._cabi import PmxError
+    with pytest.raises(PmxError):
+        run_linear(F, np.random.default_rng(0), 40, 512, 1024, 8, "f16", plan=dict(kernel=2, stream_k=1, tile_tok=16, stages=2))
+
+
+@pytest.mark.parametrize("plan", [dict(kernel=2), dict(kernel=2, balance=2), dict(kernel=2, cta_cap=5),
+                                  dict(kernel=2, max_ctas=37), dict(kernel=2, tile_tok=16, cta_cap=148),
+                                  dict(kernel=2, split_k=3), dict(kernel=2, balance=2, full_rounds=2, cta_cap=100)])
+@pytest.mark.parametrize("swiglu", [False, True])
+def test_grouped_linear_even_row_dealing(F, plan, swiglu):
+    """Weight rows on MMA-M: the feature rows of all (expert, token tile) panels are dealt
+    out in 8-row units, so items are ranges of 8..128 rows fetched as boxes of 64/32/16/8
+    rows that may start anywhere; against whole 128-row tiles (balance=2)."""
+    rng = np.random.default_rng(len(str(plan)) + swiglu)
+    for M, N, K, E in ((40, 512, 1024, 8), (3, 3584, 512, 8), (300, 384, 192, 4), (64, 1040, 64, 8), (130, 2064, 320, 6)):
+        run_linear(F, rng, M, N, K, E, "f16", plan=plan, bias=True, swiglu=swiglu)
+    run_linear(F, rng, 70, 1808, 2048, 8, "bf16", plan=plan, swiglu=swiglu, off=ragged_offsets(rng, 70, 8, empty=3))
 
 
 def test_grouped_linear_auto_plan_and_fp32(F):
@@ -354,6 +376,29 @@ def test_grouped_linear_auto_plan_and_fp32(F):
     run_linear(F, rng, 50, 100, 36, 4, "f16")            # N, K not multiples of 8 -> CUDA-core kernel
     run_linear(F, rng, 130, 96, 200, 6, "f32", bias=True)
     run_linear(F, rng, 130, 96, 200, 6, "f32", swiglu=True)
+
+
+@pytest.mark.parametrize("M,N,K,dtype", [(64, 4096, 4096, "f16"), (1, 6144, 4096, "f16"), (300, 520, 192, "bf16"),
+                                         (4096, 8, 4096, "bf16"), (2500, 64, 2048, "f16"), (3000, 1024, 512, "bf16"),
+                                         (70, 100, 36, "f16"), (33, 96, 200, "f32")])
+def test_dense_linears(F, M, N, K, dtype):
+    """linear / column_parallel_linear / row_parallel_linear without a process group (the
+    grouped kernel with one expert and no offset table) against the oracle's matrix product:
+    attention projections at decode and prefill sizes, the router gate for large batches
+    (N = 8 and 64), odd shapes and fp32 on the CUDA-core kernel."""
+    rng = np.random.default_rng(M + N + K)
+    x = orc.round_to_dtype(rng.standard_normal((M, K)).astype(np.float32), dtype)
+    w = orc.round_to_dtype((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32), dtype)
+    b = orc.round_to_dtype(rng.standard_normal(N).astype(np.float32), dtype)
+    ref = orc.moe_grouped_linear(x, np.array([0, M]), w[None], None)
+    xd, wd, bd = dev(x, dtype), dev(w, dtype), dev(b, dtype)
+    assert_close(F.linear(xd, wd, None, K, N), ref, dtype)
+    assert_close(F.linear(xd.view(1, M, K), wd, bd, K, N).view(M, N), ref + b, dtype)
+    assert_close(F.column_parallel_linear(xd, wd, bd, None, K, N, True), ref + b, dtype)
+    assert_close(F.row_parallel_linear(xd, wd, bd, None, K, N, True), ref + b, dtype)
+    assert_close(F.router_gate(xd, wd), ref, dtype)
+    with pytest.raises(Exception):
+        F.row_parallel_linear(xd, wd, None, None, K, N, False)      # the reference raises too
 
 
 def test_grouped_linear_errors(F):
@@ -394,7 +439,8 @@ def test_reduce_shapes(F, T, k, N, dtype):
 
 def test_reduce_allreduce_kernel_with_a_single_rank(F):
     """The fused combine + all-reduce kernel with world = 1 (its exchange buffer is then
-    just local memory): same result as moe_reduce, on consecutive calls (epoch parity)."""
+    just local memory): same result as moe_reduce, on consecutive calls that alternate
+    between the two exchange algorithms."""
     import ctypes as C
     from ppl.pmx_b200._cabi import lib, check, ptr, stream_of
     T, k, N = 70, 2, 512
@@ -409,11 +455,90 @@ def test_reduce_allreduce_kernel_with_a_single_rank(F):
         out = torch.empty(T, N, dtype=torch.float16, device="cuda")
         yd, wd, invd = dev(y, "f16"), dev(w, "f16"), torch.from_numpy(inv).cuda()
         check(lib.pmx_moe_reduce_allreduce(ptr(yd), ptr(wd), ptr(invd), ptr(out), T, k, N, 0, table, 0, 1,
-                                           nbytes, stream_of(out)))
+                                           nbytes, 1 + call % 2, 0, 0, stream_of(out)))
         rec = (C.c_int32 * 4)()
         check(lib.pmx_moe_reduce_allreduce_check(ptr(buf), C.byref(rec), stream_of(out)))
         assert_close(out, orc.moe_reduce(y, w, inv, k), "f16")
         assert torch.equal(out, F.moe_reduce(yd.view(T, k, N), wd, invd, k))
+
+
+def _emulated_allreduce(world, algo, T_seq, N=512, k=2, dtype="f16", T_max=None):
+    """All `world` ranks of the exchange as one cooperative launch on this GPU; returns
+    nothing, asserts every rank's result against the oracle and against each other."""
+    import ctypes as C
+    from ppl.pmx_b200._cabi import lib, check, ptr, DTYPE_CODE
+    tdt = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}[dtype]
+    code = DTYPE_CODE[tdt]
+    nbytes = lib.pmx_moe_reduce_allreduce_buffer_bytes(T_max or max(T_seq), N, code)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    table = (C.c_void_p * world)(*[b.data_ptr() for b in bufs])
+    arr = lambda ts: (C.c_void_p * world)(*[t.data_ptr() for t in ts])
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for call, T in enumerate(T_seq):
+        rng = np.random.default_rng(100 * world + call)
+        w = orc.round_to_dtype(rng.random((T, k)).astype(np.float32), dtype)
+        inv = rng.permutation(T * k).reshape(T, k)
+        ys = [orc.round_to_dtype(rng.standard_normal((T * k, N)).astype(np.float32), dtype) for _ in range(world)]
+        yd = [dev(y, dtype) for y in ys]
+        wd = [dev(w, dtype) for _ in range(world)]
+        invd = [torch.from_numpy(inv).cuda() for _ in range(world)]
+        outs = [torch.full((T, N), float("nan"), dtype=tdt, device="cuda") for _ in range(world)]
+        check(lib.pmx_moe_reduce_allreduce_emulated(arr(yd), arr(wd), arr(invd), arr(outs), T, k, N, code, table, world,
+                                                    nbytes, algo, 0, stream))
+        rec = (C.c_int32 * 4)()
+        for b in bufs:
+            check(lib.pmx_moe_reduce_allreduce_check(ptr(b), C.byref(rec), stream))
+        # partial results are rounded to the tensor type before they are exchanged
+        ref = sum(orc.round_to_dtype(orc.moe_reduce(y, w, inv, k), dtype) for y in ys)
+        for r in range(world):
+            assert_close(outs[r], ref, dtype, f"world={world} algo={algo} call={call} T={T} rank={r}")
+            assert torch.equal(outs[r], outs[0]), "ranks must hold bit-identical sums"
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("algo", [1, 2])
+def test_reduce_allreduce_protocol_with_emulated_ranks(F, world, algo):
+    """The multi-rank exchange protocols (flags, epochs, slot reuse, changing T on one
+    set of buffers) with every rank played by one slice of a single cooperative launch."""
+    _emulated_allreduce(world, algo, [64, 8, 64, 8, 1, 70, 70], T_max=70)
+    _emulated_allreduce(world, algo, [33, 5], N=2048, dtype="bf16")
+    _emulated_allreduce(world, algo, [9, 9], N=64, k=3, dtype="f32")
+
+
+@pytest.mark.parametrize("algo", [1, 2])
+def test_reduce_allreduce_wait_runs_out_and_is_reported(F, algo):
+    """Failure detection without a fault: rank 0 of a 2-rank group runs alone, so its
+    waits on rank 1 (whose buffer nobody writes) run out after the 20 ms limit.  The kernel
+    returns, the check reports who was missing, the rows it could not finish are zero,
+    and after clearing the buffers the next exchange works."""
+    import ctypes as C
+    from ppl.pmx_b200._cabi import lib, check, ptr, stream_of, PmxError
+    T, k, N = 16, 2, 512
+    nbytes = lib.pmx_moe_reduce_allreduce_buffer_bytes(T, N, 0)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    table = (C.c_void_p * 2)(*[b.data_ptr() for b in bufs])
+    rng = np.random.default_rng(0)
+    y = dev(rng.standard_normal((T * k, N)).astype(np.float32), "f16")
+    w = dev(rng.random((T, k)).astype(np.float32), "f16")
+    inv = torch.from_numpy(rng.permutation(T * k).reshape(T, k)).cuda()
+    out = torch.full((T, N), float("nan"), dtype=torch.float16, device="cuda")
+    check(lib.pmx_moe_reduce_allreduce(ptr(y), ptr(w), ptr(inv), ptr(out), T, k, N, 0, table, 0, 2, nbytes, algo, 0,
+                                       20_000_000, stream_of(out)))
+    rec = (C.c_int32 * 4)()
+    status = lib.pmx_moe_reduce_allreduce_check(ptr(bufs[0]), C.byref(rec), stream_of(out))
+    assert status == -6 and rec[0] == 1 and rec[1] == 1, (status, list(rec))
+    assert b"waiting for rank 1" in lib.pmx_moe_last_error()
+    assert not torch.isnan(out).any(), "every row must hold a defined value after a timeout"
+    assert (out == 0).any()
+    # the record is cleared by the check; fresh buffers -> the next exchange is clean
+    assert lib.pmx_moe_reduce_allreduce_check(ptr(bufs[0]), C.byref(rec), stream_of(out)) == 0
+    for b in bufs:
+        b.zero_()
+    one = (C.c_void_p * 1)(bufs[0].data_ptr())
+    check(lib.pmx_moe_reduce_allreduce(ptr(y), ptr(w), ptr(inv), ptr(out), T, k, N, 0, one, 0, 1, nbytes, algo, 0,
+                                       20_000_000, stream_of(out)))
+    check(lib.pmx_moe_reduce_allreduce_check(ptr(bufs[0]), C.byref(rec), stream_of(out)))
+    assert torch.equal(out, F.moe_reduce(y.view(T, k, N), w, inv, k))
 
 
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
@@ -473,8 +598,8 @@ def test_block_golden(F, name, fused):
 
 def test_block_with_its_own_router(F):
     """MoeFeedForward computing the router logits itself (fused router + select for a
-    decode-size batch, cuBLAS linear + moe_select for a large one) against the oracle fed
-    with the scores the block produced."""
+    decode-size batch, the dense-linear kernel + moe_select for a large one) against the
+    oracle fed with the scores the block produced."""
     from ppl.pmx_b200 import workloads as W
     from ppl.pmx_b200.moe_layers import MoeFeedForward
     for wl, kw in (("decode_t64", dict(H=512, I=1024)), ("prefill", dict(T=1500, H=256, I=512))):
@@ -488,7 +613,7 @@ def test_block_with_its_own_router(F):
             blk.w2.weight.copy_(w2)
             out = blk(x.cuda())
             routed = F.moe_route_select(x.cuda(), blk.gate.weight, sh.E, sh.k)
-            sc = routed[0] if routed is not None else torch.nn.functional.linear(x.cuda(), blk.gate.weight)
+            sc = routed[0] if routed is not None else F.router_gate(x.cuda(), blk.gate.weight)
         r = orc.moe_block(host(x), host(wr), host(wu), host(w2), sh.E, sh.k, sh.dtype, scores=host(sc),
                           round_intermediates=False)
         assert_close(out, r["out"], sh.dtype, wl)
@@ -509,6 +634,44 @@ def test_block_scaled_workloads(F, wl, scale):
         blk.wu.weight.copy_(wu)
         blk.w2.weight.copy_(w2)
         out = blk(x.cuda(), router_logits=sc.cuda())
+    r = orc.moe_block(host(x), host(wr), host(wu), host(w2), sh.E, sh.k, sh.dtype, scores=host(sc),
+                      round_intermediates=False)
+    assert_close(out, r["out"], sh.dtype)
+
+
+@pytest.mark.parametrize("fused_ffn_glu", [True, False])
+def test_reference_moe_block_runs_on_the_patched_operators(F, fused_ffn_glu):
+    """The drop-in claim itself: the reference's own MoeFeedForward module
+    (model_zoo/mixtral/modeling/dynamic_batching/Model.py:155-214, unmodified, staged under
+    oracle/_ref) is built, the operators are swapped in with patch_reference(), and its
+    output must match the oracle (fp32 math on the same routing)."""
+    import oracle
+    if oracle.ref_path() is None:
+        pytest.skip("the OPMX reference is not staged (python oracle/make_ref.py)")
+    from ppl.pmx_b200 import workloads as W
+    from ppl.pmx_b200.moe_layers import patch_reference
+    opmx, model, ModelParams = oracle.import_reference_mixtral()
+    sh = W.scaled(W.WORKLOADS["decode_t64"], H=512, I=1024, T=48)
+    x, wr, _, _ = W.make_activations(sh)
+    wu, w2 = W.make_expert_weights(sh, "cuda")
+    params = ModelParams(hidden_dim=sh.H, intermediate_dim=sh.I, num_experts=sh.E, num_experts_per_token=sh.k)
+    blk = model.MoeFeedForward(params, 0, fused_ffn_glu, False, None).cuda().half()
+    with torch.no_grad():
+        blk.gate.weight.copy_(wr)
+        if fused_ffn_glu:
+            blk.wu.weight.copy_(wu)
+        else:
+            blk.w1.weight.copy_(wu[:, :sh.I])
+            blk.w3.weight.copy_(wu[:, sh.I:])
+        blk.w2.weight.copy_(w2)
+    saved = patch_reference(opmx)
+    try:
+        with torch.no_grad():
+            out = blk(x.cuda())
+            sc = F.linear(x.cuda(), blk.gate.weight, None, sh.H, sh.E)
+    finally:
+        for name, fn in saved.items():
+            setattr(opmx, name, fn)
     r = orc.moe_block(host(x), host(wr), host(wu), host(w2), sh.E, sh.k, sh.dtype, scores=host(sc),
                       round_intermediates=False)
     assert_close(out, r["out"], sh.dtype)

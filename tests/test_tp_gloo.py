@@ -37,7 +37,8 @@ def _install_cpu_stand_ins():
                                    None if B is None else B.detach().numpy())
         if swiglu:
             y = orc.swiglu(y, beta)
-        return t(y).view(*X.shape[:-1], -1)
+        y = t(y).view(*X.shape[:-1], -1)
+        return (y, None) if return_workspace else y
 
     def select(X, scores, E, k):
         xe, ew, inv, off = orc.moe_select(X.reshape(-1, X.shape[-1]).numpy(), scores.reshape(-1, E).numpy(), E, k)
@@ -114,6 +115,66 @@ def _worker(rank, world, port, q):
         q.put((rank, traceback.format_exc()))
     finally:
         dist.destroy_process_group()
+
+
+def _leaver(rank, world, port, q):
+    """Failure detection on the host side: the ranks run two steps together, then the last
+    rank leaves between steps (no collective of its own in flight).  The others notice in
+    their next collective, which ends with an error after the group's short timeout
+    instead of blocking forever."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        group = dist.new_group(list(range(world)), backend="gloo", timeout=datetime.timedelta(seconds=5))
+        _install_cpu_stand_ins()
+        from ppl.pmx_b200 import workloads as W
+        from ppl.pmx_b200.moe_layers import MoeFeedForward
+        sh = W.scaled(W.WORKLOADS["small_f32"], T=16, H=32, I=96)
+        x, _, sc, _ = W.make_activations(sh)
+        blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, False)
+        u, d = W.make_expert_weights(sh, "cpu", tp_rank=rank, tp_size=world)
+        with torch.no_grad():
+            blk.wu.weight.copy_(u)
+            blk.w2.weight.copy_(d)
+            for _ in range(2):
+                blk(x, router_logits=sc)            # steps with everybody present
+            if rank == world - 1:
+                q.put((rank, "left"))
+                return                                # leaves between steps
+            try:
+                blk(x, router_logits=sc)            # the all-reduce of this step cannot complete
+                q.put((rank, "no error"))
+            except Exception as exc:                  # noqa: BLE001
+                q.put((rank, f"error: {type(exc).__name__}"))
+    except Exception:                                 # noqa: BLE001
+        import traceback
+        q.put((rank, traceback.format_exc()))
+    finally:
+        if rank == world - 1:
+            q.close()
+            q.join_thread()                           # the message is out before the process dies
+            os._exit(0)                               # gone without a clean shutdown, like a crashed rank
+        try:
+            dist.destroy_process_group()
+        except Exception:                             # noqa: BLE001
+            pass
+
+
+def test_a_rank_that_leaves_between_steps_is_detected_on_gloo():
+    world = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    assert results[world - 1] == "left"
+    for r in range(world - 1):
+        assert results[r].startswith("error"), f"rank {r} did not notice the missing rank: {results[r]}"
 
 
 @pytest.mark.parametrize("world", [2, 4])

@@ -39,10 +39,23 @@ def test_static_scratch_select_matches_workspace_select_twice():
     torch.cuda.set_device(0)
     cases = [(5000, 64, 8, 2, torch.float16, 1), (2100, 40, 64, 8, torch.bfloat16, 2)]   # sizes that use the scratch
     for T, H, E, k, dt, seed in cases:
+        # every case must take the three-launch path, the one that uses scratch (the
+        # single-launch path covers up to 1024 tokens and 64 experts and needs none)
+        assert T > 1024 or E > 64
         g = torch.Generator().manual_seed(seed)
         x = torch.randn(T, H, generator=g).to(dt).cuda()
         sc = torch.randn(T, E, generator=g).to(dt).cuda()
         got = _call(True, x, sc, E, k)
+        # the property the entry point exists for: with the outputs already allocated, a
+        # call neither takes device memory from the driver nor from torch's allocator
+        torch.cuda.synchronize()
+        free0, _ = torch.cuda.mem_get_info()
+        torch_allocs0 = torch.cuda.memory_stats()["allocation.all.allocated"]
+        from ppl.pmx_b200._cabi import lib, check, ptr, stream_of, DTYPE_CODE
+        check(lib.pmx_moe_select_static(ptr(x), ptr(sc), *(ptr(o) for o in got), T, H, E, k, DTYPE_CODE[dt], stream_of(x)))
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_stats()["allocation.all.allocated"] == torch_allocs0
+        assert torch.cuda.mem_get_info()[0] == free0, "device memory changed around pmx_moe_select_static"
         want = _call(False, x, sc, E, k)
         for a, b, name in zip(got, want, ("x_expand_permute", "expert_weights", "invert_permutation", "expert_offset")):
             assert torch.equal(a, b), f"{name} differs between the two entry points (T={T}, E={E}, k={k})"
