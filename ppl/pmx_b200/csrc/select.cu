@@ -624,6 +624,201 @@ bool route_select_geometry(int64_t T, int64_t H, int E, int k, int dtype, RouteS
   return g->nblk <= sms && g->smem <= 200 * 1024;
 }
 
+// ---- one launch for large batches (up to 64 experts) ----------------------------
+// Every block owns `tpb` consecutive tokens: it routes them (a thread per token, the
+// block's scores staged in shared memory), leaves its per-expert counts in global
+// memory, meets the other blocks at one bounded grid-wide barrier (at most one block per
+// SM, so all are resident), adds up the counts of the blocks in front of it, and then
+// places and gathers its own rows.  Positions only depend on the scores (no atomics
+// decide an order), so every tensor-parallel rank computes the same permutation.
+constexpr int kWideChunk = 256;          // tokens routed per pass (one per thread)
+constexpr int kWideMaxTokensPerBlock = 1024;
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256)
+select_wide_kernel(const T* __restrict__ x, const T* __restrict__ scores, int64_t Tn, int64_t H, int E, int k,
+                   int tpb, T* __restrict__ xp, T* __restrict__ weights, int64_t* __restrict__ inv,
+                   int64_t* __restrict__ expert_offset, unsigned int* __restrict__ barrier,
+                   int* __restrict__ block_counts, int* __restrict__ status, unsigned long long wait_ns) {
+  extern __shared__ unsigned int sm_wide[];
+  const int groups = (tpb + 31) / 32;
+  unsigned int* ballots = sm_wide;                                       // [groups][E]
+  int* group_base = reinterpret_cast<int*>(ballots + groups * E);       // [groups][E] tokens of earlier groups
+  int* offs = group_base + groups * E;                                   // [E] first row of this block's slots
+  int* totals = offs + E;                                                // [E] rows of each expert, all blocks
+  int* pos = totals + E;                                                 // [tpb*k]
+  float* srow = reinterpret_cast<float*>(pos + tpb * k);                 // [kWideChunk][E+1] staged scores
+  short* ids = reinterpret_cast<short*>(srow + kWideChunk * (E + 1));    // [groups*32][k]
+  __shared__ int s_abort;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int64_t t0 = (int64_t)blockIdx.x * tpb;
+  const int ntok = (int)min((int64_t)tpb, Tn - t0);
+  if (threadIdx.x == 0) s_abort = 0;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  // A. routing of my tokens, kWideChunk at a time
+  for (int c0 = 0; c0 < groups * 32; c0 += kWideChunk) {
+    const int cn = min(kWideChunk, ntok - c0);       // may be <= 0 for the padding of the last group
+    __syncthreads();
+    for (int i = threadIdx.x; i < cn * E; i += blockDim.x) {
+      const int tl = i / E, e = i - tl * E;
+      srow[tl * (E + 1) + e] = Elem<T>::to_f(scores[(t0 + c0) * E + i]);
+    }
+    __syncthreads();
+    const int tl = c0 + threadIdx.x;                 // token of this thread (its warp = one group)
+    if (tl < groups * 32) {
+      unsigned long long mask = 0ull;
+      if (tl < ntok) {
+        const float* row = srow + threadIdx.x * (E + 1);
+        unsigned long long prev = ~0ull;
+        float vmax = 0.f, denom = 0.f;
+        for (int j = 0; j < k; ++j) {
+          unsigned long long best = 0ull;
+          for (int e = 0; e < E; ++e) {
+            const unsigned long long key = ((unsigned long long)score_key(row[e]) << 32) | (uint32_t)(0x7FFFFFFF - e);
+            if (key < prev && key > best) best = key;
+          }
+          prev = best;
+          const int e_sel = 0x7FFFFFFF - (int)(uint32_t)(best & 0xFFFFFFFFull);
+          ids[tl * k + j] = (short)e_sel;
+          mask |= 1ull << e_sel;
+          if (j == 0) vmax = row[e_sel];
+          denom += expf(row[e_sel] - vmax);
+        }
+        for (int j = 0; j < k; ++j)
+          weights[(t0 + tl) * k + j] = Elem<T>::from_f(expf(row[ids[tl * k + j]] - vmax) / denom);
+      }
+      const int g = tl >> 5;
+      for (int e = 0; e < E; ++e) {
+        const unsigned int b = __ballot_sync(0xFFFFFFFFu, (mask >> e) & 1ull);
+        if (lane == 0) ballots[g * E + e] = b;
+      }
+    }
+  }
+  __syncthreads();
+  // B. per expert: tokens in earlier groups of this block, and the block's count
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int g = 0; g < groups; ++g) {
+      group_base[g * E + e] = run;
+      run += __popc(ballots[g * E + e]);
+    }
+    block_counts[(int64_t)e * gridDim.x + blockIdx.x] = run;
+  }
+  // C. grid-wide barrier (the count word is cleared by a memset node in front of the launch)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(barrier, 1u);
+    unsigned long long t_start = 0;
+    unsigned int it = 0;
+    while (ld_acquire_gpu(barrier) < gridDim.x) {
+      if ((++it & 1023u) == 0u) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (t_start == 0) t_start = now;
+        if (now - t_start > wait_ns) {
+          s_abort = 1;
+          atomicCAS(status, 0, 2);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (s_abort) return;
+  // D. rows of every expert in the blocks in front of me, and in all blocks (a warp per expert)
+  for (int e = warp; e < E; e += nwarps) {
+    int before = 0, total = 0;
+    for (int b = lane; b < (int)gridDim.x; b += 32) {
+      const int c = __ldcg(block_counts + (int64_t)e * gridDim.x + b);
+      total += c;
+      if (b < (int)blockIdx.x) before += c;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      before += __shfl_xor_sync(0xFFFFFFFFu, before, o);
+      total += __shfl_xor_sync(0xFFFFFFFFu, total, o);
+    }
+    if (lane == 0) {
+      offs[e] = before;
+      totals[e] = total;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) {
+      if (blockIdx.x == 0) expert_offset[e] = acc;
+      offs[e] += acc;
+      acc += totals[e];
+    }
+    if (blockIdx.x == 0) expert_offset[E] = acc;
+  }
+  __syncthreads();
+  // E. stable positions of my slots
+  for (int i = threadIdx.x; i < ntok * k; i += blockDim.x) {
+    const int tl = i / k, e = ids[i];
+    const int g = tl >> 5, l = tl & 31;
+    const int p = offs[e] + group_base[g * E + e] + __popc(ballots[g * E + e] & ((1u << l) - 1u));
+    pos[i] = p;
+    inv[t0 * k + i] = p;
+  }
+  __syncthreads();
+  // F. gather my rows: each token row is read once and written to its k destinations
+  if (VEC) {
+    const int chunks = (int)(H * sizeof(T) / 16);
+    const uint4* src = reinterpret_cast<const uint4*>(x + t0 * H);
+    uint4* dst = reinterpret_cast<uint4*>(xp);
+    const int total = ntok * chunks;
+    for (int i0 = threadIdx.x; i0 < total; i0 += 4 * blockDim.x) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < total) v[u] = __ldg(src + i);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < total) {
+          const int tl = i / chunks, c = i - tl * chunks;
+          for (int j = 0; j < k; ++j) dst[(int64_t)pos[tl * k + j] * chunks + c] = v[u];
+        }
+      }
+    }
+  } else {
+    const int64_t total = (int64_t)ntok * H;
+    for (int64_t i = threadIdx.x; i < total; i += blockDim.x) {
+      const int tl = (int)(i / H);
+      const int64_t c = i - (int64_t)tl * H;
+      const T v = x[(t0 + tl) * H + c];
+      for (int j = 0; j < k; ++j) xp[(int64_t)pos[tl * k + j] * H + c] = v;
+    }
+  }
+}
+
+struct WideGeometry {
+  int tpb, nblk;
+  size_t smem;
+};
+
+// One block per SM at most (the blocks wait for one another), at least 32 tokens each.
+bool select_wide_geometry(int64_t T, int E, int k, WideGeometry* g) {
+  if (E > kSmallMaxExperts || k > 32) return false;
+  const int sms = sm_count();
+  int64_t tpb = ceil_div(T, (int64_t)sms);
+  tpb = ceil_div(tpb, 32) * 32;
+  if (tpb > kWideMaxTokensPerBlock) return false;
+  g->tpb = (int)tpb;
+  g->nblk = (int)ceil_div(T, tpb);
+  const size_t groups = (size_t)tpb / 32;
+  g->smem = (groups * E * 2 + 2 * (size_t)E + (size_t)tpb * k + (size_t)kWideChunk * (E + 1)) * 4 +
+            groups * 32 * k * 2 + 16;
+  return g->nblk <= sms && g->smem <= 200 * 1024;
+}
+
 struct SelectGeometry {
   int tpb;
   int nblk;
@@ -650,6 +845,20 @@ template <typename T>
 int run_select(const void* x, const void* scores, void* xp, void* w, int64_t* inv, int64_t* off,
                int64_t Tn, int64_t H, int E, int k, void* ws, cudaStream_t s) {
   if (select_small_applies(Tn, E, k)) return run_select_small<T>(x, scores, xp, w, inv, off, Tn, H, E, k, s);
+  WideGeometry wg;
+  if (select_wide_geometry(Tn, E, k, &wg)) {
+    // scratch: 16 bytes of barrier / status words, then the per-block counts [E][blocks]
+    unsigned int* barrier = reinterpret_cast<unsigned int*>(ws);
+    int* status = reinterpret_cast<int*>(ws) + 2;
+    int* block_counts = reinterpret_cast<int*>(ws) + 4;
+    PMX_CUDA_OK(cudaMemsetAsync(ws, 0, 16, s));
+    const bool vec = (H * sizeof(T)) % 16 == 0 && aligned16(x) && aligned16(xp);
+    auto kern = vec ? select_wide_kernel<T, true> : select_wide_kernel<T, false>;
+    if (wg.smem > 48 * 1024) PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wg.smem));
+    return launch_pdl_k(kern, dim3(wg.nblk), dim3(256), wg.smem, s, reinterpret_cast<const T*>(x),
+                        reinterpret_cast<const T*>(scores), Tn, H, E, k, wg.tpb, reinterpret_cast<T*>(xp),
+                        reinterpret_cast<T*>(w), inv, off, barrier, block_counts, status, 1000000000ull);
+  }
   const SelectGeometry g = select_geometry(Tn, E, k);
   int* ids = reinterpret_cast<int*>(ws);
   int* counts = reinterpret_cast<int*>(reinterpret_cast<char*>(ws) + g.ids_bytes);
