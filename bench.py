@@ -570,6 +570,231 @@ def measure(ctx, shape, steps, warmup, regions, headline):
     return rec
 
 
+# ------------------------------------------------------------------------------ full decoder (config 5)
+DECODER_FULL = dict(hidden_dim=4096, intermediate_dim=14336, num_layers=32, num_heads=32, num_kv_heads=8,
+                    vocab_size=32000, num_experts=8, num_experts_per_token=2)
+
+
+def build_reference_decoder(cfg, proc_group, device, rank, world, dtype=torch.float16, cache_layout=0):
+    """The reference's own Mixtral `Transformer` (model_zoo/mixtral/modeling/dynamic_batching/
+    Model.py:269-359, unmodified, imported from oracle/_ref) on `device`, built the way its
+    loader does (Loader.py:76-91: default tensor type = the model's dtype on the device),
+    with seeded random weights: replicated tensors (norms, router gate) get the same values on
+    every rank, sharded tensors a per-rank seed."""
+    import oracle
+    opmx, model_mod, ModelParams = oracle.import_reference_mixtral()
+    params = ModelParams(norm_eps=1e-5, rope_theta=1e6, cache_quant_bit=0, cache_quant_group=0,
+                         cache_layout=cache_layout, cache_mode=0, **cfg)
+    old_dtype = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    torch.set_default_device(device)
+    try:
+        net = model_mod.Transformer(params, False, True, True, True, False, False, False, 0, proc_group)
+    finally:
+        torch.set_default_device("cpu")
+        torch.set_default_dtype(old_dtype)
+    gen = torch.Generator(device=device)
+    tp = {"wqkv": 1, "wu": 1, "output": 1, "wo": world, "w2": world}      # factor from the shard's to the full fan-in
+    with torch.no_grad():
+        for index, (name, w) in enumerate(net.named_parameters()):
+            if "norm" in name:
+                w.fill_(1.0)
+                continue
+            replicated = ".gate." in name
+            gen.manual_seed(1000003 * (index + 1) + (0 if replicated else 7919 * (rank + 1)))
+            if "tok_embeddings" in name:
+                std = 1.0
+            elif replicated:
+                std = 0.02
+            else:
+                leaf = name.split(".")[-2]
+                std = (w.shape[-1] * tp.get(leaf, 1)) ** -0.5
+            # filled in slices: a whole fp32 temporary of a 29 GB tensor is not needed
+            flat = w.view(-1)
+            for lo in range(0, flat.numel(), 1 << 26):
+                hi = min(flat.numel(), lo + (1 << 26))
+                flat[lo:hi] = torch.randn(hi - lo, generator=gen, device=device, dtype=torch.float32) * std
+    return opmx, model_mod, net
+
+
+def decoder_step_inputs(net, batch, cached, device, world, seed=0):
+    """One decode step (one new token per sequence) over `cached` tokens already in the KV
+    cache of every sequence; tensors as Pipeline.py:130-182 builds them.  The cache is filled
+    with seeded N(0,1) values instead of running a prefill."""
+    p = net.params
+    head_dim = p.hidden_dim // p.num_heads
+    kv_heads = p.num_kv_heads // world
+    cap = cached + 8
+    g = torch.Generator().manual_seed(seed)
+    tokens = torch.randint(0, p.vocab_size, (batch,), generator=g).to(device)
+    seqstarts = torch.arange(0, batch + 1, dtype=torch.int64, device=device)
+    start_pos = torch.full((batch,), cached, dtype=torch.int64, device=device)
+    kvstarts = torch.arange(0, (batch + 1) * (cached + 1), cached + 1, dtype=torch.int64, device=device)
+    cachestarts = torch.arange(0, batch * cap, cap, dtype=torch.int64, device=device)
+    gd = torch.Generator(device=device).manual_seed(seed + 1 + 31 * (torch.distributed.get_rank() if world > 1 else 0))
+    if p.cache_layout == 0:
+        shape = (batch * cap, p.num_layers, 2, kv_heads, head_dim)
+    else:
+        shape = (p.num_layers, 2, kv_heads, batch * cap, head_dim)
+    kv_cache = torch.randn(shape, generator=gd, device=device, dtype=torch.float16)
+    return dict(tokens=tokens, attn_mask=torch.empty(0, dtype=torch.float16), seqstarts=seqstarts, kvstarts=kvstarts,
+                cachestarts=cachestarts, decoding_batches=torch.tensor([batch], dtype=torch.int64),
+                start_pos=start_pos, max_seqlen=torch.tensor([1], dtype=torch.int64),
+                max_kvlen=torch.tensor([cached + 1], dtype=torch.int64), kv_cache=kv_cache)
+
+
+def decoder_forward(net, inp, kv_cache, dtype=torch.float16):
+    """net.forward under the reference's tensor defaults (its operators allocate with them)."""
+    old_dtype = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    torch.set_default_device(kv_cache.device)
+    try:
+        return net.forward(inp["tokens"], inp["attn_mask"], inp["seqstarts"], inp["kvstarts"], inp["cachestarts"],
+                           inp["decoding_batches"], inp["start_pos"], inp["max_seqlen"], inp["max_kvlen"],
+                           kv_cache, None)
+    finally:
+        torch.set_default_device("cpu")
+        torch.set_default_dtype(old_dtype)
+
+
+class MoeTimer:
+    """Wraps feed_forward.forward of every layer with a pair of CUDA events (measurement only)."""
+
+    def __init__(self, net):
+        self.pairs = []
+        self.saved = []
+        for layer in net.layers:
+            ff = layer.feed_forward
+            inner = ff.forward
+            self.saved.append((ff, ff.__dict__.get("forward")))
+
+            def timed_forward(x, _inner=inner):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                y = _inner(x)
+                e1.record()
+                self.pairs.append((e0, e1))
+                return y
+            ff.forward = timed_forward
+
+    def total_ms(self):
+        torch.cuda.synchronize()
+        t = sum(a.elapsed_time(b) for a, b in self.pairs)
+        self.pairs = []
+        return t
+
+    def remove(self):
+        for ff, old in self.saved:
+            if old is None:
+                del ff.forward
+            else:
+                ff.forward = old
+
+
+def run_decoder(ctx, cfg, batch, cached, steps, parity_layers=2):
+    """The full decoder step of the reference model with the operators of this package
+    swapped in.  Three variants share one set of weights: the unmodified reference
+    operators; patch_reference() (every replaced operator, call by call); and in addition
+    the fused MoeFeedForward block in place of the reference block's forward.  Parity: a
+    `parity_layers`-deep copy of the model, same inputs, logits of the variants against the
+    unmodified reference.  Timing: whole step (host clock around the synchronised call:
+    the reference's attention, KV-cache and rotary operators loop over the sequences in
+    Python) and the summed time of the MoE blocks (CUDA events)."""
+    from ppl.pmx_b200.moe_layers import MoeFeedForward, patch_reference
+    world, device = ctx.world, ctx.device
+
+    def make_fused(net):
+        """One fused MoeFeedForward of this package per layer, on the reference module's own
+        parameters; all layers share one exchange buffer for the peer-memory all-reduce."""
+        peer_tokens = 0 if (world == 1 or ctx.args.allreduce == "nccl" or ctx.peer_failed) else max(256, batch)
+        blocks = []
+        for layer in net.layers:
+            ref = layer.feed_forward
+            blk = MoeFeedForward(cfg["hidden_dim"], cfg["intermediate_dim"], cfg["num_experts"],
+                                 cfg["num_experts_per_token"], ctx.group, False, peer_reduce_tokens=peer_tokens,
+                                 peer_algorithm=ctx.args.peer_algo)
+            blk.gate.weight, blk.wu.weight, blk.w2.weight = ref.gate.weight, ref.wu.weight, ref.w2.weight
+            blocks.append(blk)
+        if peer_tokens:
+            from ppl.pmx_b200.peer_reduce import PeerCombine
+            shared = PeerCombine(ctx.group, peer_tokens, cfg["hidden_dim"], torch.float16, device,
+                                 algorithm=ctx.args.peer_algo)
+            for blk in blocks:
+                blk._peer = shared
+        return blocks
+
+    def one_pass(net, opmx, inp, variant, fused, n_steps, timer):
+        saved, undo = {}, []
+        if variant != "reference":
+            saved = patch_reference(opmx)
+        if variant == "fused":
+            for layer, blk in zip(net.layers, fused):
+                undo.append((layer.feed_forward, layer.feed_forward.__dict__.get("forward")))
+                layer.feed_forward.forward = (lambda x, _b=blk: _b(x))
+        moe = MoeTimer(net) if timer else None
+        try:
+            times, logits = [], None
+            for i in range(n_steps):
+                kv = inp["kv_cache"].clone()
+                sync_all(ctx)
+                t0 = time.perf_counter()
+                with torch.no_grad():
+                    logits = decoder_forward(net, inp, kv)
+                torch.cuda.synchronize()
+                times.append(time.perf_counter() - t0)
+                if moe is not None and i == 0:
+                    moe.total_ms()                     # first call: warm-up, drop its events
+            moe_ms = moe.total_ms() / max(1, n_steps - 1) if moe is not None else None
+        finally:
+            if moe is not None:
+                moe.remove()
+            for ff, old in undo:
+                if old is None:
+                    del ff.forward
+                else:
+                    ff.forward = old
+            for name, fn in saved.items():
+                setattr(opmx, name, fn)
+        steady = times[1:] if len(times) > 1 else times
+        return logits, statistics.median(steady) * 1e3, moe_ms
+
+    out = {"config": dict(cfg, batch=batch, cached_tokens=cached, parallelism=f"tp{world}", dtype="f16",
+                          cache_layout=0)}
+    # parity at reduced depth
+    small = dict(cfg, num_layers=parity_layers)
+    opmx, _, net = build_reference_decoder(small, ctx.group, device, ctx.rank, world)
+    inp = decoder_step_inputs(net, batch, cached, device, world)
+    fused = make_fused(net)
+    ref_logits, _, _ = one_pass(net, opmx, inp, "reference", fused, 1, False)
+    par = {}
+    for v in ("patched", "fused"):
+        logits, _, _ = one_pass(net, opmx, inp, v, fused, 1, False)
+        d = (logits.float() - ref_logits.float()).abs()
+        par[v] = {"max_abs_diff_logits": float(d.max()), "mean_abs_logit": float(ref_logits.float().abs().mean()),
+                  "argmax_agree": float((logits.argmax(-1) == ref_logits.argmax(-1)).float().mean())}
+        par[v]["ok"] = bool(par[v]["max_abs_diff_logits"] <= 5e-2 * max(1.0, float(ref_logits.float().abs().max())))
+    out["parity"] = dict(par, layers=parity_layers,
+                         note="logits of one decode step against the unmodified reference operators on the same "
+                              "GPUs; bar: max-abs 5e-2 of the largest logit")
+    del net, fused, inp
+    torch.cuda.empty_cache()
+    # timing at full depth
+    opmx, _, net = build_reference_decoder(cfg, ctx.group, device, ctx.rank, world)
+    inp = decoder_step_inputs(net, batch, cached, device, world)
+    fused = make_fused(net)
+    out["timing"] = {}
+    for v in ("reference", "patched", "fused"):
+        _, ms, moe_ms = one_pass(net, opmx, inp, v, fused, steps + 1, True)
+        out["timing"][v] = {"ms_per_step": ms, "moe_ms_per_step": moe_ms,
+                            "moe_ms_per_layer": moe_ms / cfg["num_layers"] if moe_ms is not None else None,
+                            "tokens_per_s": batch / (ms * 1e-3)}
+    out["timing"]["note"] = ("median host-clock time of a synchronised decode step; the attention, KV-cache and rotary "
+                             "operators are the reference's own (per-sequence Python loops) in all three variants")
+    del net, fused, inp
+    torch.cuda.empty_cache()
+    return out
+
+
 def parse_plan(text):
     from ppl.pmx_b200._cabi import GemmPlan
     if not text:
@@ -597,6 +822,13 @@ def main():
     ap.add_argument("--peer-algo", default="auto", choices=["auto", "push", "pull"])
     ap.add_argument("--gemm-plan", default="", help="pmx_gemm_plan fields for the gate_up / down STAGE timings, "
                                                     "e.g. balance=2,cta_cap=128 (the step itself uses the default plan)")
+    ap.add_argument("--decoder", default="auto", choices=["auto", "on", "off"],
+                    help="also run one decode step of the full Mixtral-8x7B-architecture decoder (the reference model "
+                         "from oracle/_ref with this package's operators swapped in); auto: when N = 8")
+    ap.add_argument("--decoder-scale", type=int, default=1, help="divide the decoder's widths by this (tests)")
+    ap.add_argument("--decoder-layers", type=int, default=32)
+    ap.add_argument("--decoder-batch", type=int, default=64)
+    ap.add_argument("--decoder-cached", type=int, default=2048)
     ap.add_argument("--ffn-div", type=int, default=1,
                     help="divide the ffn size by this (small cases for profiler captures; traffic and flops scale with it)")
     args = ap.parse_args()
@@ -654,6 +886,21 @@ def main():
         if rank == 0:
             extras.append(rec)
 
+    decoder = None
+    import oracle
+    want_decoder = args.decoder == "on" or (args.decoder == "auto" and world == 8 and args.workload == HEADLINE)
+    if want_decoder and oracle.ref_path() is None:
+        decoder = {"unavailable": "the OPMX reference is not staged under oracle/_ref (python oracle/make_ref.py)"}
+    elif want_decoder:
+        ctx.blocks.clear()
+        torch.cuda.empty_cache()
+        sc = args.decoder_scale
+        cfg = dict(DECODER_FULL, num_layers=args.decoder_layers)
+        if sc > 1:
+            cfg.update(hidden_dim=cfg["hidden_dim"] // sc, intermediate_dim=cfg["intermediate_dim"] // sc,
+                       vocab_size=cfg["vocab_size"] // sc)
+        decoder = run_decoder(ctx, cfg, args.decoder_batch, args.decoder_cached, steps=3)
+
     if rank == 0:
         ms_step = head["ms_per_step"]
         line = {
@@ -673,6 +920,8 @@ def main():
             "parity": head["parity"],
             "workloads": extras,
         }
+        if decoder is not None:
+            line["decoder"] = decoder
         if world == 1 and not args.no_cpu_baseline:
             blk = get_block(ctx, shape, full=False)
             x_host, w_router, _, _ = W.make_activations(shape, detie=False)

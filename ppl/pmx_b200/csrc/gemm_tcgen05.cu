@@ -435,20 +435,27 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
     const int64_t act = M < E ? M : E;
     const int64_t tok_tiles = act * (int64_t)ceil_div((int64_t)(avg_rows < 1 ? 1 : avg_rows), pl.tile_tok);
     const int64_t items = tok_tiles * feat_tiles;
-    // balanced: 8-row units are the grain, so K is sliced only when there are fewer
-    // than two units per SM; whole tiles: when there are fewer tiles than half the SMs
-    // (one token, or a thin tensor-parallel shard).  With SwiGLU the kernel then
-    // produces plain [gate | up] partial sums (twice the feature tiles) and the
-    // activation moves into the final sum.  Measured on B200: with more items than
-    // that the extra partial-sum traffic and launch cost more than the better balance gains.
-    const bool slice = pl.balanced ? tok_tiles * (n_out / 8) < 2 * (int64_t)sms : 2 * items <= sms;
+    // Whole tiles: K is sliced when there are fewer tiles than half the SMs (one token, or a
+    // thin tensor-parallel shard).  Evenly dealt rows: a CTA's time is set by its k-block
+    // rounds, and rounds that carry few rows put few bytes in flight, so K is sliced when a
+    // CTA would get at most half a 128-row tile, until it gets about a whole one.  With
+    // SwiGLU the kernel then produces plain [gate | up] partial sums and the activation
+    // moves into the final sum.
+    const int64_t ctas = sms < 128 ? sms : 128;
+    const bool slice = pl.balanced ? 2 * tok_tiles * (n_out / 8) <= 16 * ctas : 2 * items <= sms;
     if (slice) {
-      const int64_t base = pl.balanced ? (tok_tiles * (N / 8) + 15) / 16
-                                       : (swiglu ? tok_tiles * ceil_div(N, pl.tile_feat) : items);
-      int64_t want = ceil_div(2 * sms, base > 0 ? base : 1);
+      int64_t want;
+      if (pl.balanced) {
+        const int64_t units = tok_tiles * (N / 8);
+        want = 16 * ctas / (units > 0 ? units : 1);
+      } else {
+        const int64_t base = swiglu ? tok_tiles * ceil_div(N, pl.tile_feat) : items;
+        want = ceil_div(2 * sms, base);
+      }
       const int64_t cap = kblocks / 8 > 0 ? kblocks / 8 : 1;
       if (want > cap) want = cap;
       if (want > 16) want = 16;
+      if (want < 1) want = 1;
       pl.split_k = (int)want;
     }
   }
@@ -465,16 +472,16 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   const size_t stage = (size_t)(pl.tile_tok + (kernel_swiglu ? 2 : 1) * pl.tile_feat) * 128;
   const size_t fixed = 1024 + sizeof(Shared) + 2 * (size_t)(E + 1) * sizeof(int);
   int st = (int)((227 * 1024 - fixed) / stage);
-  if (st > 8) st = 8;
+  if (st > kMaxStages) st = kMaxStages;
   if (user && user->stages) st = user->stages < st ? user->stages : st;
   if (st < 2) return false;
   pl.stages = st;
   pl.max_ctas = user && user->max_ctas ? user->max_ctas : sms;
-  // Whole 128-row weight tiles stream measurably faster on B200 with 128 CTAs than with
-  // all 148 SMs (6.5-6.7 TB/s against 6.3: a ragged last round of tiles costs a full
-  // one); evenly dealt rows and the tensor-bound assignment use every SM.
+  // Weight streaming is HBM-bound: 128 CTAs with full rings in flight saturate the memory
+  // system, and more CTAs only add rounds that are no shorter (measured on B200: 6.5-6.7
+  // TB/s with 128 CTAs against 6.3 with all 148 SMs); the tensor-bound assignment uses every SM.
   pl.cta_cap = pl.max_ctas;
-  if (!(user && user->max_ctas) && pl.kernel == PMX_GEMM_TC_WEIGHTS_M && !pl.balanced && pl.cta_cap > 128) pl.cta_cap = 128;
+  if (!(user && user->max_ctas) && pl.kernel == PMX_GEMM_TC_WEIGHTS_M && pl.cta_cap > 128) pl.cta_cap = 128;
   if (user && user->cta_cap > 0 && user->cta_cap <= pl.max_ctas) pl.cta_cap = user->cta_cap;
   pl.full_rounds = !(user && user->full_rounds == 2);
   // Stream-K (k-blocks of all items dealt out evenly over the CTAs) is available on

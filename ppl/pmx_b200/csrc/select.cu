@@ -631,11 +631,12 @@ bool route_select_geometry(int64_t T, int64_t H, int E, int k, int dtype, RouteS
 // SM, so all are resident), adds up the counts of the blocks in front of it, and then
 // places and gathers its own rows.  Positions only depend on the scores (no atomics
 // decide an order), so every tensor-parallel rank computes the same permutation.
-constexpr int kWideChunk = 256;          // tokens routed per pass (one per thread)
+constexpr int kWideChunk = 256;          // tokens routed per pass (one per thread of the first 8 warps)
+constexpr int kWideThreads = 1024;       // one block per SM: the row copies need many loads in flight
 constexpr int kWideMaxTokensPerBlock = 1024;
 
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kWideThreads)
 select_wide_kernel(const T* __restrict__ x, const T* __restrict__ scores, int64_t Tn, int64_t H, int E, int k,
                    int tpb, T* __restrict__ xp, T* __restrict__ weights, int64_t* __restrict__ inv,
                    int64_t* __restrict__ expert_offset, unsigned int* __restrict__ barrier,
@@ -667,7 +668,7 @@ select_wide_kernel(const T* __restrict__ x, const T* __restrict__ scores, int64_
     }
     __syncthreads();
     const int tl = c0 + threadIdx.x;                 // token of this thread (its warp = one group)
-    if (tl < groups * 32) {
+    if (threadIdx.x < kWideChunk && tl < groups * 32) {
       unsigned long long mask = 0ull;
       if (tl < ntok) {
         const float* row = srow + threadIdx.x * (E + 1);
@@ -855,7 +856,7 @@ int run_select(const void* x, const void* scores, void* xp, void* w, int64_t* in
     const bool vec = (H * sizeof(T)) % 16 == 0 && aligned16(x) && aligned16(xp);
     auto kern = vec ? select_wide_kernel<T, true> : select_wide_kernel<T, false>;
     if (wg.smem > 48 * 1024) PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)wg.smem));
-    return launch_pdl_k(kern, dim3(wg.nblk), dim3(256), wg.smem, s, reinterpret_cast<const T*>(x),
+    return launch_pdl_k(kern, dim3(wg.nblk), dim3(kWideThreads), wg.smem, s, reinterpret_cast<const T*>(x),
                         reinterpret_cast<const T*>(scores), Tn, H, E, k, wg.tpb, reinterpret_cast<T*>(xp),
                         reinterpret_cast<T*>(w), inv, off, barrier, block_counts, status, 1000000000ull);
   }

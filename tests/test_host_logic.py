@@ -39,14 +39,12 @@ def test_workspace_sizes_and_argument_errors_without_a_gpu(lib):
     assert lib.pmx_moe_select_workspace_bytes(0, 8, 2) == 0
     n = lib.pmx_moe_select_workspace_bytes(8192, 8, 2)
     assert n >= 8192 * 2 * 4 and n % 16 == 0
-    # Mixtral down projection: 64 tokens -> enough work items, status words only;
-    # one token (2 rows): the feature rows are dealt out in 8-row units, still enough
-    # units for every SM; with whole 128-row tiles K is sliced: fp32 partial sums + status words
+    # Mixtral down projection: 64 tokens -> enough work for every SM, status words only;
+    # one token (2 rows) -> K is sliced: fp32 partial sums + status words
     assert lib.pmx_moe_grouped_linear_workspace_bytes(128, 4096, 14336, 8, 0, 0, None) == 256
-    assert lib.pmx_moe_grouped_linear_workspace_bytes(2, 4096, 14336, 8, 0, 0, None) == 256
-    whole = GemmPlan(balance=2)
-    ws = lib.pmx_moe_grouped_linear_workspace_bytes(2, 4096, 14336, 8, 0, 0, C.byref(whole))
-    assert ws > 256 and (ws - 256) % (2 * 4096 * 4) == 0
+    for plan in (None, C.byref(GemmPlan(balance=2))):
+        ws = lib.pmx_moe_grouped_linear_workspace_bytes(2, 4096, 14336, 8, 0, 0, plan)
+        assert ws > 256 and (ws - 256) % (2 * 4096 * 4) == 0
     assert lib.pmx_moe_grouped_linear_workspace_bytes(128, 4096, 14336, 8, 2, 0, None) == 256   # fp32 -> CUDA cores
     assert lib.pmx_moe_grouped_linear_workspace_bytes(128, 4097, 64, 8, 0, 1, None) == 0        # odd N with SwiGLU
     assert b"even N" in lib.pmx_moe_last_error()

@@ -61,6 +61,10 @@ def test_select_golden(F, name):
     (1, 8, 8, 2, "f16"), (2, 24, 8, 2, "bf16"), (17, 5, 3, 1, "f32"), (300, 40, 8, 2, "f16"),
     (513, 16, 64, 8, "f16"), (4097, 8, 8, 2, "bf16"), (64, 7, 8, 8, "f32"), (1000, 3, 160, 6, "f16"),
     (9000, 8, 32, 32, "bf16"),
+    # the one-launch path for large batches (<= 64 experts), its limits, and the three-launch
+    # path behind it (more than 64 experts, or more than 1024 tokens per SM)
+    (5000, 64, 64, 8, "f16"), (20000, 16, 8, 2, "f32"), (1025, 24, 5, 5, "bf16"), (3000, 8, 70, 3, "f16"),
+    (160000, 8, 8, 2, "f16"),
 ])
 def test_select_random_shapes(F, T, H, E, k, dtype):
     rng = np.random.default_rng(T * 7 + E)

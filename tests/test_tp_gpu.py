@@ -77,6 +77,59 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+def _alternating(rank, world, port, q):
+    """One set of exchange buffers, token counts that change from call to call (64, 8, 64,
+    8, ...) and one rank held back on the host between calls: a fast rank starts the next
+    exchange while the slow one may still be reading the previous one."""
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        group = dist.new_group(list(range(world)))
+        import ppl.pmx_b200.torch_function as F
+        from ppl.pmx_b200.peer_reduce import PeerCombine
+        N, k = 1024, 2
+        for algo in ("push", "pull"):
+            peer = PeerCombine(group, 64, N, torch.float16, dev, algorithm=algo)
+            for call, T in enumerate([64, 8, 64, 8, 1, 64, 33, 8]):
+                g = torch.Generator().manual_seed(call)
+                w = torch.rand(T, k, generator=g).half().to(dev)
+                inv = torch.randperm(T * k, generator=g).view(T, k).to(dev)
+                ys = [torch.randn(T * k, N, generator=g).half() for _ in range(world)]
+                if rank == 1:
+                    time.sleep(0.02)              # the slow rank
+                out = peer.combine_allreduce(ys[rank].to(dev), w, inv, k)
+                want = sum(F.moe_reduce(y.to(dev).view(T, k, N), w, inv, k).float() for y in ys)
+                torch.testing.assert_close(out.float(), want, atol=2e-2, rtol=1e-2,
+                                           msg=f"{algo} call {call} T={T} rank {rank}")
+            peer.check()
+        q.put((rank, "ok"))
+    except Exception:                            # noqa: BLE001
+        import traceback
+        q.put((rank, traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_exchange_buffers_survive_changing_token_counts_and_a_slow_rank():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_alternating, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
+
+
 def test_tensor_parallel_block_on_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
