@@ -275,7 +275,8 @@ def get_block(ctx, shape, full: bool, w_router=None):
         if ctx.args.allreduce == "peer":
             peer_tokens = max(peer_tokens, 8192)
     blk = MoeFeedForward(shape.H, shape.I, shape.E, shape.k, None if full else ctx.group, False,
-                         peer_reduce_tokens=peer_tokens, peer_algorithm=ctx.args.peer_algo).to(ctx.device, dt)
+                         peer_reduce_tokens=peer_tokens, peer_algorithm=ctx.args.peer_algo,
+                         overlap_chunks=ctx.args.overlap_chunks).to(ctx.device, dt)
     wu, w2 = W.make_expert_weights(shape, ctx.device, tp_rank=0 if full else ctx.rank, tp_size=tp)
     if w_router is None:
         _, w_router, _, _ = W.make_activations(shape, detie=False)
@@ -693,15 +694,18 @@ class MoeTimer:
 
 def run_decoder(ctx, cfg, batch, cached, steps, parity_layers=2):
     """The full decoder step of the reference model with the operators of this package
-    swapped in.  Three variants share one set of weights: the unmodified reference
-    operators; patch_reference() (every replaced operator, call by call); and in addition
-    the fused MoeFeedForward block in place of the reference block's forward.  Parity: a
+    swapped in.  Four variants share one set of weights: the unmodified reference
+    operators; "patched": patch_reference() of the MoE operators, the norms and the dense
+    linears, call by call; "fused": in addition the fused MoeFeedForward block in place of
+    the reference block's forward; "fused+attention": in addition the decode-step cache
+    attention kernel in place of the reference's per-sequence loops.  Parity: a
     `parity_layers`-deep copy of the model, same inputs, logits of the variants against the
     unmodified reference.  Timing: whole step (host clock around the synchronised call:
     the reference's attention, KV-cache and rotary operators loop over the sequences in
     Python) and the summed time of the MoE blocks (CUDA events)."""
-    from ppl.pmx_b200.moe_layers import MoeFeedForward, patch_reference
+    from ppl.pmx_b200.moe_layers import MoeFeedForward, PATCHED_NAMES, patch_reference, unpatch_reference
     world, device = ctx.world, ctx.device
+    no_attention = tuple(n for n in PATCHED_NAMES if "attention" not in n)
 
     def make_fused(net):
         """One fused MoeFeedForward of this package per layer, on the reference module's own
@@ -726,8 +730,8 @@ def run_decoder(ctx, cfg, batch, cached, steps, parity_layers=2):
     def one_pass(net, opmx, inp, variant, fused, n_steps, timer):
         saved, undo = {}, []
         if variant != "reference":
-            saved = patch_reference(opmx)
-        if variant == "fused":
+            saved = patch_reference(opmx, PATCHED_NAMES if variant == "fused+attention" else no_attention)
+        if variant.startswith("fused"):
             for layer, blk in zip(net.layers, fused):
                 undo.append((layer.feed_forward, layer.feed_forward.__dict__.get("forward")))
                 layer.feed_forward.forward = (lambda x, _b=blk: _b(x))
@@ -753,8 +757,7 @@ def run_decoder(ctx, cfg, batch, cached, steps, parity_layers=2):
                     del ff.forward
                 else:
                     ff.forward = old
-            for name, fn in saved.items():
-                setattr(opmx, name, fn)
+            unpatch_reference(opmx, saved)
         steady = times[1:] if len(times) > 1 else times
         return logits, statistics.median(steady) * 1e3, moe_ms
 
@@ -767,7 +770,7 @@ def run_decoder(ctx, cfg, batch, cached, steps, parity_layers=2):
     fused = make_fused(net)
     ref_logits, _, _ = one_pass(net, opmx, inp, "reference", fused, 1, False)
     par = {}
-    for v in ("patched", "fused"):
+    for v in ("patched", "fused", "fused+attention"):
         logits, _, _ = one_pass(net, opmx, inp, v, fused, 1, False)
         d = (logits.float() - ref_logits.float()).abs()
         par[v] = {"max_abs_diff_logits": float(d.max()), "mean_abs_logit": float(ref_logits.float().abs().mean()),
@@ -783,13 +786,14 @@ def run_decoder(ctx, cfg, batch, cached, steps, parity_layers=2):
     inp = decoder_step_inputs(net, batch, cached, device, world)
     fused = make_fused(net)
     out["timing"] = {}
-    for v in ("reference", "patched", "fused"):
+    for v in ("reference", "patched", "fused", "fused+attention"):
         _, ms, moe_ms = one_pass(net, opmx, inp, v, fused, steps + 1, True)
         out["timing"][v] = {"ms_per_step": ms, "moe_ms_per_step": moe_ms,
                             "moe_ms_per_layer": moe_ms / cfg["num_layers"] if moe_ms is not None else None,
                             "tokens_per_s": batch / (ms * 1e-3)}
-    out["timing"]["note"] = ("median host-clock time of a synchronised decode step; the attention, KV-cache and rotary "
-                             "operators are the reference's own (per-sequence Python loops) in all three variants")
+    out["timing"]["note"] = ("median host-clock time of a synchronised decode step; the rotary embedding (and, except in "
+                             "the last variant, the attention and KV-cache operators) are the reference's own "
+                             "per-sequence Python loops")
     del net, fused, inp
     torch.cuda.empty_cache()
     return out
@@ -820,6 +824,9 @@ def main():
                     help="N > 1: fused combine + all-reduce kernel over NVLink peer memory, or moe_reduce + NCCL "
                          "(auto: peer when the [T,H] result is at most 4 MB)")
     ap.add_argument("--peer-algo", default="auto", choices=["auto", "push", "pull"])
+    ap.add_argument("--overlap-chunks", type=int, default=4,
+                    help="N > 1, results too large for the peer kernel: hidden-column slices of the down projection "
+                         "whose all-reduces overlap the next slice's GEMM (1: one GEMM, one all-reduce)")
     ap.add_argument("--gemm-plan", default="", help="pmx_gemm_plan fields for the gate_up / down STAGE timings, "
                                                     "e.g. balance=2,cta_cap=128 (the step itself uses the default plan)")
     ap.add_argument("--decoder", default="auto", choices=["auto", "on", "off"],

@@ -79,6 +79,11 @@ typedef struct pmx_gemm_plan {
   int32_t balance;      /* PMX_GEMM_TC_WEIGHTS_M only: 0 = choose, 1 = deal the feature rows evenly
                            over the CTAs in units of 8 rows (every SM streams the same number of
                            weight bytes), 2 = whole 128-row tiles */
+  int32_t w_expert_pitch; /* 0: w is a dense [E,N,K] tensor.  Otherwise the number of rows between
+                           consecutive experts in memory (and of elements between their biases):
+                           w points at a window of N feature rows inside a wider [E,pitch,K]
+                           weight tensor, e.g. a slice of the hidden columns of the down
+                           projection.  Not with SwiGLU, split-K or stream-K. */
 } pmx_gemm_plan;
 
 int pmx_moe_abi_version(void);
@@ -257,6 +262,33 @@ int pmx_skip_rms_norm(const void* x, const void* skip, const void* weight, void*
 int pmx_moe_reduce(const void* y, const void* expert_weights,
                    const int64_t* invert_permutation, void* out, int64_t T,
                    int32_t k, int64_t N, int32_t dtype, void* stream);
+
+/*
+ * Decode-step attention over the key/value cache -- replaces, for steps in which every
+ * sequence contributes ONE new token, MultiHeadCacheAttention.forward
+ * (torch_function/dynamic_batching/MultiHeadCacheAttention.py:104-130), i.e.
+ * KeyValueCache.forward (dynamic_batching/KeyValueCache.py:86-138; cache_mode 0, no
+ * quantisation) followed by MultiHeadAttention.forward (dynamic_batching/MultiHeadAttention.py:54-108):
+ *   for every sequence b: the new key / value [num_kv_heads, head_dim] are stored at cache
+ *   row cachestarts[b] + start_pos[b]; out[b,h,:] = softmax(q[b,h] . K^T / sqrt(head_dim)) . V
+ *   over the start_pos[b] + 1 cached positions of the key/value head h / (num_heads / num_kv_heads).
+ * query, out [B, num_heads, head_dim]; current_key, current_value [B, num_kv_heads, head_dim];
+ * cachestarts, start_pos [B] int64 on the device.  The cache element (row, kv, head, d), kv = 0
+ * for keys and 1 for values, of the layer in question lives at
+ *   cache + layer_offset + row*row_stride + kv*kv_stride + head*head_stride + d   (in elements),
+ * which covers the four cache layouts of the reference.  max_kvlen >= start_pos[b] + 1 for all b
+ * (it sizes the split of the cached positions over the CTAs).  fp32 arithmetic, one rounding
+ * of the result.  float16 / bfloat16, head_dim 64 or 128, at most 8 query heads per kv head.
+ * Workspace: pmx_decode_cache_attention_workspace_bytes(...) bytes, 16-byte aligned.
+ */
+size_t pmx_decode_cache_attention_workspace_bytes(int64_t B, int32_t num_heads, int32_t num_kv_heads,
+                                                  int32_t head_dim, int64_t max_kvlen);
+int pmx_decode_cache_attention(const void* query, const void* current_key, const void* current_value,
+                               void* cache, const int64_t* cachestarts, const int64_t* start_pos,
+                               void* out, int64_t B, int32_t num_heads, int32_t num_kv_heads,
+                               int32_t head_dim, int64_t layer_offset, int64_t row_stride,
+                               int64_t kv_stride, int64_t head_stride, int64_t max_kvlen,
+                               int32_t dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /* how pmx_moe_reduce_allreduce moves the partial results between the ranks */
 typedef enum pmx_allreduce_algorithm {

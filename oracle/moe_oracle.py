@@ -28,7 +28,8 @@ import numpy as np
 __all__ = [
     "bf16_bits_to_f32", "f32_to_bf16_bits", "round_to_dtype", "topk_desc",
     "moe_select", "moe_grouped_linear", "swiglu", "silu_gate", "moe_reduce",
-    "moe_block", "detie_scores", "rows_with_ties", "skip_rms_norm",
+    "moe_block", "detie_scores", "rows_with_ties", "skip_rms_norm", "linear", "decode_cache_attention",
+    "cache_view",
 ]
 
 
@@ -263,3 +264,62 @@ def moe_block(x, w_router, w_gate_up, w_down, num_experts, k, dtype="f32",
     out = moe_reduce(y, ew, inv, k)
     return dict(scores=scores, x_expand_permute=xe, expert_weights=ew,
                 invert_permutation=inv, expert_offset=off, x13=x13, h=h, y=y, out=out)
+
+
+# ----------------------------------------------------------------------------
+# dense linear and decode-step cache attention (the operators around the MoE block)
+# ----------------------------------------------------------------------------
+def linear(x: np.ndarray, w: np.ndarray, b: np.ndarray | None = None) -> np.ndarray:
+    """torch_function/Linear.py:32 (`F.linear(X, W, B)`), also the local product of
+    ColumnParallelLinear.py:43 and RowParallelLinear.py:41 (+ bias at :44-45).
+    x [*, K], w [N, K], b [N] | None -> [*, N] float32 (float64 accumulation)."""
+    y = np.asarray(x, np.float64) @ np.asarray(w, np.float64).T
+    if b is not None:
+        y = y + np.asarray(b, np.float64)
+    return y.astype(np.float32)
+
+
+def cache_view(cache: np.ndarray, layout: int, layer_idx: int) -> np.ndarray:
+    """View [rows, 2, heads, d] of one layer of a cache_mode-0 key/value cache in any of the
+    four layouts (the index expressions of dynamic_batching/KeyValueCache.py:119-227)."""
+    if layout == 0:      # [rows, layers, 2, heads, d]
+        return cache[:, layer_idx]
+    if layout == 1:      # [layers, rows, 2, heads, d]
+        return cache[layer_idx]
+    if layout == 2:      # [layers, 2, rows, heads, d]
+        return cache[layer_idx].transpose(1, 0, 2, 3)
+    if layout == 3:      # [layers, 2, heads, rows, d]
+        return cache[layer_idx].transpose(2, 0, 1, 3)
+    raise ValueError(f"unsupported cache_layout: {layout}")
+
+
+def decode_cache_attention(q: np.ndarray, k_new: np.ndarray, v_new: np.ndarray, cache: np.ndarray,
+                           cachestarts: np.ndarray, start_pos: np.ndarray, layout: int, layer_idx: int) -> np.ndarray:
+    """One decode step of dynamic_batching.MultiHeadCacheAttention.forward
+    (torch_function/dynamic_batching/MultiHeadCacheAttention.py:104-130) with one new token per
+    sequence, cache_mode 0, no quantisation, no mask:
+      KeyValueCache.forward (dynamic_batching/KeyValueCache.py:86-138): the new key / value of
+      sequence b go to cache row cachestarts[b] + start_pos[b]; its keys / values are cache
+      rows cachestarts[b] .. cachestarts[b] + start_pos[b];
+      MultiHeadAttention.forward (dynamic_batching/MultiHeadAttention.py:56-108): kv heads are
+      repeated for the query heads that share them, scores = q . K^T / sqrt(d), softmax, . V.
+    q [B,Hq,d], k_new / v_new [B,Hkv,d]; `cache` (float32 values) is updated in place.
+    -> [B,Hq,d] float32 (float64 accumulation, no intermediate rounding)."""
+    B, Hq, d = q.shape
+    Hkv = k_new.shape[1]
+    rep = Hq // Hkv
+    view = cache_view(cache, layout, layer_idx)            # [rows, 2, Hkv, d], a view: writes reach `cache`
+    out = np.zeros((B, Hq, d), np.float32)
+    for b in range(B):
+        pos = int(start_pos[b])
+        row = int(cachestarts[b]) + pos
+        view[row, 0] = k_new[b]
+        view[row, 1] = v_new[b]
+        keys = view[int(cachestarts[b]):row + 1, 0].astype(np.float64)      # [kvlen, Hkv, d]
+        vals = view[int(cachestarts[b]):row + 1, 1].astype(np.float64)
+        for h in range(Hq):
+            s = keys[:, h // rep] @ q[b, h].astype(np.float64) / np.sqrt(d)
+            p = np.exp(s - s.max())
+            p /= p.sum()
+            out[b, h] = (p @ vals[:, h // rep]).astype(np.float32)
+    return out

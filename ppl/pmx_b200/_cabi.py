@@ -24,7 +24,7 @@ class GemmPlan(C.Structure):
     """Mirror of pmx_gemm_plan."""
     _fields_ = [("kernel", C.c_int32), ("tile_feat", C.c_int32), ("tile_tok", C.c_int32),
                 ("split_k", C.c_int32), ("stages", C.c_int32), ("max_ctas", C.c_int32), ("stream_k", C.c_int32),
-                ("cta_cap", C.c_int32), ("full_rounds", C.c_int32), ("balance", C.c_int32)]
+                ("cta_cap", C.c_int32), ("full_rounds", C.c_int32), ("balance", C.c_int32), ("w_expert_pitch", C.c_int32)]
 
 
 class PmxError(RuntimeError):
@@ -64,6 +64,9 @@ def _load() -> C.CDLL:
         "pmx_silu": (C.c_int, [vp, vp, vp, i64, i32, vp]),
         "pmx_skip_rms_norm": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, f32, i32, vp]),
         "pmx_moe_reduce": (C.c_int, [vp, vp, vp, vp, i64, i32, i64, i32, vp]),
+        "pmx_decode_cache_attention_workspace_bytes": (sz, [i64, i32, i32, i32, i64]),
+        "pmx_decode_cache_attention": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i64, i64, i64, i64, i64,
+                                                 i32, vp, sz, vp]),
         "pmx_moe_reduce_allreduce_buffer_bytes": (sz, [i64, i64, i32]),
         "pmx_moe_reduce_allreduce": (C.c_int, [vp, vp, vp, vp, i64, i32, i64, i32, C.POINTER(vp), i32, i32, sz,
                                                i32, i32, i64, vp]),

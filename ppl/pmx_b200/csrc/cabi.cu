@@ -76,6 +76,9 @@ int choose_linear(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
     return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear: SwiGLU needs an even N");
   const int want = user ? user->kernel : PMX_GEMM_AUTO;
   c->tc = false;
+  const int64_t pitch = user ? user->w_expert_pitch : 0;
+  if (pitch != 0 && (pitch < N || epilogue == PMX_EPILOGUE_SWIGLU || (user->split_k > 1) || user->stream_k == 1))
+    return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear: w_expert_pitch (%lld) must be at least N (%lld) and cannot be combined with SwiGLU, split-K or stream-K", (long long)pitch, (long long)N);
   if (want == PMX_GEMM_SIMT) return PMX_OK;
   if (want == PMX_GEMM_TC_TOKENS_M_PAIRED) {
     c->tc = plan_gemm_tc_pair(M, N, K, E, dtype, epilogue, user, &c->plan);
@@ -87,6 +90,14 @@ int choose_linear(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
     if (c->tc && want == PMX_GEMM_AUTO && c->plan.kernel == PMX_GEMM_TC_TOKENS_M && M / E >= 1024) {
       TcPlan paired;
       if (plan_gemm_tc_pair(M, N, K, E, dtype, epilogue, user, &paired)) c->plan = paired;
+    }
+  }
+  if (c->tc) {
+    c->plan.w_pitch = (int)pitch;
+    if (pitch != 0 && c->plan.split_k > 1) {     // a window of a wider tensor: whole-K tiles only
+      pmx_gemm_plan whole = *user;
+      whole.split_k = 1;
+      return choose_linear(M, N, K, E, dtype, epilogue, &whole, c);
     }
   }
   if (!c->tc && want != PMX_GEMM_AUTO)
@@ -207,7 +218,8 @@ int pmx_moe_grouped_linear(const void* x, const int64_t* expert_offset, const vo
     if (!workspace || workspace_bytes < kStatusBytes)
       return fail(PMX_ERR_WORKSPACE, "grouped_linear: workspace of %zu bytes needed, %zu given", kStatusBytes, workspace_bytes);
     PMX_CUDA_OK(cudaMemsetAsync(workspace, 0, 16, s));
-    st = launch_gemm_simt(x, expert_offset, w, bias, y, M, N, K, E, dtype, epilogue, beta, s);
+    st = launch_gemm_simt(x, expert_offset, w, bias, y, M, N, K, E, dtype, epilogue, beta,
+                          plan ? plan->w_expert_pitch : 0, s);
     if (st != PMX_OK) return st;
     if (zero_outside) return launch_zero_outside(y, expert_offset, M, n_out, E, dtype, s);
     return PMX_OK;
@@ -250,6 +262,21 @@ int pmx_skip_rms_norm(const void* x, const void* skip, const void* weight, void*
 int pmx_moe_reduce(const void* y, const void* expert_weights, const int64_t* invert_permutation,
                    void* out, int64_t T, int32_t k, int64_t N, int32_t dtype, void* stream) {
   return launch_reduce(y, expert_weights, invert_permutation, out, T, k, N, dtype, (cudaStream_t)stream);
+}
+
+size_t pmx_decode_cache_attention_workspace_bytes(int64_t B, int32_t num_heads, int32_t num_kv_heads,
+                                                  int32_t head_dim, int64_t max_kvlen) {
+  return decode_attention_workspace_bytes(B, num_heads, num_kv_heads, head_dim, max_kvlen);
+}
+
+int pmx_decode_cache_attention(const void* query, const void* current_key, const void* current_value, void* cache,
+                               const int64_t* cachestarts, const int64_t* start_pos, void* out, int64_t B,
+                               int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, int64_t layer_offset,
+                               int64_t row_stride, int64_t kv_stride, int64_t head_stride, int64_t max_kvlen,
+                               int32_t dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  return launch_decode_attention(query, current_key, current_value, cache, cachestarts, start_pos, out, B, num_heads,
+                                 num_kv_heads, head_dim, layer_offset, row_stride, kv_stride, head_stride, max_kvlen,
+                                 dtype, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
 size_t pmx_moe_reduce_allreduce_buffer_bytes(int64_t T, int64_t N, int32_t dtype) {

@@ -145,6 +145,12 @@ int launch_reduce_allreduce_emulated(const void* const* y, const void* const* w,
                                      long long wait_limit_ns, cudaStream_t s);
 int reduce_allreduce_check(void* my_buffer, int out[4], cudaStream_t s);
 int reduce_allreduce_phases(const void* my_buffer, unsigned long long out[8], cudaStream_t s);
+size_t decode_attention_workspace_bytes(int64_t B, int Hq, int Hkv, int D, int64_t max_kvlen);
+int launch_decode_attention(const void* q, const void* k_cur, const void* v_cur, void* cache,
+                            const int64_t* cachestarts, const int64_t* start_pos, void* out, int64_t B, int Hq,
+                            int Hkv, int D, int64_t layer_off, int64_t row_stride, int64_t kv_stride,
+                            int64_t head_stride, int64_t max_kvlen, int dtype, void* ws, size_t ws_bytes,
+                            cudaStream_t s);
 int launch_zero_outside(void* y, const int64_t* off, int64_t M, int64_t n_out, int E, int dtype,
                         cudaStream_t s);
 int launch_splitk_finish(const float* partial, const int64_t* off, const void* bias, void* y,
@@ -153,7 +159,7 @@ int launch_splitk_finish(const float* partial, const int64_t* off, const void* b
 
 int launch_gemm_simt(const void* x, const int64_t* off, const void* w, const void* bias, void* y,
                      int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue, float beta,
-                     cudaStream_t s);
+                     int64_t w_pitch, cudaStream_t s);
 
 struct TcPlan {
   int kernel;      // PMX_GEMM_TC_TOKENS_M or PMX_GEMM_TC_WEIGHTS_M
@@ -165,7 +171,8 @@ struct TcPlan {
   int cta_cap;
   int full_rounds;
   int stream_k;
-  int balanced;    // weight rows on MMA-M: feature rows dealt evenly over the CTAs in 8-row units
+  int balanced;    // weight rows on MMA-M: contiguous whole-tile ranges per CTA, panels not shared
+  int w_pitch;     // rows between experts in w (0: N)
 };
 // Fills `plan` for the tensor-core kernel or returns false when the shape is
 // outside what it covers (the caller then uses the CUDA-core kernel).

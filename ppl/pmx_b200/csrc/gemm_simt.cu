@@ -16,7 +16,7 @@ template <typename T, bool SWIGLU>
 __global__ void __launch_bounds__(256)
 grouped_gemm_simt_kernel(const T* __restrict__ x, const int64_t* __restrict__ off,
                          const T* __restrict__ w, const T* __restrict__ bias, T* __restrict__ y,
-                         int64_t M, int N, int K, int E, float beta) {
+                         int64_t M, int N, int K, int E, float beta, int64_t w_pitch) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   __shared__ float Bu[SWIGLU ? BK : 1][BN + 4];
@@ -47,7 +47,7 @@ grouped_gemm_simt_kernel(const T* __restrict__ x, const int64_t* __restrict__ of
   if (e < 0) return;
   const int row0 = s_row0, row_end = s_row_end;
   const int n0 = blockIdx.x * BN;
-  const T* we = w + (int64_t)e * N * K;
+  const T* we = w + (int64_t)e * w_pitch * K;
 
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
   float acc[4][4] = {}, accu[4][4] = {};
@@ -94,10 +94,10 @@ grouped_gemm_simt_kernel(const T* __restrict__ x, const int64_t* __restrict__ of
       const int n = n0 + tx * 4 + j;
       if (n >= n_out) continue;
       float v = acc[i][j];
-      if (bias) v += Elem<T>::to_f(bias[(int64_t)e * N + n]);
+      if (bias) v += Elem<T>::to_f(bias[(int64_t)e * w_pitch + n]);
       if (SWIGLU) {
         float u = accu[i][j];
-        if (bias) u += Elem<T>::to_f(bias[(int64_t)e * N + n_out + n]);
+        if (bias) u += Elem<T>::to_f(bias[(int64_t)e * w_pitch + n_out + n]);
         v = u * v / (1.0f + expf(-beta * v));
       }
       y[(int64_t)r * n_out + n] = Elem<T>::from_f(v);
@@ -107,15 +107,15 @@ grouped_gemm_simt_kernel(const T* __restrict__ x, const int64_t* __restrict__ of
 
 template <typename T>
 int run(const void* x, const int64_t* off, const void* w, const void* bias, void* y, int64_t M,
-        int64_t N, int64_t K, int E, int epilogue, float beta, cudaStream_t s) {
+        int64_t N, int64_t K, int E, int epilogue, float beta, int64_t w_pitch, cudaStream_t s) {
   const int64_t n_out = epilogue == PMX_EPILOGUE_SWIGLU ? N / 2 : N;
   const int64_t row_tiles = ceil_div(M, BM) + E;  // upper bound on ragged row tiles
   if (row_tiles > 65535) return fail(PMX_ERR_UNSUPPORTED, "grouped_linear (CUDA-core kernel): too many rows (%lld)", (long long)M);
   dim3 grid((unsigned)ceil_div(n_out, BN), (unsigned)row_tiles);
   if (epilogue == PMX_EPILOGUE_SWIGLU)
-    grouped_gemm_simt_kernel<T, true><<<grid, 256, 0, s>>>((const T*)x, off, (const T*)w, (const T*)bias, (T*)y, M, (int)N, (int)K, E, beta);
+    grouped_gemm_simt_kernel<T, true><<<grid, 256, 0, s>>>((const T*)x, off, (const T*)w, (const T*)bias, (T*)y, M, (int)N, (int)K, E, beta, w_pitch);
   else
-    grouped_gemm_simt_kernel<T, false><<<grid, 256, 0, s>>>((const T*)x, off, (const T*)w, (const T*)bias, (T*)y, M, (int)N, (int)K, E, beta);
+    grouped_gemm_simt_kernel<T, false><<<grid, 256, 0, s>>>((const T*)x, off, (const T*)w, (const T*)bias, (T*)y, M, (int)N, (int)K, E, beta, w_pitch);
   PMX_LAUNCHED();
   return PMX_OK;
 }
@@ -124,11 +124,12 @@ int run(const void* x, const int64_t* off, const void* w, const void* bias, void
 
 int launch_gemm_simt(const void* x, const int64_t* off, const void* w, const void* bias, void* y,
                      int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue, float beta,
-                     cudaStream_t s) {
+                     int64_t w_pitch, cudaStream_t s) {
+  if (w_pitch <= 0) w_pitch = N;
   switch (dtype) {
-    case PMX_DTYPE_F16: return run<__half>(x, off, w, bias, y, M, N, K, E, epilogue, beta, s);
-    case PMX_DTYPE_BF16: return run<__nv_bfloat16>(x, off, w, bias, y, M, N, K, E, epilogue, beta, s);
-    case PMX_DTYPE_F32: return run<float>(x, off, w, bias, y, M, N, K, E, epilogue, beta, s);
+    case PMX_DTYPE_F16: return run<__half>(x, off, w, bias, y, M, N, K, E, epilogue, beta, w_pitch, s);
+    case PMX_DTYPE_BF16: return run<__nv_bfloat16>(x, off, w, bias, y, M, N, K, E, epilogue, beta, w_pitch, s);
+    case PMX_DTYPE_F32: return run<float>(x, off, w, bias, y, M, N, K, E, epilogue, beta, w_pitch, s);
   }
   return fail(PMX_ERR_UNSUPPORTED, "grouped_linear: unknown dtype %d", dtype);
 }

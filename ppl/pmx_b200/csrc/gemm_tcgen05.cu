@@ -123,7 +123,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       work.init(p, total_items);
       bool ok = true;
       while (ok && work.next(p, total_items, s_off, s_prefix, it, item)) {
-        const int wrow = it.e * p.N + it.f0;
+        const int wrow = it.e * p.w_pitch + it.f0;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           ok = wait_barrier(&sh->empty[stage], phase ^ 1u, sh, p.status, 0, item);
           if (!ok) break;
@@ -287,7 +287,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       if (MODE == 0) {
         const int row = it.row0 + q * 32 + lane;
         const bool row_ok = row < it.row_end;
-        const T* be = bias ? bias + (int64_t)it.e * p.N : nullptr;
+        const T* be = bias ? bias + (int64_t)it.e * p.w_pitch : nullptr;
         for (int c = 0; c < ft; c += 16) {
           float g[16], u[16];
           __syncwarp();  // tcgen05.ld is warp-collective: keep the lanes together
@@ -332,8 +332,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         const bool f_ok = f < p.n_out && q * 32 + lane < it.fn;
         float bg = 0.f, bu = 0.f;
         if (bias && f_ok) {
-          bg = Elem<T>::to_f(bias[(int64_t)it.e * p.N + f]);
-          if (SWIGLU) bu = Elem<T>::to_f(bias[(int64_t)it.e * p.N + p.n_out + f]);
+          bg = Elem<T>::to_f(bias[(int64_t)it.e * p.w_pitch + f]);
+          if (SWIGLU) bu = Elem<T>::to_f(bias[(int64_t)it.e * p.w_pitch + p.n_out + f]);
         }
         for (int c = 0; c < tt; c += 16) {
           if (it.row0 + c >= it.row_end || q * 32 >= it.fn) break;  // same for the whole warp
@@ -524,13 +524,13 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   CUtensorMap mx, mw;
   int st = make_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint32_t)plan.tile_tok, dtype);
   if (st != PMX_OK) return st;
-  st = make_map(&mw, w, (uint64_t)E * N, (uint64_t)K, (uint32_t)plan.tile_feat, dtype);
+  st = make_map(&mw, w, (uint64_t)(E - 1) * (uint64_t)(plan.w_pitch > 0 ? plan.w_pitch : N) + (uint64_t)N, (uint64_t)K, (uint32_t)plan.tile_feat, dtype);
   if (st != PMX_OK) return st;
 
   SmallBoxMaps mws{};
   if (plan.balanced) {
     for (int b = 0; b < 4; ++b) {
-      st = make_map(&mws.m[b], w, (uint64_t)E * N, (uint64_t)K, (uint32_t)(64 >> b), dtype);
+      st = make_map(&mws.m[b], w, (uint64_t)(E - 1) * (uint64_t)(plan.w_pitch > 0 ? plan.w_pitch : N) + (uint64_t)N, (uint64_t)K, (uint32_t)(64 >> b), dtype);
       if (st != PMX_OK) return st;
     }
   }
@@ -540,6 +540,7 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   p.status = reinterpret_cast<int*>(ws);
   p.y = plan.split_k > 1 ? reinterpret_cast<void*>(reinterpret_cast<char*>(ws) + kStatusBytes) : y;
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.E = E;
+  p.w_pitch = plan.w_pitch > 0 ? plan.w_pitch : (int)N;
   p.n_out = (int)n_out;
   p.tile_tok = plan.tile_tok;
   p.tile_feat = plan.tile_feat;

@@ -161,7 +161,7 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x,
         decode_item(item, e, s_off, s_prefix, p, it);
         // weight rows this CTA fetches: SwiGLU -> leader the gate rows, peer the up rows;
         // otherwise the two halves of the feature tile
-        const int wrow = it.e * p.N + it.f0 + (SWIGLU ? (int)rank * (p.N / 2) : (int)rank * my_wrows);
+        const int wrow = it.e * p.w_pitch + it.f0 + (SWIGLU ? (int)rank * (p.N / 2) : (int)rank * my_wrows);
         const int row0 = it.row0 + (int)rank * 128;
         for (int kb = 0; kb < p.kblocks; ++kb) {
           ok = wait_barrier(&sh->empty[stage], phase ^ 1u, sh, p.status, 0, item);
@@ -230,7 +230,7 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x,
       const uint32_t taddr = tmem_base + acc * kAccStride + (static_cast<uint32_t>(q * 32) << 16);
       const int row = it.row0 + (int)rank * 128 + q * 32 + lane;
       const bool row_ok = row < it.row_end;
-      const T* be = bias ? bias + (int64_t)it.e * p.N : nullptr;
+      const T* be = bias ? bias + (int64_t)it.e * p.w_pitch : nullptr;
       for (int c = 0; c < ft; c += 16) {
         float g[16], u[16];
         __syncwarp();
@@ -337,7 +337,7 @@ int launch_gemm_tc_pair(const void* x, const int64_t* off, const void* w, const 
   CUtensorMap mx, mw;
   int st = make_map(&mx, x, (uint64_t)M, (uint64_t)K, 128u, dtype);
   if (st != PMX_OK) return st;
-  st = make_map(&mw, w, (uint64_t)E * N, (uint64_t)K, (uint32_t)(wrows / 2), dtype);
+  st = make_map(&mw, w, (uint64_t)(E - 1) * (uint64_t)(plan.w_pitch > 0 ? plan.w_pitch : N) + (uint64_t)N, (uint64_t)K, (uint32_t)(wrows / 2), dtype);
   if (st != PMX_OK) return st;
   Params p{};
   p.off = off;
@@ -345,6 +345,7 @@ int launch_gemm_tc_pair(const void* x, const int64_t* off, const void* w, const 
   p.status = reinterpret_cast<int*>(ws);
   p.y = y;
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.E = E;
+  p.w_pitch = plan.w_pitch > 0 ? plan.w_pitch : (int)N;
   p.n_out = (int)n_out;
   p.tile_tok = 256;
   p.tile_feat = plan.tile_feat;

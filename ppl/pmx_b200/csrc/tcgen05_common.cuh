@@ -19,6 +19,8 @@ struct Params {
   const void* bias;     // [E, N] T or null
   int* status;          // 4 ints: code, role, item, aux
   int M, N, K, E;
+  int w_pitch;          // rows between consecutive experts in w (and elements in bias): N unless the
+                        // caller passes a window of the feature rows of a wider weight tensor
   int n_out;            // N, or N/2 with SwiGLU
   int tile_tok, tile_feat;
   int feat_tiles;

@@ -20,7 +20,11 @@ import torch.distributed as dist
 from torch import nn
 
 from . import torch_function as OPMX
+from ._cabi import GemmPlan
 from .torch_function.moe import moe_grouped_linear, moe_route_select, moe_norm_route_select
+
+# below this many bytes of [T,H] result one all-reduce is cheaper than overlapped slices
+OVERLAP_MIN_BYTES = 8 << 20
 
 
 # set to True to wrap the stages of MoeFeedForward in NVTX ranges (visible in a profiler
@@ -163,7 +167,8 @@ class MoeFeedForward(nn.Module):
 
     def __init__(self, hidden_dim: int, intermediate_dim: int, num_experts: int,
                  num_experts_per_token: int, proc_group=None, linear_bias_term: bool = False,
-                 fused: bool = True, peer_reduce_tokens: int = 0, peer_algorithm: str = "auto") -> None:
+                 fused: bool = True, peer_reduce_tokens: int = 0, peer_algorithm: str = "auto",
+                 overlap_chunks: int = 4) -> None:
         super().__init__()
         self.num_experts = num_experts
         self.num_experts_per_token = num_experts_per_token
@@ -174,6 +179,9 @@ class MoeFeedForward(nn.Module):
         # all-reduce run as one kernel over NVLink peer memory (set up on first use)
         self.peer_reduce_tokens = peer_reduce_tokens
         self.peer_algorithm = peer_algorithm
+        # tensor-parallel batches too large for the peer kernel: hidden-column slices whose
+        # all-reduces overlap the following slice's GEMM (1 = one GEMM, one all-reduce)
+        self.overlap_chunks = overlap_chunks
         self._peer = None
         self._last_workspaces = ()     # status words of the last step's expert GEMMs, for check()
         self.gate = Linear(hidden_dim, num_experts, bias_term=False)
@@ -229,6 +237,11 @@ class MoeFeedForward(nn.Module):
         bias2 = self.w2.bias
         if bias2 is not None and world > 1 and dist.get_rank(group=self.proc_group) != 0:
             bias2 = None
+        tokens = expert_weights.numel() // k
+        if (world > 1 and self.overlap_chunks > 1 and self.hidden_dim % (8 * self.overlap_chunks) == 0
+                and tokens * self.hidden_dim * h.element_size() >= OVERLAP_MIN_BYTES
+                and not (self.peer_reduce_tokens >= tokens and self._peer_fits(tokens, h.dtype))):
+            return self._down_combine_overlapped(h, expert_offset, expert_weights, invert_permutation, bias2, ws1)
         with _range("moe.down"):
             y, ws2 = moe_grouped_linear(h, expert_offset, self.w2.weight, bias2, zero_outside=False,
                                         return_workspace=True)
@@ -245,6 +258,36 @@ class MoeFeedForward(nn.Module):
             if world > 1:
                 dist.all_reduce(out, group=self.proc_group)
         return out
+
+    def _peer_fits(self, tokens: int, dtype) -> bool:
+        from .peer_reduce import ONE_SHOT_LIMIT_BYTES
+        return tokens * self.hidden_dim * torch.empty((), dtype=dtype).element_size() <= ONE_SHOT_LIMIT_BYTES
+
+    def _down_combine_overlapped(self, h, expert_offset, expert_weights, invert_permutation, bias2, ws1):
+        """Large batches under tensor parallelism: the down projection and the combine run per
+        slice of the hidden columns, and the all-reduce of slice i (NCCL, on the process
+        group's own stream) overlaps the GEMM of slice i+1.  Same sums as the unsliced path:
+        every output element is produced by one GEMM tile, one combine and one all-reduce."""
+        k = self.num_experts_per_token
+        chunks = self.overlap_chunks
+        Hc = self.hidden_dim // chunks
+        plan = GemmPlan(stages=6)          # leaves shared memory on every SM for the collective's CTAs
+        parts, works, spaces = [], [], [ws1]
+        for c in range(chunks):
+            w_c = self.w2.weight[:, c * Hc:(c + 1) * Hc, :]
+            b_c = bias2[:, c * Hc:(c + 1) * Hc] if bias2 is not None else None
+            with _range(f"moe.down[{c}]"):
+                y_c, ws = moe_grouped_linear(h, expert_offset, w_c, b_c, zero_outside=False, plan=plan,
+                                             return_workspace=True)
+            with _range(f"moe.combine[{c}]"):
+                o_c = OPMX.moe_reduce(y_c.view(*expert_weights.shape, Hc), expert_weights, invert_permutation, k)
+            works.append(dist.all_reduce(o_c, group=self.proc_group, async_op=True))
+            parts.append(o_c)
+            spaces.append(ws)
+        self._last_workspaces = tuple(spaces)
+        for work in works:
+            work.wait()
+        return torch.cat(parts, dim=-1)
 
     def check(self) -> None:
         """Synchronises the device and raises (PmxError, status -6) if a kernel of the last
@@ -264,20 +307,49 @@ class MoeFeedForward(nn.Module):
 
 PATCHED_NAMES = ("moe_select", "moe_column_parallel_linear", "moe_row_parallel_linear", "moe_reduce",
                  "swiglu", "silu", "rms_norm", "skip_rms_norm",
-                 "linear", "column_parallel_linear", "row_parallel_linear")
+                 "linear", "column_parallel_linear", "row_parallel_linear",
+                 "dynamic_batching.multi_head_cache_attention")
+
+
+def _resolve(module, dotted: str):
+    *path, leaf = dotted.split(".")
+    for part in path:
+        module = getattr(module, part)
+    return module, leaf
 
 
 def patch_reference(opmx_module, names=PATCHED_NAMES) -> dict:
     """Rebind operators of an imported OPMX `torch_function` module to this implementation:
     the MoE entry points (the reference resolves them through that module at call time,
     Model.py:191-211 and ModelParallel.py:156,193), the normalisation in front of the block
-    (ModelLayers.py:36-49) and the dense linears around it (ModelLayers.py:69,
-    ModelParallel.py:89,121).  Returns {name: original function} so the caller can undo it
-    (`for n, f in saved.items(): setattr(opmx_module, n, f)`)."""
+    (ModelLayers.py:36-49), the dense linears around it (ModelLayers.py:69,
+    ModelParallel.py:89,121) and the cache attention of decode steps (Model.py:103).  The
+    attention replacement covers decode steps only: for any other call it hands over to the
+    operator it replaced.  Returns {name: original function} so the caller can undo it
+    (`for n, f in saved.items(): unpatch ...` or `unpatch_reference(opmx_module, saved)`)."""
     saved = {}
     for name in names:
         if name not in PATCHED_NAMES:
             raise ValueError(f"{name} is not an operator this package replaces")
-        saved[name] = getattr(opmx_module, name)
-        setattr(opmx_module, name, getattr(OPMX, name))
+        theirs_mod, leaf = _resolve(opmx_module, name)
+        ours_mod, _ = _resolve(OPMX, name)
+        original = getattr(theirs_mod, leaf)
+        ours = getattr(ours_mod, leaf)
+        saved[name] = original
+        if name == "dynamic_batching.multi_head_cache_attention":
+            def attention(*args, _ours=ours, _theirs=original, **kwargs):
+                try:
+                    return _ours(*args, **kwargs)
+                except NotImplementedError:          # a prefill step, a paged or quantised cache, a mask
+                    return _theirs(*args, **kwargs)
+            setattr(theirs_mod, leaf, attention)
+        else:
+            setattr(theirs_mod, leaf, ours)
     return saved
+
+
+def unpatch_reference(opmx_module, saved: dict) -> None:
+    """Puts back what patch_reference() replaced."""
+    for name, fn in saved.items():
+        mod, leaf = _resolve(opmx_module, name)
+        setattr(mod, leaf, fn)

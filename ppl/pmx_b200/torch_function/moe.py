@@ -241,8 +241,25 @@ def moe_grouped_linear(X: torch.Tensor, expert_offset: torch.Tensor, W: torch.Te
     if M == 0:
         return (y, None) if return_workspace else y
     x2 = X.contiguous().view(M, K)
-    w = W.contiguous()
-    b = B.contiguous() if B is not None else None
+    # W may be a window of the feature rows of a wider weight tensor (W_full[:, n0:n1, :]):
+    # it is used in place, with the distance between experts passed as a row pitch
+    pitch = 0
+    if (not W.is_contiguous() and not swiglu and W.stride(2) == 1 and W.stride(1) == K and E > 1
+            and W.stride(0) % K == 0 and W.stride(0) // K >= N and (B is None or B.is_contiguous() is False)):
+        pitch = W.stride(0) // K
+        w = W
+        b = B
+        if b is not None and not (b.stride(1) == 1 and b.stride(0) == pitch):
+            raise ValueError("a bias passed with a window of W must be the same window of the full bias")
+    else:
+        w = W.contiguous()
+        b = B.contiguous() if B is not None else None
+    if pitch:
+        if plan is None:
+            plan = _cabi.GemmPlan()
+        else:
+            plan = _cabi.GemmPlan.from_buffer_copy(plan)
+        plan.w_expert_pitch = pitch
     if expert_offset is None and E != 1:
         raise ValueError("expert_offset may be None only for a single expert")
     off = _offsets_on(expert_offset, dev, E) if expert_offset is not None else None

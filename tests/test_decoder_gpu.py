@@ -23,8 +23,8 @@ def test_reference_decoder_step_with_the_operators_swapped_in():
     cfg = dict(hidden_dim=512, intermediate_dim=1024, num_layers=3, num_heads=8, num_kv_heads=2, vocab_size=1024,
                num_experts=8, num_experts_per_token=2)
     out = bench.run_decoder(ctx, cfg, batch=12, cached=40, steps=2, parity_layers=2)
-    for variant in ("patched", "fused"):
+    for variant in ("patched", "fused", "fused+attention"):
         assert out["parity"][variant]["ok"], out["parity"]
         assert out["parity"][variant]["argmax_agree"] >= 0.9
-    for variant in ("reference", "patched", "fused"):
+    for variant in ("reference", "patched", "fused", "fused+attention"):
         assert out["timing"][variant]["ms_per_step"] > 0 and out["timing"][variant]["moe_ms_per_step"] > 0

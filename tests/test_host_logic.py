@@ -229,27 +229,33 @@ def test_workloads_detie_and_algorithmic_work():
 def test_patch_reference_rebinds_exactly_the_replaced_operators():
     """patch_reference() swaps the operators this package replaces into an imported OPMX
     `torch_function` module (the staged, unmodified reference), leaves every other
-    attribute alone, and its return value undoes it."""
+    attribute alone, and unpatch_reference() undoes it."""
     import oracle
     if oracle.ref_path() is None:
         pytest.skip("the OPMX reference is not staged (python oracle/make_ref.py)")
     import ppl.pmx_b200.torch_function as F
-    from ppl.pmx_b200.moe_layers import patch_reference, PATCHED_NAMES
+    from ppl.pmx_b200.moe_layers import patch_reference, unpatch_reference, PATCHED_NAMES
     opmx = oracle.import_reference()
-    before = dict(vars(opmx))
+    before, before_db = dict(vars(opmx)), dict(vars(opmx.dynamic_batching))
     saved = patch_reference(opmx)
     try:
         assert set(saved) == set(PATCHED_NAMES) == {
             "moe_select", "moe_column_parallel_linear", "moe_row_parallel_linear", "moe_reduce", "swiglu", "silu",
-            "rms_norm", "skip_rms_norm", "linear", "column_parallel_linear", "row_parallel_linear"}
+            "rms_norm", "skip_rms_norm", "linear", "column_parallel_linear", "row_parallel_linear",
+            "dynamic_batching.multi_head_cache_attention"}
         for name, value in vars(opmx).items():
             if name in PATCHED_NAMES:
                 assert value is getattr(F, name) and value is not before[name]
             else:
                 assert value is before[name], f"{name} must not be touched"
+        for name, value in vars(opmx.dynamic_batching).items():
+            if name == "multi_head_cache_attention":
+                assert value is not before_db[name]
+            else:
+                assert value is before_db[name], f"dynamic_batching.{name} must not be touched"
         with pytest.raises(ValueError):
             patch_reference(opmx, names=("multi_head_attention",))
     finally:
-        for name, fn in saved.items():
-            setattr(opmx, name, fn)
-    assert all(getattr(opmx, n) is before[n] for n in PATCHED_NAMES)
+        unpatch_reference(opmx, saved)
+    assert all(getattr(opmx, n) is before[n] for n in PATCHED_NAMES if "." not in n)
+    assert opmx.dynamic_batching.multi_head_cache_attention is before_db["multi_head_cache_attention"]

@@ -151,3 +151,35 @@ def test_onnx_fixture_lists_the_five_nodes():
     assert [n["kind"] for n in nodes] == [
         "opmx::MoeSelect", "opmx::MoeColumnParallelLinear", "opmx::SwiGLU",
         "opmx::MoeRowParallelLinear", "opmx::MoeReduce"]
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_dense_linear_matches_reference(dtype):
+    g = load(f"dense_linear_{dtype}.npz")
+    tol = dict(atol=2e-5, rtol=1e-5) if dtype == "f32" else dict(atol=2e-2, rtol=1e-2)
+    y = orc.linear(g["x"], g["w"])
+    np.testing.assert_allclose(y, g["linear"], **tol)
+    yb = orc.linear(g["x"], g["w"], g["b"])
+    for name in ("linear_bias", "column", "row"):
+        np.testing.assert_allclose(yb, g[name], err_msg=name, **tol)
+    np.testing.assert_allclose(yb, g["linear_bias_fp32"], atol=2e-5, rtol=1e-5)
+
+
+def attention_fixture(name):
+    """-> (fixture dict, cache_in, cache_out) with the caches as float32 values."""
+    g = load(name)
+    conv = (lambda a: a.astype(np.float32)) if str(g["dtype"]) == "f16" else orc.bf16_bits_to_f32
+    return g, conv(g["cache_in"]), conv(g["cache_out"])
+
+
+ATTN = [f"attn_decode_f16_layout{l}.npz" for l in range(4)] + [f"attn_decode_bf16_layout{l}.npz" for l in (0, 3)]
+
+
+@pytest.mark.parametrize("name", ATTN)
+def test_decode_cache_attention_matches_reference(name):
+    g, cache, cache_out = attention_fixture(name)
+    out = orc.decode_cache_attention(g["q"], g["k"], g["v"], cache, g["cachestarts"], g["start_pos"],
+                                     int(g["layout"]), int(g["layer_idx"]))
+    assert np.array_equal(cache, cache_out), "the new keys / values must land where the reference puts them"
+    # the reference rounds the probabilities to the cache dtype before the value product
+    np.testing.assert_allclose(out, g["out"], atol=2e-2, rtol=1e-2)

@@ -371,6 +371,28 @@ def test_grouped_linear_even_row_dealing(F, plan, swiglu):
     run_linear(F, rng, 70, 1808, 2048, 8, "bf16", plan=plan, swiglu=swiglu, off=ragged_offsets(rng, 70, 8, empty=3))
 
 
+@pytest.mark.parametrize("M,dtype", [(40, "f16"), (700, "bf16"), (5000, "bf16"), (33, "f32")])
+def test_grouped_linear_on_a_window_of_the_weight_rows(F, M, dtype):
+    """W given as a strided window W_full[:, n0:n1, :] of a wider weight tensor (the hidden-column
+    slices of the down projection): used in place through the expert row pitch, same result as
+    the contiguous copy, on every kernel the automatic choice picks (decode, prefill, paired, fp32)."""
+    from ppl.pmx_b200.torch_function.moe import moe_grouped_linear
+    rng = np.random.default_rng(M)
+    E, N_full, K = 4, 512, 256
+    x = orc.round_to_dtype(rng.standard_normal((M, K)).astype(np.float32), dtype)
+    w = orc.round_to_dtype((rng.standard_normal((E, N_full, K)) / np.sqrt(K)).astype(np.float32), dtype)
+    b = orc.round_to_dtype(rng.standard_normal((E, N_full)).astype(np.float32), dtype)
+    off = ragged_offsets(rng, M, E, empty=1)
+    xd, wd, bd, od = dev(x, dtype), dev(w, dtype), dev(b, dtype), torch.from_numpy(off).cuda()
+    for n0, n1 in ((0, 128), (128, 384), (384, 512)):
+        ref = orc.moe_grouped_linear(x, off, w[:, n0:n1], b[:, n0:n1])
+        window = wd[:, n0:n1, :]
+        assert not window.is_contiguous() or n1 - n0 == N_full
+        y = moe_grouped_linear(xd, od, window, bd[:, n0:n1])
+        assert_close(y, ref, dtype, f"window [{n0},{n1})")
+        assert torch.equal(y, moe_grouped_linear(xd, od, window.contiguous(), bd[:, n0:n1].contiguous()))
+
+
 def test_grouped_linear_auto_plan_and_fp32(F):
     rng = np.random.default_rng(12)
     run_linear(F, rng, 4500, 256, 128, 4, "bf16", bias=True)   # auto -> paired CTAs (>= 1024 rows per expert)
@@ -403,6 +425,20 @@ def test_dense_linears(F, M, N, K, dtype):
     assert_close(F.router_gate(xd, wd), ref, dtype)
     with pytest.raises(Exception):
         F.row_parallel_linear(xd, wd, None, None, K, N, False)      # the reference raises too
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_dense_linear_golden(F, dtype):
+    """Golden vectors of the reference's linear / column_parallel_linear / row_parallel_linear
+    (run on CPU without a process group)."""
+    g = load(f"dense_linear_{dtype}.npz")
+    x, w, b = dev(g["x"], dtype), dev(g["w"], dtype), dev(g["b"], dtype)
+    K, N = w.shape[1], w.shape[0]
+    assert_close(F.linear(x, w, None, K, N), g["linear"], dtype)
+    assert_close(F.linear(x, w, b, K, N), g["linear_bias"], dtype)
+    assert_close(F.column_parallel_linear(x, w, b, None, K, N, True), g["column"], dtype)
+    assert_close(F.row_parallel_linear(x, w, b, None, K, N, True), g["row"], dtype)
+    assert_close(F.linear(x, w, b, K, N), g["linear_bias_fp32"], dtype)
 
 
 def test_grouped_linear_errors(F):
@@ -653,7 +689,7 @@ def test_reference_moe_block_runs_on_the_patched_operators(F, fused_ffn_glu):
     if oracle.ref_path() is None:
         pytest.skip("the OPMX reference is not staged (python oracle/make_ref.py)")
     from ppl.pmx_b200 import workloads as W
-    from ppl.pmx_b200.moe_layers import patch_reference
+    from ppl.pmx_b200.moe_layers import patch_reference, unpatch_reference
     opmx, model, ModelParams = oracle.import_reference_mixtral()
     sh = W.scaled(W.WORKLOADS["decode_t64"], H=512, I=1024, T=48)
     x, wr, _, _ = W.make_activations(sh)
@@ -674,8 +710,7 @@ def test_reference_moe_block_runs_on_the_patched_operators(F, fused_ffn_glu):
             out = blk(x.cuda())
             sc = F.linear(x.cuda(), blk.gate.weight, None, sh.H, sh.E)
     finally:
-        for name, fn in saved.items():
-            setattr(opmx, name, fn)
+        unpatch_reference(opmx, saved)
     r = orc.moe_block(host(x), host(wr), host(wu), host(w2), sh.E, sh.k, sh.dtype, scores=host(sc),
                       round_intermediates=False)
     assert_close(out, r["out"], sh.dtype)

@@ -75,9 +75,13 @@ def _worker(rank, world, port, q):
         bias_u = torch.cat([bias_u_full[:, rank * Il:(rank + 1) * Il],
                             bias_u_full[:, sh.I + rank * Il: sh.I + (rank + 1) * Il]], 1)
         ref_b = None
-        for fused in (True, False):
+        import ppl.pmx_b200.moe_layers as layers_mod
+        for fused in (True, False, "sliced"):
+            # "sliced": the fused block with the down projection, combine and all-reduce done
+            # per slice of the hidden columns (the all-reduces overlap the next slice's GEMM)
+            layers_mod.OVERLAP_MIN_BYTES = 0 if fused == "sliced" else 1 << 60
             for with_bias in (False, True):
-                blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, with_bias, fused=fused)
+                blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, with_bias, fused=bool(fused), overlap_chunks=2)
                 u, d = W.make_expert_weights(sh, "cpu", tp_rank=rank, tp_size=world)
                 assert blk.wu.weight.shape == u.shape and blk.w2.weight.shape == d.shape
                 with torch.no_grad():

@@ -37,9 +37,13 @@ def _worker(rank, world, port, q):
             f = lambda t: t.detach().float().cpu().numpy()
             ref = orc.moe_block(f(x), f(wr), f(full_u), f(full_d), sh.E, sh.k, sh.dtype, scores=f(sc),
                                 round_intermediates=False)
-            for fused, peer in ((True, 0), (False, 0), (True, sh.T)):
-                blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, False, fused=fused,
-                                     peer_reduce_tokens=peer).to(dev, W.TORCH_DTYPE[sh.dtype])
+            import ppl.pmx_b200.moe_layers as layers_mod
+            for fused, peer in ((True, 0), (False, 0), (True, sh.T), ("sliced", 0)):
+                # "sliced": down projection + combine + all-reduce per slice of the hidden columns,
+                # the all-reduce of a slice overlapping the GEMM of the next one
+                layers_mod.OVERLAP_MIN_BYTES = 0 if fused == "sliced" else 1 << 60
+                blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, False, fused=bool(fused),
+                                     peer_reduce_tokens=peer, overlap_chunks=2).to(dev, W.TORCH_DTYPE[sh.dtype])
                 u, d = W.make_expert_weights(sh, dev, tp_rank=rank, tp_size=world)
                 xd, scd = x.to(dev), sc.to(dev)
                 with torch.no_grad():
