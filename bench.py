@@ -276,7 +276,8 @@ def get_block(ctx, shape, full: bool, w_router=None):
             peer_tokens = max(peer_tokens, 8192)
     blk = MoeFeedForward(shape.H, shape.I, shape.E, shape.k, None if full else ctx.group, False,
                          peer_reduce_tokens=peer_tokens, peer_algorithm=ctx.args.peer_algo,
-                         overlap_chunks=ctx.args.overlap_chunks).to(ctx.device, dt)
+                         overlap_chunks=ctx.args.overlap_chunks,
+                         dense_decode=not ctx.args.no_dense_decode).to(ctx.device, dt)
     wu, w2 = W.make_expert_weights(shape, ctx.device, tp_rank=0 if full else ctx.rank, tp_size=tp)
     if w_router is None:
         _, w_router, _, _ = W.make_activations(shape, detie=False)
@@ -457,13 +458,22 @@ def measure(ctx, shape, steps, warmup, regions, headline):
 
         sync_all(ctx)
         plan = ctx.gemm_plan
-        if OPMX.moe_route_select(x_dev, blk.gate.weight, E, k) is not None:
-            _, xe, ew, inv, off = stage("route_select", lambda: OPMX.moe_route_select(x_dev, blk.gate.weight, E, k))
+        from ppl.pmx_b200.torch_function.moe import dense_gate_up_covers
+        dense = (blk.dense_decode and dense_gate_up_covers(shape.T, blk.wu.weight, k)
+                 and OPMX.moe_route_select(x_dev, blk.gate.weight, E, k, gather=False) is not None)
+        if dense:
+            # the step's own kernels: router without the gather, gate/up from the un-permuted tokens
+            _, _, ew, inv, off = stage("route_select", lambda: OPMX.moe_route_select(x_dev, blk.gate.weight, E, k,
+                                                                                     gather=False))
+            h = stage("gate_up", lambda: OPMX.moe_dense_gate_up(x_dev, inv, off, blk.wu.weight, None))
         else:
-            logits = stage("gate", lambda: OPMX.router_gate(x_dev, blk.gate.weight))
-            xe, ew, inv, off = stage("select", lambda: OPMX.moe_select(x_dev, logits, E, k))
-        h = stage("gate_up", lambda: moe_grouped_linear(xe.view(-1, shape.H), off, blk.wu.weight, None,
-                                                        swiglu=True, zero_outside=False, plan=plan))
+            if OPMX.moe_route_select(x_dev, blk.gate.weight, E, k) is not None:
+                _, xe, ew, inv, off = stage("route_select", lambda: OPMX.moe_route_select(x_dev, blk.gate.weight, E, k))
+            else:
+                logits = stage("gate", lambda: OPMX.router_gate(x_dev, blk.gate.weight))
+                xe, ew, inv, off = stage("select", lambda: OPMX.moe_select(x_dev, logits, E, k))
+            h = stage("gate_up", lambda: moe_grouped_linear(xe.view(-1, shape.H), off, blk.wu.weight, None,
+                                                            swiglu=True, zero_outside=False, plan=plan))
         y = stage("down", lambda: moe_grouped_linear(h, off, blk.w2.weight, None, zero_outside=False, plan=plan))
         if use_peer:
             stage("reduce_allreduce", lambda: blk._peer.combine_allreduce(y, ew, inv, k))
@@ -556,6 +566,7 @@ def measure(ctx, shape, steps, warmup, regions, headline):
                   "allreduce": ((f"peer-memory kernel fused with the combine ({args.peer_algo})" if use_peer else "nccl")
                                 if ctx.world > 1 else None),
                   "allreduce_phases_ns": ar_phases,
+                  "gate_up_from_unpermuted_tokens": bool(dense),
                   "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items() if n in STAGES and v > 0}},
         "parity": parity,
     }
@@ -824,6 +835,9 @@ def main():
                     help="N > 1: fused combine + all-reduce kernel over NVLink peer memory, or moe_reduce + NCCL "
                          "(auto: peer when the [T,H] result is at most 4 MB)")
     ap.add_argument("--peer-algo", default="auto", choices=["auto", "push", "pull"])
+    ap.add_argument("--no-dense-decode", action="store_true",
+                    help="decode-size batches: gather the routed rows first instead of the gate/up projection that "
+                         "reads the un-permuted tokens and overlaps the router")
     ap.add_argument("--overlap-chunks", type=int, default=4,
                     help="N > 1, results too large for the peer kernel: hidden-column slices of the down projection "
                          "whose all-reduces overlap the next slice's GEMM (1: one GEMM, one all-reduce)")

@@ -125,6 +125,8 @@ int pmx_moe_select(const void* x, const void* scores, void* x_expand_permute,
  *   x [T,H] T1, w_router [E,H] T1  ->  scores [T,E] T1 = x . w_router^T (fp32
  *   accumulation, one rounding), then the four outputs of pmx_moe_select computed
  *   from exactly those scores.
+ * x_expand_permute may be NULL: the gathered rows are then not written (for callers that
+ * feed the un-permuted tokens to pmx_moe_dense_gate_up).
  * Covers 1 <= T <= 1024, E <= 64, k <= 32, H*sizeof(T1) a multiple of 16;
  * pmx_moe_route_select_workspace_bytes returns 0 for other shapes (use a linear
  * and pmx_moe_select then).  The blocks of the launch (at most one per SM) meet at
@@ -229,6 +231,33 @@ int pmx_moe_grouped_linear(const void* x, const int64_t* expert_offset,
                            int32_t epilogue, float beta, int32_t zero_outside,
                            const pmx_gemm_plan* plan, void* workspace,
                            size_t workspace_bytes, void* stream);
+
+/*
+ * Gate/up projection with SwiGLU for decode-size batches, computed from the UN-permuted
+ * tokens so that it can overlap the routing: replaces MoeColumnParallelLinear.forward
+ * (torch_function/MoeColumnParallelLinear.py:58-69) + SwiGLU.forward (SwiGLU.py:15-16) as
+ * the Mixtral block calls them (Model.py:198-200), taking x [T,K] instead of the gathered
+ * rows of moe_select:
+ *   h[r,:] = SwiGLU(x[t,:] . w[e]^T (+ bias[e]))  for every token t and every expert e it was
+ *   routed to, r = the row of (t,e) in the expert-sorted order, i.e. the entry of
+ *   invert_permutation[t,:] that lies in [expert_offset[e], expert_offset[e+1]).
+ * h [T*k, N/2] is exactly what pmx_moe_grouped_linear with PMX_EPILOGUE_SWIGLU writes for
+ * the gathered rows.  Every expert's weights are streamed once and multiplied with all T
+ * tokens (tensor-core work is free at these sizes), so nothing but the final stores depends
+ * on the routing: launched directly behind pmx_moe_route_select / pmx_moe_norm_route_select
+ * on the same stream, the weight streaming runs WHILE the router works (programmatic
+ * dependent launch) and the epilogue waits for it.  Requirements: x must already be complete
+ * when the kernel in front of this one on the stream started (it is read before that kernel
+ * finishes); invert_permutation / expert_offset are read only after it has finished.
+ * Covers T <= 128, float16 / bfloat16 (pmx_moe_dense_gate_up_covers); every expert's weights
+ * are read even if no token chose it, so it pays when (nearly) all experts are active.
+ * Workspace: 256 bytes, 16-byte aligned (status words, read by pmx_moe_grouped_linear_check).
+ */
+int pmx_moe_dense_gate_up_covers(int64_t T, int64_t N, int64_t K, int32_t E, int32_t k, int32_t dtype);
+int pmx_moe_dense_gate_up(const void* x, const int64_t* invert_permutation,
+                          const int64_t* expert_offset, const void* w, const void* bias, void* h,
+                          int64_t T, int64_t N, int64_t K, int32_t E, int32_t k, int32_t dtype,
+                          float beta, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Reads back (synchronising `stream`) the self-check record a grouped-linear
  * launch left in its workspace: out[0] = 0 if clean, else a code; out[1..3] =

@@ -60,6 +60,8 @@ def _load() -> C.CDLL:
         "pmx_moe_grouped_linear": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, f32, i32,
                                              plan_p, vp, sz, vp]),
         "pmx_moe_grouped_linear_check": (C.c_int, [vp, C.POINTER(i32 * 4), vp]),
+        "pmx_moe_dense_gate_up_covers": (C.c_int, [i64, i64, i64, i32, i32, i32]),
+        "pmx_moe_dense_gate_up": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, f32, vp, sz, vp]),
         "pmx_swiglu": (C.c_int, [vp, vp, i64, i64, f32, i32, vp]),
         "pmx_silu": (C.c_int, [vp, vp, vp, i64, i32, vp]),
         "pmx_skip_rms_norm": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, f32, i32, vp]),

@@ -236,6 +236,18 @@ int pmx_moe_grouped_linear(const void* x, const int64_t* expert_offset, const vo
   return PMX_OK;
 }
 
+int pmx_moe_dense_gate_up_covers(int64_t T, int64_t N, int64_t K, int32_t E, int32_t k, int32_t dtype) {
+  return dense_gate_up_covers(T, N, K, E, k, dtype) ? 1 : 0;
+}
+
+int pmx_moe_dense_gate_up(const void* x, const int64_t* invert_permutation, const int64_t* expert_offset,
+                          const void* w, const void* bias, void* h, int64_t T, int64_t N, int64_t K, int32_t E,
+                          int32_t k, int32_t dtype, float beta, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  return launch_gemm_tc_dense(x, invert_permutation, expert_offset, w, bias, h, T, N, K, E, k, dtype, beta,
+                              workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
 int pmx_moe_grouped_linear_check(const void* workspace, int32_t out[4], void* stream) {
   if (!workspace || !out) return fail(PMX_ERR_INVALID_ARGUMENT, "grouped_linear_check: null pointer");
   cudaStream_t s = (cudaStream_t)stream;

@@ -185,6 +185,11 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
                    int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue, float beta,
                    const TcPlan& plan, void* ws, size_t ws_bytes, cudaStream_t s);
 
+bool dense_gate_up_covers(int64_t T, int64_t N, int64_t K, int E, int k, int dtype);
+int launch_gemm_tc_dense(const void* x, const int64_t* inv, const int64_t* off, const void* w, const void* bias,
+                         void* h, int64_t T, int64_t N, int64_t K, int E, int k, int dtype, float beta, void* ws,
+                         size_t ws_bytes, cudaStream_t s);
+
 bool plan_gemm_tc_pair(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue,
                        const pmx_gemm_plan* user, TcPlan* plan);
 int launch_gemm_tc_pair(const void* x, const int64_t* off, const void* w, const void* bias, void* y,

@@ -43,7 +43,7 @@ namespace {
 
 #include "tcgen05_common.cuh"
 
-template <typename T, int MODE, bool SWIGLU>
+template <typename T, int MODE, bool SWIGLU, bool DENSE = false>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                        const __grid_constant__ CUtensorMap map_w,
@@ -57,6 +57,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)p.stages * stage_bytes);
   int* s_off = reinterpret_cast<int*>(sh + 1);       // [E+1] row offsets, clamped
   int* s_prefix = s_off + (p.E + 1);                 // [E+1] first work item of each expert
+  int* s_rowmap = s_prefix + (p.E + 1);              // DENSE: [4 warps][128] output row of every token for the current expert
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -86,13 +87,21 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     tmem_alloc(&sh->tmem_base, kTmemCols);
     tmem_relinquish();
   }
-  pdl_wait();
-  // CTA 0 clears the status words (a failed wait is recorded no earlier than
-  // its 2 s limit, long after this store)
-  if (blockIdx.x == 0 && threadIdx.x < 4) p.status[threadIdx.x] = 0;
-  for (int e = threadIdx.x; e <= p.E; e += blockDim.x) {
-    long long o = offset_at(p.off, e, p.M);
-    s_off[e] = (int)(o < 0 ? 0 : (o > p.M ? p.M : o));
+  if (DENSE) {
+    // Every expert is applied to all p.M tokens (operand x itself, not the gathered rows), so
+    // the work list does not depend on the routing and the loads and MMAs start while the
+    // routing kernel in front of this one is still running; only the epilogue warps wait for
+    // it (they need to know which token rows an expert owns, and where they go).
+    for (int e = threadIdx.x; e <= p.E; e += blockDim.x) s_off[e] = e * p.M;
+  } else {
+    pdl_wait();
+    // CTA 0 clears the status words (a failed wait is recorded no earlier than
+    // its 2 s limit, long after this store)
+    if (blockIdx.x == 0 && threadIdx.x < 4) p.status[threadIdx.x] = 0;
+    for (int e = threadIdx.x; e <= p.E; e += blockDim.x) {
+      long long o = offset_at(p.off, e, p.M);
+      s_off[e] = (int)(o < 0 ? 0 : (o > p.M ? p.M : o));
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -123,6 +132,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       work.init(p, total_items);
       bool ok = true;
       while (ok && work.next(p, total_items, s_off, s_prefix, it, item)) {
+        if (DENSE) it.row0 = 0;
         const int wrow = it.e * p.w_pitch + it.f0;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           ok = wait_barrier(&sh->empty[stage], phase ^ 1u, sh, p.status, 0, item);
@@ -221,7 +231,34 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     float* yp = reinterpret_cast<float*>(p.y);
     const T* bias = reinterpret_cast<const T*>(p.bias);
     const int acc_cols = MODE == 0 ? wrows : (SWIGLU ? 2 * tt : tt);   // accumulator columns in use
+    int map_expert = -1;
+    if (DENSE) {
+      pdl_wait();   // the routing (invert_permutation, expert_offset) is complete from here on
+      if (blockIdx.x == 0 && warp == 2 && lane < 4) p.status[lane] = 0;
+    }
     while (work.next(p, total_items, s_off, s_prefix, it, item)) {
+      if (DENSE) {
+        it.row0 = 0;
+        it.row_end = p.M;
+        if (it.e != map_expert) {
+          // which row of the expert-sorted output holds token t for this expert (-1: not routed
+          // here); every epilogue warp keeps its own copy, so no warp waits for another
+          __syncwarp();
+          const long long lo = p.off[it.e], hi = p.off[it.e + 1];
+          for (int t = lane; t < 128; t += 32) {
+            int r = -1;
+            if (t < p.M) {
+              for (int j = 0; j < p.k; ++j) {
+                const long long v = p.inv[(long long)t * p.k + j];
+                if (v >= lo && v < hi) r = (int)v;
+              }
+            }
+            s_rowmap[q * 128 + t] = r;
+          }
+          __syncwarp();
+          map_expert = it.e;
+        }
+      }
       ok = wait_barrier(&sh->acc_full[acc], acc_phase, sh, p.status, 3, item);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
@@ -344,8 +381,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int row = it.row0 + c + i;
-            if (row < it.row_end && f_ok) {
+            const int row = DENSE ? s_rowmap[q * 128 + c + i] : it.row0 + c + i;
+            if ((DENSE ? row >= 0 : row < it.row_end) && f_ok) {
               float v = g[i] + bg;
               if (SWIGLU) v = swiglu_f(v, u[i] + bu, p.beta);
               if (partial)
@@ -373,9 +410,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
 }
 
 // ----------------------------------------------------------------------------- host side
+constexpr size_t kRowMapBytes = 4 * 128 * sizeof(int);   // the dense variant's token -> row maps
+
 size_t smem_bytes_for(const TcPlan& plan, bool swiglu, int E) {
   const size_t stage = (size_t)(plan.tile_tok + (swiglu ? 2 : 1) * plan.tile_feat) * 128;
-  return 1024 + stage * plan.stages + sizeof(Shared) + 2 * (size_t)(E + 1) * sizeof(int);
+  return 1024 + stage * plan.stages + sizeof(Shared) + 2 * (size_t)(E + 1) * sizeof(int) + kRowMapBytes;
 }
 
 template <typename T, int MODE, bool SWIGLU>
@@ -470,7 +509,7 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   if (!kernel_swiglu && pl.kernel == PMX_GEMM_TC_TOKENS_M && !(user && user->tile_feat) && swiglu)
     pl.tile_feat = pow2_at_least(N, 16, 256);
   const size_t stage = (size_t)(pl.tile_tok + (kernel_swiglu ? 2 : 1) * pl.tile_feat) * 128;
-  const size_t fixed = 1024 + sizeof(Shared) + 2 * (size_t)(E + 1) * sizeof(int);
+  const size_t fixed = 1024 + sizeof(Shared) + 2 * (size_t)(E + 1) * sizeof(int) + kRowMapBytes;
   int st = (int)((227 * 1024 - fixed) / stage);
   if (st > kMaxStages) st = kMaxStages;
   if (user && user->stages) st = user->stages < st ? user->stages : st;
@@ -581,6 +620,85 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
     return launch_splitk_finish(reinterpret_cast<const float*>(p.y), off, bias, y, M,
                                 swiglu_any ? N / 2 : N, E, plan.split_k, dtype, swiglu_any, beta, s);
   return PMX_OK;
+}
+
+// ----------------------------------------------------------------------------- dense gate/up
+// h[row(t,e), :] = SwiGLU(x[t] . w[e]^T (+ bias[e])) for every token t routed to expert e, with
+// the products computed for ALL tokens against every expert (weights on MMA-M, the T tokens on
+// MMA-N): the kernel's loads and MMAs need nothing from the routing, so under programmatic
+// dependent launch they overlap the routing kernel in front; only the epilogue waits for it.
+bool dense_gate_up_covers(int64_t T, int64_t N, int64_t K, int E, int k, int dtype) {
+  return T >= 1 && T <= 128 && E >= 1 && E <= kMaxExperts && k >= 1 && k <= E && K % 8 == 0 && K >= 8 && N % 16 == 0 &&
+         (dtype == PMX_DTYPE_F16 || dtype == PMX_DTYPE_BF16) && (int64_t)E * N < (1ll << 31);
+}
+
+int launch_gemm_tc_dense(const void* x, const int64_t* inv, const int64_t* off, const void* w, const void* bias,
+                         void* h, int64_t T, int64_t N, int64_t K, int E, int k, int dtype, float beta, void* ws,
+                         size_t ws_bytes, cudaStream_t s) {
+  if (!x || !inv || !off || !w || !h) return fail(PMX_ERR_INVALID_ARGUMENT, "dense_gate_up: null pointer");
+  if (!dense_gate_up_covers(T, N, K, E, k, dtype))
+    return fail(PMX_ERR_UNSUPPORTED, "dense_gate_up: covers 1..128 tokens, float16 / bfloat16, K a multiple of 8 and N of 16 (T=%lld N=%lld K=%lld)", (long long)T, (long long)N, (long long)K);
+  if (!aligned16(x) || !aligned16(w) || !aligned16(h)) return fail(PMX_ERR_ALIGNMENT, "dense_gate_up: x, w and h must be 16-byte aligned");
+  if (!ws || ws_bytes < kStatusBytes || !aligned16(ws))
+    return fail(PMX_ERR_WORKSPACE, "dense_gate_up: a 16-byte aligned workspace of %zu bytes is needed", kStatusBytes);
+  TcPlan plan{};
+  plan.kernel = PMX_GEMM_TC_WEIGHTS_M;
+  plan.tile_feat = 128;
+  plan.tile_tok = (int)(ceil_div(T, 16) * 16);
+  plan.split_k = 1;
+  plan.balanced = 1;
+  plan.full_rounds = 1;
+  const int sms = sm_count();
+  plan.max_ctas = sms;
+  plan.cta_cap = sms < 128 ? sms : 128;
+  const size_t stage = (size_t)(plan.tile_tok + 2 * plan.tile_feat) * 128;
+  const size_t fixed = 1024 + sizeof(Shared) + 2 * (size_t)(E + 1) * sizeof(int) + kRowMapBytes;
+  // 24 KB of every SM's shared memory stay free, so that a CTA of the routing kernel and a
+  // CTA of this one fit on an SM together
+  int st_n = (int)((203 * 1024 - fixed) / stage);
+  if (st_n > kMaxStages) st_n = kMaxStages;
+  if (st_n < 2) return fail(PMX_ERR_UNSUPPORTED, "dense_gate_up: the stage does not fit in shared memory");
+  plan.stages = st_n;
+
+  const int64_t n_out = N / 2;
+  CUtensorMap mx, mw;
+  int st = make_map(&mx, x, (uint64_t)T, (uint64_t)K, (uint32_t)plan.tile_tok, dtype);
+  if (st != PMX_OK) return st;
+  st = make_map(&mw, w, (uint64_t)E * N, (uint64_t)K, 128u, dtype);
+  if (st != PMX_OK) return st;
+  SmallBoxMaps mws{};
+  for (int b = 0; b < 4; ++b) {
+    st = make_map(&mws.m[b], w, (uint64_t)E * N, (uint64_t)K, (uint32_t)(64 >> b), dtype);
+    if (st != PMX_OK) return st;
+  }
+  Params p{};
+  p.off = off;
+  p.inv = inv;
+  p.k = k;
+  p.bias = bias;
+  p.status = reinterpret_cast<int*>(ws);
+  p.y = h;
+  p.M = (int)T; p.N = (int)N; p.K = (int)K; p.E = E;
+  p.w_pitch = (int)N;
+  p.n_out = (int)n_out;
+  p.tile_tok = plan.tile_tok;
+  p.tile_feat = 128;
+  p.feat_tiles = 1;
+  p.balanced = 1;
+  p.units_per_panel = (int)(n_out / 8);
+  p.kblocks = (int)ceil_div(K, kBlockK);
+  p.split_k = 1;
+  p.kb_per_split = p.kblocks;
+  p.stages = plan.stages;
+  p.beta = beta;
+  p.cta_cap = plan.cta_cap;
+  p.full_rounds = 1;
+  const size_t smem = smem_bytes_for(plan, true, E);
+  const void* kern = dtype == PMX_DTYPE_BF16 ? (const void*)grouped_gemm_tc_kernel<__nv_bfloat16, 1, true, true>
+                                             : (const void*)grouped_gemm_tc_kernel<__half, 1, true, true>;
+  PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  void* args[] = {(void*)&mx, (void*)&mw, (void*)&mws, (void*)&p};
+  return launch_pdl(kern, dim3(plan.max_ctas), dim3(kThreads), smem, s, args);
 }
 
 }  // namespace pmx

@@ -419,8 +419,10 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
   constexpr int V = kVec<T>;
   const int chunks = (int)(H / V);
   if (threadIdx.x == 0) s_abort = 0;
-  pdl_launch_dependents();
+  // The dependent kernel may read x while this one runs (the dense gate/up projection does):
+  // it is released only after this kernel's own predecessors, which produced x, are complete.
   pdl_wait();   // x (and skip) come from the kernel in front of this one
+  pdl_launch_dependents();
 
   // A0. (NORM) normalise my tokens into shared memory
   if (NORM) {
@@ -596,7 +598,8 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
     inv[(int64_t)t0 * k + i] = p;
   }
   __syncthreads();
-  // C. gather my tokens
+  // C. gather my tokens (not wanted by callers that feed the un-permuted tokens to the experts)
+  if (xp == nullptr) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)t0 * H);
   uint4* dst = reinterpret_cast<uint4*>(xp);
   for (int i = threadIdx.x; i < ntok * chunks; i += blockDim.x) {
@@ -918,7 +921,7 @@ int launch_route_select_impl(const void* x, const void* wr, void* scores, void* 
                              int64_t* off, int64_t T, int64_t H, int E, int k, int dtype, void* ws,
                              size_t ws_bytes, cudaStream_t s, bool with_norm, NormArgs norm) {
   const char* name = with_norm ? "moe_norm_route_select" : "moe_route_select";
-  if (!x || !wr || !scores || !xp || !w || !inv || !off) return fail(PMX_ERR_INVALID_ARGUMENT, "%s: null pointer", name);
+  if (!x || !wr || !scores || !w || !inv || !off) return fail(PMX_ERR_INVALID_ARGUMENT, "%s: null pointer", name);
   if (with_norm && (!norm.weight || (norm.skip && !norm.skip_out)))
     return fail(PMX_ERR_INVALID_ARGUMENT, "%s: norm weight missing, or skip given without skip_out", name);
   RouteSelectGeometry g;

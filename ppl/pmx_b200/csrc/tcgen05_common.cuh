@@ -32,6 +32,8 @@ struct Params {
   int stream_k;         // 1: the k-blocks of all work items are dealt out evenly over the CTAs
   int* sk_flags;        // [grid] number of epilogue warps that have stored CTA c's partial tile
   float* sk_slots;      // [grid][256 columns][128 lanes] fp32 partial accumulators
+  const int64_t* inv;   // DENSE: invert_permutation [M tokens, k]
+  int k;                // DENSE: experts per token
   int balanced;         // weight rows on MMA-M only: every CTA works on a contiguous range of the
                         // feature rows of one (expert, token tile, K slice) panel, or on a run of
                         // whole panels, cut into pieces of at most 128 rows in 8-row units

@@ -21,7 +21,8 @@ from torch import nn
 
 from . import torch_function as OPMX
 from ._cabi import GemmPlan
-from .torch_function.moe import moe_grouped_linear, moe_route_select, moe_norm_route_select
+from .torch_function.moe import (moe_grouped_linear, moe_route_select, moe_norm_route_select, moe_dense_gate_up,
+                                 dense_gate_up_covers)
 
 # below this many bytes of [T,H] result one all-reduce is cheaper than overlapped slices
 OVERLAP_MIN_BYTES = 8 << 20
@@ -168,7 +169,7 @@ class MoeFeedForward(nn.Module):
     def __init__(self, hidden_dim: int, intermediate_dim: int, num_experts: int,
                  num_experts_per_token: int, proc_group=None, linear_bias_term: bool = False,
                  fused: bool = True, peer_reduce_tokens: int = 0, peer_algorithm: str = "auto",
-                 overlap_chunks: int = 4) -> None:
+                 overlap_chunks: int = 4, dense_decode: bool = True) -> None:
         super().__init__()
         self.num_experts = num_experts
         self.num_experts_per_token = num_experts_per_token
@@ -182,6 +183,8 @@ class MoeFeedForward(nn.Module):
         # tensor-parallel batches too large for the peer kernel: hidden-column slices whose
         # all-reduces overlap the following slice's GEMM (1 = one GEMM, one all-reduce)
         self.overlap_chunks = overlap_chunks
+        # decode-size batches: gate/up projection from the un-permuted tokens, overlapping the router
+        self.dense_decode = dense_decode
         self._peer = None
         self._last_workspaces = ()     # status words of the last step's expert GEMMs, for check()
         self.gate = Linear(hidden_dim, num_experts, bias_term=False)
@@ -211,6 +214,19 @@ class MoeFeedForward(nn.Module):
     def forward(self, x: torch.Tensor, router_logits: torch.Tensor | None = None) -> torch.Tensor:
         E, k = self.num_experts, self.num_experts_per_token
         routed = None
+        tokens = x.numel() // x.shape[-1] if x.shape[-1] else 0
+        if (router_logits is None and self.fused and self.dense_decode and tokens > 0
+                and dense_gate_up_covers(tokens, self.wu.weight, k)):
+            # decode-size batch with (almost surely) every expert in use: the gate/up projection
+            # reads the un-permuted tokens and streams its weights while the router is running
+            with _range("moe.route_select"):
+                routed = moe_route_select(x, self.gate.weight, E, k, gather=False)
+            if routed is not None:
+                _, _, expert_weights, invert_permutation, expert_offset = routed
+                with _range("moe.gate_up_swiglu(dense)"):
+                    h, ws1 = moe_dense_gate_up(x, invert_permutation, expert_offset, self.wu.weight, self.wu.bias,
+                                               return_workspace=True)
+                return self._down_combine(h, ws1, expert_weights, invert_permutation, expert_offset)
         with _range("moe.route_select"):
             if router_logits is None and self.fused:
                 routed = moe_route_select(x, self.gate.weight, E, k)     # decode-size batches: one launch
@@ -234,6 +250,12 @@ class MoeFeedForward(nn.Module):
         with _range("moe.gate_up_swiglu"):
             h, ws1 = moe_grouped_linear(flat, expert_offset, self.wu.weight, self.wu.bias, swiglu=True,
                                         zero_outside=False, return_workspace=True)
+        return self._down_combine(h, ws1, expert_weights, invert_permutation, expert_offset)
+
+    def _down_combine(self, h, ws1, expert_weights, invert_permutation, expert_offset):
+        """down GEMM -> combine (+ exchange over TP) on the gate/up result h [T*k, I/tp]."""
+        k = self.num_experts_per_token
+        world = _world(self.proc_group)
         bias2 = self.w2.bias
         if bias2 is not None and world > 1 and dist.get_rank(group=self.proc_group) != 0:
             bias2 = None

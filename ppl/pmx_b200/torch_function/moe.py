@@ -131,14 +131,16 @@ def route_select_check(workspace: torch.Tensor | None = None, device=None) -> No
 
 
 def moe_route_select(X: torch.Tensor, W_router: torch.Tensor, num_experts: int, num_experts_per_token: int,
-                     workspace: torch.Tensor | None = None):
+                     workspace: torch.Tensor | None = None, gather: bool = True):
     """Router gate and moe_select in one launch for decode-size batches:
     scores = X @ W_router.T (Linear.py:24-33 as called at Model.py:188), then
     MoeSelect (MoeSelect.py:36-64) on those scores.
     -> (scores [*,E], X_expand_permute, expert_weights, invert_permutation, expert_offset),
     or None when the shape is outside what the fused kernel covers (more than 1024
     tokens, more than 64 experts, ...): call a linear and moe_select then.
-    `workspace`: see _cabi.barrier_workspace (default: one kept buffer per device)."""
+    `workspace`: see _cabi.barrier_workspace (default: one kept buffer per device).
+    gather=False: X_expand_permute is not produced (None is returned in its place), for the
+    dense gate/up projection that reads the un-permuted tokens."""
     _require_cuda("moe_route_select", X=X, W_router=W_router)
     k, E = int(num_experts_per_token), int(num_experts)
     lead, H = tuple(X.shape[:-1]), X.shape[-1]
@@ -155,7 +157,7 @@ def moe_route_select(X: torch.Tensor, W_router: torch.Tensor, num_experts: int, 
     x2 = X.contiguous().view(T, H)
     wr = W_router.contiguous()
     scores = torch.empty(*lead, E, dtype=X.dtype, device=dev)
-    xp = torch.empty(*lead, k, H, dtype=X.dtype, device=dev)
+    xp = torch.empty(*lead, k, H, dtype=X.dtype, device=dev) if gather else None
     w = torch.empty(*lead, k, dtype=X.dtype, device=dev)
     inv = torch.empty(*lead, k, dtype=torch.int64, device=dev)
     off = torch.empty(E + 1, dtype=torch.int64, device=dev)
@@ -274,6 +276,44 @@ def moe_grouped_linear(X: torch.Tensor, expert_offset: torch.Tensor, W: torch.Te
                                          float(beta), 1 if zero_outside else 0, plan_ref, ptr(ws),
                                          ws.numel(), stream_of(X)))
     return (y, ws) if return_workspace else y
+
+
+def dense_gate_up_covers(T: int, W: torch.Tensor, k: int) -> bool:
+    """Whether moe_dense_gate_up takes this shape AND pays: every expert's weights are streamed
+    even if no token chose it, so the chance of an unused expert, ((E-k)/E)^T, must be small."""
+    E, N, K = W.shape
+    code = DTYPE_CODE.get(W.dtype)
+    if code is None or not lib.pmx_moe_dense_gate_up_covers(T, N, K, E, k, code):
+        return False
+    return ((E - k) / E) ** T < 0.02
+
+
+def moe_dense_gate_up(X: torch.Tensor, invert_permutation: torch.Tensor, expert_offset: torch.Tensor,
+                      W: torch.Tensor, B: torch.Tensor | None = None, beta: float = 1.0,
+                      return_workspace: bool = False):
+    """H[r] = SwiGLU(X[t] @ W[e].T (+ B[e])) for every (token t, chosen expert e), r = the row of
+    that pair in the expert-sorted order: what moe_column_parallel_linear + swiglu give for
+    the rows moe_select gathers (MoeColumnParallelLinear.py:58-69, SwiGLU.py:15-16), computed
+    from the un-permuted X [T,K].  Launch it directly behind moe_route_select on the same
+    stream: the weight streaming then overlaps the router (see pmx_moe_dense_gate_up)."""
+    _require_cuda("moe_dense_gate_up", X=X, W=W, B=B, invert_permutation=invert_permutation)
+    E, N, K = W.shape
+    T = X.numel() // K
+    k = invert_permutation.shape[-1]
+    code = _dtype_code("moe_dense_gate_up", X)
+    if W.dtype != X.dtype or (B is not None and B.dtype != X.dtype):
+        raise TypeError("X, W and B must have the same dtype")
+    dev = X.device
+    h = torch.empty(T * k, N // 2, dtype=X.dtype, device=dev)
+    ws = workspace(256, dev)
+    x2, w = X.contiguous().view(T, K), W.contiguous()
+    b = B.contiguous() if B is not None else None
+    inv = invert_permutation.contiguous()
+    off = _offsets_on(expert_offset, dev, E)
+    with torch.cuda.device(dev):
+        check(lib.pmx_moe_dense_gate_up(ptr(x2), ptr(inv), ptr(off), ptr(w), ptr(b), ptr(h), T, N, K, E, k, code,
+                                        float(beta), ptr(ws), ws.numel(), stream_of(X)))
+    return (h, ws) if return_workspace else h
 
 
 def grouped_linear_check(ws: torch.Tensor) -> None:

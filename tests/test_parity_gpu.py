@@ -393,6 +393,72 @@ def test_grouped_linear_on_a_window_of_the_weight_rows(F, M, dtype):
         assert torch.equal(y, moe_grouped_linear(xd, od, window.contiguous(), bd[:, n0:n1].contiguous()))
 
 
+@pytest.mark.parametrize("T,H,E,k,N,dtype", [(64, 512, 8, 2, 1024, "f16"), (16, 256, 8, 2, 3584, "f16"),
+                                             (100, 320, 16, 4, 528, "bf16"), (128, 512, 8, 8, 256, "bf16"),
+                                             (1, 256, 4, 1, 272, "f16"), (37, 4096, 8, 2, 2048, "f16")])
+def test_dense_gate_up_matches_the_routed_projection(F, T, H, E, k, N, dtype):
+    """The gate/up projection computed from the un-permuted tokens (every expert against all
+    tokens, the routing applied in the epilogue) against the routed grouped GEMM on the
+    gathered rows and against the oracle; one expert is left without tokens."""
+    from ppl.pmx_b200.torch_function.moe import moe_grouped_linear, grouped_linear_check
+    rng = np.random.default_rng(T + N)
+    x = orc.round_to_dtype(rng.standard_normal((T, H)).astype(np.float32), dtype)
+    sc = rng.standard_normal((T, E)).astype(np.float32)
+    if E > k:
+        sc[:, E // 2] = -1e4                       # nobody picks this expert
+    sc, _ = orc.detie_scores(sc, dtype)
+    w = orc.round_to_dtype((rng.standard_normal((E, N, H)) / np.sqrt(H)).astype(np.float32), dtype)
+    b = orc.round_to_dtype(rng.standard_normal((E, N)).astype(np.float32), dtype)
+    xd, wd, bd = dev(x, dtype), dev(w, dtype), dev(b, dtype)
+    xe, ew, inv, off = F.moe_select(xd, dev(sc, dtype), E, k)
+    for bias in (None, bd):
+        h, ws = F.moe_dense_gate_up(xd, inv, off, wd, bias, return_workspace=True)
+        grouped_linear_check(ws)
+        routed = moe_grouped_linear(xe.view(-1, H), off, wd, bias, swiglu=True, zero_outside=False)
+        oxe, _, _, ooff = orc.moe_select(x, sc, E, k, dtype)
+        ref = orc.swiglu(orc.moe_grouped_linear(oxe, ooff, w, None if bias is None else b))
+        assert_close(h, ref, dtype)
+        assert_close(h, host(routed), dtype)
+    assert h.shape == (T * k, N // 2)
+
+
+def test_block_dense_decode_path_equals_the_routed_path(F):
+    """MoeFeedForward with the router + dense gate/up path (decode-size batch) against the
+    same block with that path switched off, eagerly and replayed from a CUDA graph."""
+    from ppl.pmx_b200 import workloads as W
+    from ppl.pmx_b200.moe_layers import MoeFeedForward
+    sh = W.scaled(W.WORKLOADS["decode_t64"], H=512, I=1024)
+    x, wr, _, _ = W.make_activations(sh)
+    wu, w2 = W.make_expert_weights(sh, "cuda")
+    blocks = []
+    for dense in (True, False):
+        blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, None, False, dense_decode=dense).cuda().half()
+        with torch.no_grad():
+            blk.gate.weight.copy_(wr)
+            blk.wu.weight.copy_(wu)
+            blk.w2.weight.copy_(w2)
+        blocks.append(blk)
+    xd = x.cuda()
+    with torch.no_grad():
+        a, b = blocks[0](xd), blocks[1](xd)
+        torch.cuda.synchronize()
+        blocks[0].check()
+        torch.testing.assert_close(a.float(), b.float(), atol=2e-3, rtol=2e-3)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            blocks[0](xd)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = blocks[0](xd)
+        for _ in range(5):
+            g.replay()
+        torch.cuda.synchronize()
+        torch.testing.assert_close(out.float(), b.float(), atol=2e-3, rtol=2e-3)
+        g.reset()
+
+
 def test_grouped_linear_auto_plan_and_fp32(F):
     rng = np.random.default_rng(12)
     run_linear(F, rng, 4500, 256, 128, 4, "bf16", bias=True)   # auto -> paired CTAs (>= 1024 rows per expert)
