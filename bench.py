@@ -810,6 +810,63 @@ def run_decoder(ctx, cfg, batch, cached, steps, parity_layers=2):
     return out
 
 
+def measure_attention(ctx, steps, batch=64, cached=2048, heads=32, kv_heads=8, head_dim=128, layers=4):
+    """The decode-step cache attention kernel at the full decoder's shape on this rank's share of
+    the heads (fp16, one layer of a `layers`-deep cache in the reference's layouts 0 and 3):
+    time by graph replay, algorithmic bytes = every cached key and value of the layer read once,
+    parity of a few sequences against fp32 torch math on the same device."""
+    import ppl.pmx_b200.torch_function as OPMX
+    world, dev = ctx.world, ctx.device
+    if heads % world or kv_heads % world:
+        return None
+    Hq, Hkv = heads // world, kv_heads // world
+    g = torch.Generator(device=dev).manual_seed(3)
+    cap = cached + 8
+    rows = batch * cap
+    q = torch.randn(batch, Hq, head_dim, generator=g, device=dev, dtype=torch.float16)
+    kn = torch.randn(batch, Hkv, head_dim, generator=g, device=dev, dtype=torch.float16)
+    vn = torch.randn(batch, Hkv, head_dim, generator=g, device=dev, dtype=torch.float16)
+    start_pos = torch.full((batch,), cached, dtype=torch.int64, device=dev)
+    cachestarts = torch.arange(0, rows, cap, dtype=torch.int64, device=dev)
+    seqstarts = torch.arange(0, batch + 1, dtype=torch.int64, device=dev)
+    kvstarts = torch.arange(0, (batch + 1) * (cached + 1), cached + 1, dtype=torch.int64, device=dev)
+    one, nb, kvmax = torch.tensor([1]), torch.tensor([batch]), torch.tensor([cached + 1])
+    out = {}
+    for layout in (0, 3):
+        shape = (rows, layers, 2, Hkv, head_dim) if layout == 0 else (layers, 2, Hkv, rows, head_dim)
+        cache = torch.randn(shape, generator=g, device=dev, dtype=torch.float16)
+
+        def call():
+            return OPMX.dynamic_batching.multi_head_cache_attention(
+                q, kn, vn, seqstarts, kvstarts, cachestarts, start_pos, nb, one, kvmax, cache, None, None, Hq,
+                head_dim, True, False, Hkv, layers, 1, 0, 8, 0, layout)
+        with torch.no_grad():
+            res = call()
+            graph, _ = capture(call)
+            ms = timed(ctx, graph.replay, steps) / steps
+            graph.reset()
+        # parity on three sequences: fp32 softmax(q K^T / sqrt(d)) V over the cached rows + the new token
+        view = cache[:, 1] if layout == 0 else cache[1].permute(2, 0, 1, 3)      # [rows, 2, Hkv, d]
+        worst = 0.0
+        for b in (0, batch // 2, batch - 1):
+            r0 = int(cachestarts[b])
+            keys = view[r0:r0 + cached + 1, 0].float()
+            vals = view[r0:r0 + cached + 1, 1].float()
+            for h in range(Hq):
+                sc = keys[:, h // (Hq // Hkv)] @ q[b, h].float() / head_dim ** 0.5
+                want = torch.softmax(sc, 0) @ vals[:, h // (Hq // Hkv)]
+                worst = max(worst, float((res[b, h].float() - want).abs().max()))
+        nbytes = 2.0 * batch * (cached + 1) * Hkv * head_dim * 2
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[f"layout{layout}"] = {"ms": ms, "algorithmic_bytes": nbytes, "achieved_gbs": gbs,
+                                  "frac_of_hbm_peak": gbs / ctx.peaks["hbm_gbs"], "max_abs_err": worst,
+                                  "ok": worst <= ATOL}
+        del cache
+    out["config"] = {"batch": batch, "cached_tokens": cached, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": head_dim,
+                     "parallelism": f"tp{world}", "dtype": "f16"}
+    return out
+
+
 def parse_plan(text):
     from ppl.pmx_b200._cabi import GemmPlan
     if not text:
@@ -825,7 +882,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=HEADLINE, help="the workload of the headline figures")
     ap.add_argument("--extra", default=None,
-                    help="comma-separated workloads reported in the `workloads` array ('' for none; default: all "
+                    help="comma-separated workloads reported in the `workloads` array ('none' for none; default: all "
                          "the other configurations when the headline is the default one)")
     ap.add_argument("--regions", type=int, default=5, help="timed regions of K steps per workload (median reported)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
@@ -892,7 +949,7 @@ def main():
 
     head = measure(ctx, shape, args.steps, args.warmup, args.regions, headline=True)
     extra_names = (EXTRA_WORKLOADS if args.workload == HEADLINE else []) if args.extra is None else \
-        [n for n in args.extra.split(",") if n]
+        [n for n in args.extra.split(",") if n and n != "none"]
     extras = []
     for name in extra_names:
         sh = shape_of(name)
@@ -907,6 +964,7 @@ def main():
         if rank == 0:
             extras.append(rec)
 
+    attention = measure_attention(ctx, min(args.steps, 100)) if args.workload == HEADLINE and args.ffn_div == 1 else None
     decoder = None
     import oracle
     want_decoder = args.decoder == "on" or (args.decoder == "auto" and world == 8 and args.workload == HEADLINE)
@@ -941,6 +999,8 @@ def main():
             "parity": head["parity"],
             "workloads": extras,
         }
+        if attention is not None:
+            line["decode_attention"] = attention
         if decoder is not None:
             line["decoder"] = decoder
         if world == 1 and not args.no_cpu_baseline:

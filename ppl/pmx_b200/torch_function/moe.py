@@ -279,11 +279,18 @@ def moe_grouped_linear(X: torch.Tensor, expert_offset: torch.Tensor, W: torch.Te
 
 
 def dense_gate_up_covers(T: int, W: torch.Tensor, k: int) -> bool:
-    """Whether moe_dense_gate_up takes this shape AND pays: every expert's weights are streamed
-    even if no token chose it, so the chance of an unused expert, ((E-k)/E)^T, must be small."""
+    """Whether moe_dense_gate_up takes this shape AND pays.  Measured on B200 (Mixtral shapes,
+    64 tokens): hiding the router saves 6-7 us per step, but the larger token tile (all T tokens
+    instead of an expert's share) costs one ring stage, about 5 % of the weight-streaming time,
+    and every expert's weights are read even if no token chose it.  So: at most 64 tokens, a
+    launch of at most two 128-row weight tiles per working CTA (the thin shards of tensor
+    parallelism, where the router is a tenth of the step), and a chance of an unused expert,
+    ((E-k)/E)^T, below 2 %."""
     E, N, K = W.shape
     code = DTYPE_CODE.get(W.dtype)
-    if code is None or not lib.pmx_moe_dense_gate_up_covers(T, N, K, E, k, code):
+    if T > 64 or code is None or not lib.pmx_moe_dense_gate_up_covers(T, N, K, E, k, code):
+        return False
+    if E * ((N // 2 + 127) // 128) > 2 * 128:
         return False
     return ((E - k) / E) ** T < 0.02
 

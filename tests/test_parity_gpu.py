@@ -427,9 +427,12 @@ def test_block_dense_decode_path_equals_the_routed_path(F):
     same block with that path switched off, eagerly and replayed from a CUDA graph."""
     from ppl.pmx_b200 import workloads as W
     from ppl.pmx_b200.moe_layers import MoeFeedForward
+    from ppl.pmx_b200.torch_function.moe import dense_gate_up_covers
     sh = W.scaled(W.WORKLOADS["decode_t64"], H=512, I=1024)
     x, wr, _, _ = W.make_activations(sh)
     wu, w2 = W.make_expert_weights(sh, "cuda")
+    assert dense_gate_up_covers(sh.T, wu, sh.k), "this shape must take the dense path"
+    assert not dense_gate_up_covers(128, wu, sh.k) and not dense_gate_up_covers(4, wu, sh.k)
     blocks = []
     for dense in (True, False):
         blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, None, False, dense_decode=dense).cuda().half()
