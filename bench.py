@@ -907,6 +907,8 @@ def main():
     ap.add_argument("--decoder-layers", type=int, default=32)
     ap.add_argument("--decoder-batch", type=int, default=64)
     ap.add_argument("--decoder-cached", type=int, default=2048)
+    ap.add_argument("--attention-only", action="store_true",
+                    help="measure only the decode-step cache attention kernel and print its record")
     ap.add_argument("--ffn-div", type=int, default=1,
                     help="divide the ffn size by this (small cases for profiler captures; traffic and flops scale with it)")
     args = ap.parse_args()
@@ -947,6 +949,13 @@ def main():
         _cabi.lib.pmx_moe_set_programmatic_launch(0)
     ctx.gemm_plan = parse_plan(args.gemm_plan)
 
+    if args.attention_only:
+        rec = measure_attention(ctx, min(args.steps, 100))
+        if rank == 0:
+            print(json.dumps({"decode_attention": rec}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     head = measure(ctx, shape, args.steps, args.warmup, args.regions, headline=True)
     extra_names = (EXTRA_WORKLOADS if args.workload == HEADLINE else []) if args.extra is None else \
         [n for n in args.extra.split(",") if n and n != "none"]

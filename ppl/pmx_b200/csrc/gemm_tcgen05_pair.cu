@@ -231,33 +231,42 @@ grouped_gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x,
       const int row = it.row0 + (int)rank * 128 + q * 32 + lane;
       const bool row_ok = row < it.row_end;
       const T* be = bias ? bias + (int64_t)it.e * p.w_pitch : nullptr;
-      for (int c = 0; c < ft; c += 16) {
-        float g[16], u[16];
-        __syncwarp();
-        tmem_ld16(taddr + c, g);
-        if (SWIGLU) tmem_ld16(taddr + ft + c, u);
-        tmem_wait_ld();
-        const int col = it.f0 + c;
-        if (col < p.n_out && row_ok) {
-          if (be) {
+      // 16 accumulator columns of this thread's row: bias, SwiGLU, cast, store
+      auto emit = [&](int col, float (&g)[16], float (&u)[16]) {
+        if (col >= p.n_out || !row_ok) return;
+        if (be) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (col + i < p.n_out) {
-                g[i] += Elem<T>::to_f(be[col + i]);
-                if (SWIGLU) u[i] += Elem<T>::to_f(be[p.n_out + col + i]);
-              }
-          }
-          if (SWIGLU) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) g[i] = swiglu_f(g[i], u[i], p.beta);
-          }
-          T* dst = y + (int64_t)row * p.n_out + col;
-          if (col + 16 <= p.n_out) {
-            store16<T>(dst, g);
-          } else {
-            for (int i = 0; i < 16 && col + i < p.n_out; ++i) dst[i] = Elem<T>::from_f(g[i]);
-          }
+          for (int i = 0; i < 16; ++i)
+            if (col + i < p.n_out) {
+              g[i] += Elem<T>::to_f(be[col + i]);
+              if (SWIGLU) u[i] += Elem<T>::to_f(be[p.n_out + col + i]);
+            }
         }
+        if (SWIGLU) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) g[i] = swiglu_f(g[i], u[i], p.beta);
+        }
+        T* dst = y + (int64_t)row * p.n_out + col;
+        if (col + 16 <= p.n_out) {
+          store16<T>(dst, g);
+        } else {
+          for (int i = 0; i < 16 && col + i < p.n_out; ++i) dst[i] = Elem<T>::from_f(g[i]);
+        }
+      };
+      // 32 columns per round: both halves' tensor-memory loads are in flight before the wait
+      for (int c = 0; c < ft; c += 32) {
+        const bool two = c + 32 <= ft;
+        float g0[16], g1[16], u0[16], u1[16];
+        __syncwarp();
+        tmem_ld16(taddr + c, g0);
+        if (two) tmem_ld16(taddr + c + 16, g1);
+        if (SWIGLU) {
+          tmem_ld16(taddr + ft + c, u0);
+          if (two) tmem_ld16(taddr + ft + c + 16, u1);
+        }
+        tmem_wait_ld();
+        emit(it.f0 + c, g0, u0);
+        if (two) emit(it.f0 + c + 16, g1, u1);
       }
       tc_fence_before();
       __syncwarp();
