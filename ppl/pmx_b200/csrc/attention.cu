@@ -10,9 +10,9 @@
 //
 // HBM-bound: every cached key and value of the layer is read once.  The work is split over
 // (sequence, kv head, slice of the cached positions); a CTA streams its slice once for all
-// query heads that share the kv head, one position per warp at a time (a 256-byte row is one
-// coalesced load of the warp), with the running maximum / sum / weighted value sum of an
-// online softmax in registers.  The slices of a (sequence, kv head) are merged by a second,
+// query heads that share the kv head with 16-byte loads (a warp fetches 2 or 4 head rows per
+// instruction, several instructions in flight), with the running maximum / sum / weighted
+// value sum of an online softmax in registers.  The slices of a (sequence, kv head) are merged by a second,
 // tiny kernel.  All cache layouts of cache_mode 0 are covered through strides.
 #include "common.cuh"
 
@@ -20,7 +20,8 @@ namespace pmx {
 namespace {
 
 constexpr int kAttnWarps = 4;
-constexpr int kMaxGroup = 8;       // query heads per kv head
+constexpr int kGroupLimit = 8;     // query heads per kv head
+constexpr int kUnroll = 4;         // cached positions a warp works on per round
 
 struct AttnParams {
   const void* q;        // [B, Hq, D]
@@ -36,12 +37,19 @@ struct AttnParams {
   float scale;
 };
 
-template <typename T, int VPL>   // VPL = head_dim / 32 values per lane
-__global__ void __launch_bounds__(kAttnWarps * 32)
+// A head row (D 16-bit values) is read by D/8 lanes with one 16-byte load each, so a warp
+// fetches 32/(D/8) positions per load instruction (2 for D = 128, 4 for D = 64).  Every such
+// group of lanes runs its own online softmax over the positions it sees; the groups of a
+// warp are merged with shuffles, the warps of the CTA through shared memory.
+template <typename T, int D, int GMAX>   // GMAX: query heads per kv head the registers are sized for (>= the actual number)
+__global__ void __launch_bounds__(kAttnWarps * 32, 3)
 decode_attention_kernel(const AttnParams p) {
-  constexpr int D = VPL * 32;
+  constexpr int kMaxGroup = GMAX;
+  constexpr int LPP = D / 8;          // lanes per position
+  constexpr int PPL = 32 / LPP;       // positions per load instruction of a warp
   const int b = blockIdx.x, h = blockIdx.y, s = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane / LPP, sl = lane % LPP;      // which position of the load, which 8 dims of the row
   const int G = p.Hq / p.Hkv;
   __shared__ float sm_acc[kAttnWarps][kMaxGroup][D];
   __shared__ float sm_m[kAttnWarps][kMaxGroup], sm_l[kAttnWarps][kMaxGroup];
@@ -52,94 +60,130 @@ decode_attention_kernel(const AttnParams p) {
   const int64_t row0 = p.cachestarts[b];
   const T* q = reinterpret_cast<const T*>(p.q) + ((int64_t)b * p.Hq + (int64_t)h * G) * D;
   T* cache = reinterpret_cast<T*>(p.cache);
-  const int64_t base = p.layer_off + (int64_t)h * p.head_stride;
+  const int64_t base = p.layer_off + (int64_t)h * p.head_stride + sl * 8;
 
-  // this lane's VPL dims of every query of the group, pre-scaled
-  float qv[kMaxGroup][VPL];
+  // this lane's 8 dims of every query of the group, pre-scaled
+  float qv[kMaxGroup][8];
 #pragma unroll
   for (int g = 0; g < kMaxGroup; ++g) {
     if (g < G) {
+      float f[8];
+      unpack16<T>(ld_nc16(q + (int64_t)g * D + sl * 8), f);
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) qv[g][v] = Elem<T>::to_f(q[(int64_t)g * D + lane * VPL + v]) * p.scale;
+      for (int v = 0; v < 8; ++v) qv[g][v] = f[v] * p.scale;
     }
   }
   // the new key / value of this sequence and kv head: stored into the cache by the CTA of
   // slice 0 and taken from registers (not from the cache) by whoever owns position pos_new
-  float kn[VPL], vn[VPL];
-  {
-    const T* kc = reinterpret_cast<const T*>(p.k_cur) + ((int64_t)b * p.Hkv + h) * D + lane * VPL;
-    const T* vc = reinterpret_cast<const T*>(p.v_cur) + ((int64_t)b * p.Hkv + h) * D + lane * VPL;
-#pragma unroll
-    for (int v = 0; v < VPL; ++v) {
-      kn[v] = Elem<T>::to_f(kc[v]);
-      vn[v] = Elem<T>::to_f(vc[v]);
-    }
-    if (s == 0 && warp == 0) {
-      T* krow = cache + base + (row0 + pos_new) * p.row_stride + lane * VPL;
-#pragma unroll
-      for (int v = 0; v < VPL; ++v) {
-        krow[v] = kc[v];
-        krow[p.kv_stride + v] = vc[v];
-      }
-    }
+  const T* kc = reinterpret_cast<const T*>(p.k_cur) + ((int64_t)b * p.Hkv + h) * D + sl * 8;
+  const T* vc = reinterpret_cast<const T*>(p.v_cur) + ((int64_t)b * p.Hkv + h) * D + sl * 8;
+  const uint4 kn = ld_nc16(kc), vn = ld_nc16(vc);
+  if (s == 0 && warp == 0 && sub == 0) {
+    T* krow = cache + base + (row0 + pos_new) * p.row_stride;
+    *reinterpret_cast<uint4*>(krow) = kn;
+    *reinterpret_cast<uint4*>(krow + p.kv_stride) = vn;
   }
-  float m[kMaxGroup], l[kMaxGroup], acc[kMaxGroup][VPL];
+  float m[kMaxGroup], l[kMaxGroup], acc[kMaxGroup][8];
 #pragma unroll
   for (int g = 0; g < kMaxGroup; ++g) {
     m[g] = -INFINITY;
     l[g] = 0.f;
 #pragma unroll
-    for (int v = 0; v < VPL; ++v) acc[g][v] = 0.f;
+    for (int v = 0; v < 8; ++v) acc[g][v] = 0.f;
   }
   const int64_t p_begin = (int64_t)s * p.chunk;
   const int64_t p_end = min(kvlen, p_begin + p.chunk);
-  for (int64_t pos = p_begin + warp; pos < p_end; pos += kAttnWarps) {
-    float kf[VPL], vf[VPL];
-    if (pos == pos_new) {
+  // kUnroll load rounds per iteration: 2 x kUnroll 16-byte loads of every lane are in flight
+  // before the first is used, and the dot products reduce as independent shuffle chains
+  constexpr int kStep = PPL * kUnroll;          // positions of a warp per iteration
+  for (int64_t pos0 = p_begin + (int64_t)warp * kStep; pos0 < p_end; pos0 += kAttnWarps * kStep) {
+    uint4 kraw[kUnroll], vraw[kUnroll];
+    bool valid[kUnroll];
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) { kf[v] = kn[v]; vf[v] = vn[v]; }
-    } else {
-      const T* krow = cache + base + (row0 + pos) * p.row_stride + lane * VPL;
-      // VPL 16-bit (or 32-bit) values per lane: one 8- or 16-byte load
-      T kraw[VPL], vraw[VPL];
-      if (sizeof(T) * VPL == 8) {
-        *reinterpret_cast<uint2*>(kraw) = __ldg(reinterpret_cast<const uint2*>(krow));
-        *reinterpret_cast<uint2*>(vraw) = __ldg(reinterpret_cast<const uint2*>(krow + p.kv_stride));
-      } else if (sizeof(T) * VPL == 16) {
-        *reinterpret_cast<uint4*>(kraw) = __ldg(reinterpret_cast<const uint4*>(krow));
-        *reinterpret_cast<uint4*>(vraw) = __ldg(reinterpret_cast<const uint4*>(krow + p.kv_stride));
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t pos = pos0 + u * PPL + sub;
+      valid[u] = pos < p_end;
+      if (!valid[u]) {
+        kraw[u] = make_uint4(0, 0, 0, 0);
+        vraw[u] = kraw[u];
+      } else if (pos == pos_new) {
+        kraw[u] = kn;
+        vraw[u] = vn;
       } else {
-#pragma unroll
-        for (int v = 0; v < VPL; ++v) { kraw[v] = krow[v]; vraw[v] = krow[p.kv_stride + v]; }
+        const T* krow = cache + base + (row0 + pos) * p.row_stride;
+        kraw[u] = __ldg(reinterpret_cast<const uint4*>(krow));
+        vraw[u] = __ldg(reinterpret_cast<const uint4*>(krow + p.kv_stride));
       }
-#pragma unroll
-      for (int v = 0; v < VPL; ++v) { kf[v] = Elem<T>::to_f(kraw[v]); vf[v] = Elem<T>::to_f(vraw[v]); }
     }
+    float kf[kUnroll][8];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) unpack16<T>(kraw[u], kf[u]);
 #pragma unroll
     for (int g = 0; g < kMaxGroup; ++g) {
       if (g < G) {
-        float dot = 0.f;
+        float dot[kUnroll];
 #pragma unroll
-        for (int v = 0; v < VPL; ++v) dot = fmaf(qv[g][v], kf[v], dot);
+        for (int u = 0; u < kUnroll; ++u) {
+          dot[u] = 0.f;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
-        const float m_new = fmaxf(m[g], dot);
+          for (int v = 0; v < 8; ++v) dot[u] = fmaf(qv[g][v], kf[u][v], dot[u]);
+        }
+#pragma unroll
+        for (int o = LPP / 2; o > 0; o >>= 1) {
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) dot[u] += __shfl_xor_sync(0xFFFFFFFFu, dot[u], o);
+        }
+        float m_new = m[g];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u)
+          if (valid[u]) m_new = fmaxf(m_new, dot[u]);
+        if (m_new == -INFINITY) continue;          // this lane group has seen no position yet
         const float corr = __expf(m[g] - m_new);
-        const float pr = __expf(dot - m_new);
-        l[g] = l[g] * corr + pr;
+        float lsum = l[g] * corr;
 #pragma unroll
-        for (int v = 0; v < VPL; ++v) acc[g][v] = fmaf(pr, vf[v], acc[g][v] * corr);
+        for (int v = 0; v < 8; ++v) acc[g][v] *= corr;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const float pr = valid[u] ? __expf(dot[u] - m_new) : 0.f;
+          lsum += pr;
+          float vf[8];
+          unpack16<T>(vraw[u], vf);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) acc[g][v] = fmaf(pr, vf[v], acc[g][v]);
+        }
+        l[g] = lsum;
         m[g] = m_new;
       }
     }
   }
-  // merge the warps of the CTA
+  // merge the lane groups of the warp (same dims, different positions) ...
+#pragma unroll
+  for (int o = LPP; o < 32; o <<= 1) {
+#pragma unroll
+    for (int g = 0; g < kMaxGroup; ++g) {
+      if (g < G) {
+        const float m_o = __shfl_xor_sync(0xFFFFFFFFu, m[g], o);
+        const float l_o = __shfl_xor_sync(0xFFFFFFFFu, l[g], o);
+        const float mm = fmaxf(m[g], m_o);
+        const float c_me = m[g] == -INFINITY ? 0.f : __expf(m[g] - mm);
+        const float c_o = m_o == -INFINITY ? 0.f : __expf(m_o - mm);
+        l[g] = l[g] * c_me + l_o * c_o;
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const float a_o = __shfl_xor_sync(0xFFFFFFFFu, acc[g][v], o);
+          acc[g][v] = acc[g][v] * c_me + a_o * c_o;
+        }
+        m[g] = mm;
+      }
+    }
+  }
+  // ... and the warps of the CTA
 #pragma unroll
   for (int g = 0; g < kMaxGroup; ++g) {
-    if (g < G) {
+    if (g < G && sub == 0) {
 #pragma unroll
-      for (int v = 0; v < VPL; ++v) sm_acc[warp][g][lane * VPL + v] = acc[g][v];
-      if (lane == 0) {
+      for (int v = 0; v < 8; ++v) sm_acc[warp][g][sl * 8 + v] = acc[g][v];
+      if (sl == 0) {
         sm_m[warp][g] = m[g];
         sm_l[warp][g] = l[g];
       }
@@ -196,8 +240,9 @@ __global__ void decode_attention_merge_kernel(const float* __restrict__ part, T*
 }
 
 int pick_splits(int64_t B, int Hkv, int64_t max_kvlen) {
-  // enough CTAs to cover the SMs about three times, slices of at least 64 positions
-  const int64_t want = ceil_div(3 * (int64_t)sm_count(), B * Hkv);
+  // enough CTAs for twelve 4-warp CTAs per SM (the kernel hides latency with warps, not
+  // with bytes in flight per warp), slices of at least 64 positions
+  const int64_t want = ceil_div(12 * (int64_t)sm_count(), B * Hkv);
   int64_t cap = ceil_div(max_kvlen, 64);
   int64_t s = want < cap ? want : cap;
   if (s < 1) s = 1;
@@ -222,15 +267,15 @@ int launch_decode_attention(const void* q, const void* k_cur, const void* v_cur,
     return fail(PMX_ERR_INVALID_ARGUMENT, "decode_cache_attention: null pointer");
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || max_kvlen <= 0 || Hq % Hkv)
     return fail(PMX_ERR_INVALID_ARGUMENT, "decode_cache_attention: B, heads and max_kvlen must be positive and num_heads a multiple of num_kv_heads (B=%lld Hq=%d Hkv=%d)", (long long)B, Hq, Hkv);
-  if (Hq / Hkv > kMaxGroup)
-    return fail(PMX_ERR_UNSUPPORTED, "decode_cache_attention: at most %d query heads per key/value head", kMaxGroup);
+  if (Hq / Hkv > kGroupLimit)
+    return fail(PMX_ERR_UNSUPPORTED, "decode_cache_attention: at most %d query heads per key/value head", kGroupLimit);
   if (D != 64 && D != 128) return fail(PMX_ERR_UNSUPPORTED, "decode_cache_attention: head_dim %d (64 and 128 are covered)", D);
   if (dtype != PMX_DTYPE_F16 && dtype != PMX_DTYPE_BF16)
     return fail(PMX_ERR_UNSUPPORTED, "decode_cache_attention: float16 and bfloat16 caches are covered");
   if (B > 65535 * 32ll) return fail(PMX_ERR_UNSUPPORTED, "decode_cache_attention: too many sequences");
-  const int vpl = D / 32;
-  if (row_stride % vpl || kv_stride % vpl || head_stride % vpl || layer_off % vpl || !aligned16(cache) || !aligned16(q))
-    return fail(PMX_ERR_ALIGNMENT, "decode_cache_attention: cache strides must keep head rows %d-byte aligned", vpl * 2);
+  if (row_stride % 8 || kv_stride % 8 || head_stride % 8 || layer_off % 8 || !aligned16(cache) || !aligned16(q) ||
+      !aligned16(k_cur) || !aligned16(v_cur))
+    return fail(PMX_ERR_ALIGNMENT, "decode_cache_attention: tensors and cache strides must keep head rows 16-byte aligned");
   const size_t need = decode_attention_workspace_bytes(B, Hq, Hkv, D, max_kvlen);
   if (!ws || ws_bytes < need) return fail(PMX_ERR_WORKSPACE, "decode_cache_attention: workspace of %zu bytes needed, %zu given", need, ws_bytes);
   AttnParams p{};
@@ -243,14 +288,18 @@ int launch_decode_attention(const void* q, const void* k_cur, const void* v_cur,
   p.chunk = (int)ceil_div(max_kvlen, p.splits);
   p.scale = 1.0f / sqrtf((float)D);
   const dim3 grid((unsigned)B, (unsigned)Hkv, (unsigned)p.splits);
-  int st;
   const bool bf = dtype == PMX_DTYPE_BF16;
-  if (D == 128)
-    st = bf ? launch_pdl_k(decode_attention_kernel<__nv_bfloat16, 4>, grid, dim3(kAttnWarps * 32), 0, s, p)
-            : launch_pdl_k(decode_attention_kernel<__half, 4>, grid, dim3(kAttnWarps * 32), 0, s, p);
-  else
-    st = bf ? launch_pdl_k(decode_attention_kernel<__nv_bfloat16, 2>, grid, dim3(kAttnWarps * 32), 0, s, p)
-            : launch_pdl_k(decode_attention_kernel<__half, 2>, grid, dim3(kAttnWarps * 32), 0, s, p);
+  const int G = Hq / Hkv;
+  const void* kern = nullptr;
+#define PMX_ATTN_PICK(GM)                                                                                         \
+  kern = D == 128 ? (bf ? (const void*)decode_attention_kernel<__nv_bfloat16, 128, GM>                            \
+                        : (const void*)decode_attention_kernel<__half, 128, GM>)                                   \
+                  : (bf ? (const void*)decode_attention_kernel<__nv_bfloat16, 64, GM>                             \
+                        : (const void*)decode_attention_kernel<__half, 64, GM>)
+  if (G == 1) { PMX_ATTN_PICK(1); } else if (G == 2) { PMX_ATTN_PICK(2); } else if (G <= 4) { PMX_ATTN_PICK(4); } else { PMX_ATTN_PICK(8); }
+#undef PMX_ATTN_PICK
+  void* args[] = {(void*)&p};
+  int st = launch_pdl(kern, grid, dim3(kAttnWarps * 32), 0, s, args);
   if (st != PMX_OK || p.splits == 1) return st;
   const dim3 mgrid((unsigned)B, (unsigned)Hq);
   if (bf)
