@@ -244,6 +244,69 @@ skip_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ skip, const 
   }
 }
 
+// Many rows (prefill): a WARP per row, the whole row (up to 16 sixteen-byte chunks per lane, kept
+// as the rounded T values) in registers, no block-wide barrier: all of a row's loads are in
+// flight at once and the reduction is five shuffles.
+template <typename T>
+__global__ void __launch_bounds__(256)
+skip_rms_norm_warp_kernel(const T* __restrict__ x, const T* __restrict__ skip, const T* __restrict__ weight,
+                          T* __restrict__ y, T* __restrict__ skip_out, int64_t M, int64_t H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int V = kVec<T>;
+  constexpr int R = 16;                       // chunks per lane
+  const int lane = threadIdx.x & 31;
+  const int chunks = (int)(H / V);
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < M; row += warps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+    const uint4* sr = skip ? reinterpret_cast<const uint4*>(skip + row * H) : nullptr;
+    uint4 a[R], b[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int c = lane + 32 * r;
+      if (c < chunks) {
+        a[r] = __ldg(xr + c);
+        if (sr) b[r] = __ldg(sr + c);
+      }
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int c = lane + 32 * r;
+      if (c < chunks) {
+        float f[V];
+        unpack16<T>(a[r], f);
+        if (sr) {
+          float g[V];
+          unpack16<T>(b[r], g);
+#pragma unroll
+          for (int v = 0; v < V; ++v) f[v] = Elem<T>::to_f(Elem<T>::from_f(f[v] + g[v]));
+          a[r] = pack16<T>(f);
+          reinterpret_cast<uint4*>(skip_out + row * H)[c] = a[r];
+        }
+#pragma unroll
+        for (int v = 0; v < V; ++v) acc = fmaf(f[v], f[v], acc);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+    const float scale = rsqrtf(acc / (float)H + eps);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int c = lane + 32 * r;
+      if (c < chunks) {
+        float f[V], wv[V];
+        unpack16<T>(a[r], f);
+        unpack16<T>(__ldg(reinterpret_cast<const uint4*>(weight) + c), wv);
+#pragma unroll
+        for (int v = 0; v < V; ++v) f[v] = Elem<T>::to_f(Elem<T>::from_f(f[v] * scale)) * wv[v];
+        reinterpret_cast<uint4*>(y + row * H)[c] = pack16<T>(f);
+      }
+    }
+  }
+}
+
 // rows outside [off[0], off[E]) <- 0   (the zero-initialised output of
 // MoeColumnParallelLinear.py:59 / MoeRowParallelLinear.py:45)
 template <typename T>
@@ -383,7 +446,10 @@ int launch_skip_rms_norm(const void* x, const void* skip, const void* weight, vo
     const bool vec = H % kVec<T> == 0 && aligned16(x) && aligned16(y) && aligned16(weight) &&
                      (!skip || (aligned16(skip) && aligned16(skip_out)));
     T* so = skip ? (T*)skip_out : (T*)y;   // unused without skip
-    if (vec && H / kVec<T> <= 4 * 256)
+    if (vec && H / kVec<T> <= 32 * 16 && M >= 2048) {
+      const int64_t wblocks = ceil_div(M, 8) < (int64_t)sm_count() * 8 ? ceil_div(M, 8) : (int64_t)sm_count() * 8;
+      PMX_PDL_LAUNCH((skip_rms_norm_warp_kernel<T>), (int)wblocks, 256, 0, s, (const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
+    } else if (vec && H / kVec<T> <= 4 * 256)
       PMX_PDL_LAUNCH((skip_rms_norm_kernel<T, true, true>), (int)blocks, 256, 0, s, (const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);
     else if (vec)
       PMX_PDL_LAUNCH((skip_rms_norm_kernel<T, true, false>), (int)blocks, 256, 0, s, (const T*)x, (const T*)skip, (const T*)weight, (T*)y, so, M, H, eps);

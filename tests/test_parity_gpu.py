@@ -667,7 +667,9 @@ def test_rms_norm_golden(F, dtype):
     np.testing.assert_allclose(host(F.skip_rms_norm(x, w, sk)[0]), oy, rtol=ulp, atol=1e-6)
 
 
-@pytest.mark.parametrize("M,H,dtype", [(1, 4096, "f16"), (64, 4096, "f16"), (300, 1000, "bf16"), (7, 50, "f32"), (2000, 2048, "bf16")])
+@pytest.mark.parametrize("M,H,dtype", [(1, 4096, "f16"), (64, 4096, "f16"), (300, 1000, "bf16"), (7, 50, "f32"), (2000, 2048, "bf16"),
+                                       # many rows: the warp-per-row kernel (rows of up to 512 sixteen-byte chunks)
+                                       (3000, 4096, "f16"), (2500, 1000, "bf16"), (2100, 2048, "f32"), (2049, 8, "f16")])
 def test_rms_norm_shapes(F, M, H, dtype):
     rng = np.random.default_rng(M + H)
     x = orc.round_to_dtype(rng.standard_normal((M, H)).astype(np.float32) * 3, dtype)
@@ -678,6 +680,8 @@ def test_rms_norm_shapes(F, M, H, dtype):
     oy, os_ = orc.skip_rms_norm(x, w, sk, 1e-5, dtype)
     assert np.array_equal(host(s), os_)
     np.testing.assert_allclose(host(y), oy, rtol=ulp, atol=1e-6)
+    oy2, _ = orc.skip_rms_norm(x, w, None, 1e-5, dtype)
+    np.testing.assert_allclose(host(F.rms_norm(dev(x, dtype), dev(w, dtype), -1, 1e-5)), oy2, rtol=ulp, atol=1e-6)
     with pytest.raises(ValueError):
         F.rms_norm(dev(x, dtype), dev(w, dtype), 0)
     with pytest.raises(RuntimeError):
