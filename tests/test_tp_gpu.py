@@ -81,6 +81,78 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+def _op_level(rank, world, port, q):
+    """The operator-level collectives on real GPUs: moe_column_parallel_linear with
+    gather_output=True (all-gather + rank-major concatenation, MoeColumnParallelLinear.py:71-78),
+    moe_row_parallel_linear (all-reduce of the expanded rows, MoeRowParallelLinear.py:57-58), and
+    the dense column / row parallel linears (ColumnParallelLinear.py:44-52, RowParallelLinear.py:41-45)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        group = dist.new_group(list(range(world)))
+        import ppl.pmx_b200.torch_function as F
+        from oracle import moe_oracle as orc
+        g = torch.Generator().manual_seed(7)
+        E, k, T, H, N = 4, 2, 96, 128, 256
+        x = torch.randn(T, H, generator=g).half()
+        sc = torch.randn(T, E, generator=g).half()
+        w_col = (torch.randn(E, N, H, generator=g) / H ** 0.5).half()          # full [E, N, H]
+        b_col = torch.randn(E, N, generator=g).half()
+        w_row = (torch.randn(E, H, N, generator=g) / N ** 0.5).half()          # full [E, H, N]
+        f = lambda t: t.float().numpy()
+        xe, ew, inv, off = F.moe_select(x.to(dev), sc.to(dev), E, k)
+        Nl = N // world
+        shard = slice(rank * Nl, (rank + 1) * Nl)
+        y = F.moe_column_parallel_linear(xe, off, w_col[:, shard].contiguous().to(dev), b_col[:, shard].contiguous().to(dev),
+                                         group, E, H, N, True)
+        oxe, _, _, ooff = orc.moe_select(f(x), f(sc), E, k, "f16")
+        want = orc.moe_grouped_linear(oxe, ooff, f(w_col), f(b_col))
+        assert y.shape == (T, k, N)
+        np.testing.assert_allclose(y.float().cpu().numpy().reshape(T * k, N), want, atol=2e-2, rtol=1e-2)
+        z = F.moe_row_parallel_linear(y[..., shard].contiguous(), off, w_row[:, :, shard].contiguous().to(dev), None,
+                                      group, E, N, H, True)
+        want_z = orc.moe_grouped_linear(orc.round_to_dtype(want, "f16"), ooff, f(w_row), None)
+        np.testing.assert_allclose(z.float().cpu().numpy().reshape(T * k, H), want_z, atol=3e-2, rtol=2e-2)
+        # dense linears
+        wd = (torch.randn(N, H, generator=g) / H ** 0.5).half()
+        bd = torch.randn(N, generator=g).half()
+        yc = F.column_parallel_linear(x.to(dev), wd[shard].contiguous().to(dev), bd[shard].contiguous().to(dev), group, H, N, True)
+        np.testing.assert_allclose(yc.float().cpu().numpy(), orc.linear(f(x), f(wd), f(bd)), atol=2e-2, rtol=1e-2)
+        wr = (torch.randn(H, N, generator=g) / N ** 0.5).half()
+        br = torch.randn(H, generator=g).half()
+        yr = F.row_parallel_linear(yc[:, shard].contiguous(), wr[:, shard].contiguous().to(dev), br.to(dev), group, N, H, True)
+        np.testing.assert_allclose(yr.float().cpu().numpy(), orc.linear(orc.round_to_dtype(orc.linear(f(x), f(wd), f(bd)), "f16"),
+                                                                        f(wr), f(br)), atol=3e-2, rtol=2e-2)
+        q.put((rank, "ok"))
+    except Exception:                            # noqa: BLE001
+        import traceback
+        q.put((rank, traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _spawn(target, world=2):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=target, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, msg in results:
+        assert msg == "ok", f"rank {rank}: {msg}"
+
+
+def test_operator_level_collectives_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _spawn(_op_level)
+
+
 def _alternating(rank, world, port, q):
     """One set of exchange buffers, token counts that change from call to call (64, 8, 64,
     8, ...) and one rank held back on the host between calls: a fast rank starts the next
