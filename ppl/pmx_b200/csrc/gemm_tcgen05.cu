@@ -87,6 +87,30 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     tmem_alloc(&sh->tmem_base, kTmemCols);
     tmem_relinquish();
   }
+  // Weights never depend on the kernel in front.  Guess that every expert owns rows that fit one
+  // token tile (decode: true unless an expert is empty); the CTA's first item is then known from
+  // the shapes alone, and the producer fills the ring with its weight tiles (no token tiles yet)
+  // BEFORE the dependency wait.  A wrong guess costs nothing but those loads: the stages are
+  // handed back unused.
+  int pre_n = 0, pre_e = -1, pre_f0 = 0;
+  const uint32_t smem_base = smem_u32(smem);
+  if (MODE == 1 && !DENSE && p.prefetch && threadIdx.x == 0) {
+    sh->discard = 0;
+    WorkIter guess;
+    guess.init(p, p.E);
+    if (guess.next_item < guess.panel_end && guess.u_end - guess.u >= 16) {
+      pre_e = guess.next_item;
+      pre_f0 = (int)guess.u * 8;
+      pre_n = p.stages < p.kblocks ? p.stages : p.kblocks;
+      const int wrow = pre_e * p.w_pitch + pre_f0;
+      for (int st = 0; st < pre_n; ++st) {
+        const uint32_t dst = smem_base + st * stage_bytes + tok_bytes;
+        mbar_expect_tx_only(&sh->full[st], w_bytes);
+        tma_load_2d(dst, &map_w, &sh->full[st], st * kBlockK, wrow);
+        if (SWIGLU) tma_load_2d(dst + ft * 128, &map_w, &sh->full[st], st * kBlockK, wrow + p.N / 2);
+      }
+    }
+  }
   if (DENSE) {
     // Every expert is applied to all p.M tokens (operand x itself, not the gathered rows), so
     // the work list does not depend on the routing and the loads and MMAs start while the
@@ -113,19 +137,38 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       acc += ((rows + tt - 1) / tt) * p.feat_tiles * p.split_k;
     }
     s_prefix[p.E] = acc;
+    if (MODE == 1 && !DENSE && p.prefetch && pre_n > 0) {
+      // was the guess right?  compare it with the real first item of this CTA
+      WorkIter real;
+      Item first;
+      int idx = 0;
+      real.init(p, acc);
+      const bool have = real.next(p, acc, s_off, s_prefix, first, idx);
+      const bool hit = have && first.e == pre_e && first.f0 == pre_f0 && first.fn == ft && first.kb0 == 0 &&
+                       first.kb1 >= pre_n;
+      if (!hit) {
+        sh->discard = pre_n;
+        for (int st = 0; st < pre_n; ++st) mbar_arrive(&sh->full[st]);   // completes once the weights have landed
+        pre_n = -pre_n;                                                  // negative: discarded
+      }
+    }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
   const int total_items = s_prefix[p.E];
-  const uint32_t smem_base = smem_u32(smem);
 
   if (warp == 0) {
     // ========================= TMA producer =================================
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      int pre_left = pre_n > 0 ? pre_n : 0;     // stages that already hold the first item's weight tiles
+      if (pre_n < 0) {                          // discarded stages: the ring starts behind them
+        stage = -pre_n;
+        if (stage == p.stages) { stage = 0; phase ^= 1u; }
+      }
       Item it;
       int item = 0;
       WorkIter work;
@@ -135,6 +178,14 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         if (DENSE) it.row0 = 0;
         const int wrow = it.e * p.w_pitch + it.f0;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
+          if (pre_left > 0) {
+            // the weights of this k-block are in flight (or there) already: add the token tile
+            --pre_left;
+            mbar_expect_tx(&sh->full[stage], tok_bytes);
+            tma_load_2d(smem_base + stage * stage_bytes, &map_x, &sh->full[stage], kb * kBlockK, it.row0);
+            if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+            continue;
+          }
           ok = wait_barrier(&sh->empty[stage], phase ^ 1u, sh, p.status, 0, item);
           if (!ok) break;
           const uint32_t dst = smem_base + stage * stage_bytes;
@@ -184,6 +235,15 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       WorkIter work;
       work.init(p, total_items);
       bool ok = true;
+      if (MODE == 1 && !DENSE && p.prefetch) {
+        // stages the producer filled for an item this CTA does not have: wait for the copies, hand them back
+        for (int d = sh->discard; d > 0 && ok; --d) {
+          ok = wait_barrier(&sh->full[stage], phase, sh, p.status, 2, -1);
+          if (!ok) break;
+          mbar_arrive(&sh->empty[stage]);
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+      }
       while (ok && work.next(p, total_items, s_off, s_prefix, it, item)) {
         ok = wait_barrier(&sh->acc_empty[acc], acc_phase ^ 1u, sh, p.status, 1, item);
         if (!ok) break;
@@ -595,6 +655,8 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   p.tile_feat = plan.tile_feat;
   p.feat_tiles = plan.balanced ? 1 : (int)ceil_div(n_out, plan.tile_feat);
   p.balanced = plan.balanced;
+  p.prefetch = plan.kernel == PMX_GEMM_TC_WEIGHTS_M && plan.balanced && plan.split_k == 1 && !plan.stream_k &&
+               n_out >= 128;
   p.units_per_panel = (int)(n_out / 8);
   p.kblocks = (int)ceil_div(K, kBlockK);
   p.split_k = plan.split_k;

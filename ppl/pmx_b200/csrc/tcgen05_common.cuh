@@ -32,6 +32,8 @@ struct Params {
   int stream_k;         // 1: the k-blocks of all work items are dealt out evenly over the CTAs
   int* sk_flags;        // [grid] number of epilogue warps that have stored CTA c's partial tile
   float* sk_slots;      // [grid][256 columns][128 lanes] fp32 partial accumulators
+  int prefetch;         // weight rows on MMA-M: fetch the weight tiles of the CTA's (guessed) first item
+                        // before waiting for the kernel in front
   const int64_t* inv;   // DENSE: invert_permutation [M tokens, k]
   int k;                // DENSE: experts per token
   int balanced;         // weight rows on MMA-M only: every CTA works on a contiguous range of the
@@ -57,6 +59,11 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
+}
+// adds to the barrier's pending byte count WITHOUT arriving (the phase cannot complete before
+// the matching arrive)
+__device__ __forceinline__ void mbar_expect_tx_only(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -191,6 +198,8 @@ struct Shared {          // control block placed after the ring stages
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile int abort;
+  int discard;           // ring stages filled ahead of the dependency wait that turned out not to be
+                         // the first item's: the MMA thread hands them back unused
 };
 
 // Bounded wait.  Returns false when the CTA is aborting.
