@@ -895,7 +895,7 @@ def main():
     ap.add_argument("--no-dense-decode", action="store_true",
                     help="decode-size batches: gather the routed rows first instead of the gate/up projection that "
                          "reads the un-permuted tokens and overlaps the router")
-    ap.add_argument("--overlap-chunks", type=int, default=4,
+    ap.add_argument("--overlap-chunks", type=int, default=1,
                     help="N > 1, results too large for the peer kernel: hidden-column slices of the down projection "
                          "whose all-reduces overlap the next slice's GEMM (1: one GEMM, one all-reduce)")
     ap.add_argument("--gemm-plan", default="", help="pmx_gemm_plan fields for the gate_up / down STAGE timings, "

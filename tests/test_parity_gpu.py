@@ -474,6 +474,9 @@ def test_grouped_linear_auto_plan_and_fp32(F):
 
 
 @pytest.mark.parametrize("M,N,K,dtype", [(64, 4096, 4096, "f16"), (1, 6144, 4096, "f16"), (300, 520, 192, "bf16"),
+                                         # the router gate of a decode batch through `linear`: few output
+                                         # features, long K (K is sliced)
+                                         (64, 8, 4096, "f16"), (16, 64, 2048, "bf16"), (128, 8, 14336, "f16"),
                                          (4096, 8, 4096, "bf16"), (2500, 64, 2048, "f16"), (3000, 1024, 512, "bf16"),
                                          (70, 100, 36, "f16"), (33, 96, 200, "f32")])
 def test_dense_linears(F, M, N, K, dtype):
@@ -752,8 +755,9 @@ def test_block_scaled_workloads(F, wl, scale):
     assert_close(out, r["out"], sh.dtype)
 
 
+@pytest.mark.parametrize("H,I,T", [(512, 1024, 48), (4096, 1792, 64)])      # toy width; a rank's shard of Mixtral at tp 8
 @pytest.mark.parametrize("fused_ffn_glu", [True, False])
-def test_reference_moe_block_runs_on_the_patched_operators(F, fused_ffn_glu):
+def test_reference_moe_block_runs_on_the_patched_operators(F, fused_ffn_glu, H, I, T):
     """The drop-in claim itself: the reference's own MoeFeedForward module
     (model_zoo/mixtral/modeling/dynamic_batching/Model.py:155-214, unmodified, staged under
     oracle/_ref) is built, the operators are swapped in with patch_reference(), and its
@@ -764,7 +768,7 @@ def test_reference_moe_block_runs_on_the_patched_operators(F, fused_ffn_glu):
     from ppl.pmx_b200 import workloads as W
     from ppl.pmx_b200.moe_layers import patch_reference, unpatch_reference
     opmx, model, ModelParams = oracle.import_reference_mixtral()
-    sh = W.scaled(W.WORKLOADS["decode_t64"], H=512, I=1024, T=48)
+    sh = W.scaled(W.WORKLOADS["decode_t64"], H=H, I=I, T=T)
     x, wr, _, _ = W.make_activations(sh)
     wu, w2 = W.make_expert_weights(sh, "cuda")
     params = ModelParams(hidden_dim=sh.H, intermediate_dim=sh.I, num_experts=sh.E, num_experts_per_token=sh.k)
@@ -784,6 +788,22 @@ def test_reference_moe_block_runs_on_the_patched_operators(F, fused_ffn_glu):
             sc = F.linear(x.cuda(), blk.gate.weight, None, sh.H, sh.E)
     finally:
         unpatch_reference(opmx, saved)
+    assert_close(sc, orc.linear(host(x), host(wr)), sh.dtype, "router logits")
     r = orc.moe_block(host(x), host(wr), host(wu), host(w2), sh.E, sh.k, sh.dtype, scores=host(sc),
                       round_intermediates=False)
     assert_close(out, r["out"], sh.dtype)
+    # and against the unmodified reference operators on the same GPU (its linears allocate with the
+    # global default dtype and device, so it runs under the regime its loader sets)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.float16)
+    torch.set_default_device("cuda")
+    try:
+        with torch.no_grad():
+            ref_out = blk(x.cuda())
+    finally:
+        torch.set_default_device("cpu")
+        torch.set_default_dtype(old)
+    # the reference routes on cuBLAS logits: tokens whose two best logits are within rounding of
+    # each other may pick another expert there, so compare the bulk of the tokens
+    close = ((out.float() - ref_out.float()).abs() <= 2e-2 + 1e-2 * ref_out.float().abs()).all(dim=-1)
+    assert close.float().mean() >= 0.9, f"only {int(close.sum())} of {T} tokens agree with the reference operators"
