@@ -52,7 +52,7 @@ HEADLINE = "decode_t64"
 EXTRA_WORKLOADS = ["decode_t1", "decode_t8", "decode_t32", "decode_t128", "decode_t256", "prefill", "finegrained",
                    "finegrained_empty"]
 ATOL, RTOL = 2e-2, 1e-2          # parity tolerance of fp16 / bf16 results against fp32 math
-STAGES = ["gate", "select", "route_select", "gate_up", "down", "reduce", "allreduce", "reduce_allreduce"]
+STAGES = ["gate", "select", "route_select", "experts", "gate_up", "down", "reduce", "allreduce", "reduce_allreduce"]
 
 
 def load_peaks():
@@ -277,7 +277,8 @@ def get_block(ctx, shape, full: bool, w_router=None):
     blk = MoeFeedForward(shape.H, shape.I, shape.E, shape.k, None if full else ctx.group, False,
                          peer_reduce_tokens=peer_tokens, peer_algorithm=ctx.args.peer_algo,
                          overlap_chunks=ctx.args.overlap_chunks,
-                         dense_decode=not ctx.args.no_dense_decode).to(ctx.device, dt)
+                         dense_decode=not ctx.args.no_dense_decode,
+                         one_launch_experts=not ctx.args.no_one_launch).to(ctx.device, dt)
     wu, w2 = W.make_expert_weights(shape, ctx.device, tp_rank=0 if full else ctx.rank, tp_size=tp)
     if w_router is None:
         _, w_router, _, _ = W.make_activations(shape, detie=False)
@@ -458,13 +459,18 @@ def measure(ctx, shape, steps, warmup, regions, headline):
 
         sync_all(ctx)
         plan = ctx.gemm_plan
-        from ppl.pmx_b200.torch_function.moe import dense_gate_up_covers
+        from ppl.pmx_b200.torch_function.moe import dense_gate_up_covers, dense_mlp_covers
+        one_launch = False
         dense = (blk.dense_decode and dense_gate_up_covers(shape.T, blk.wu.weight, k)
                  and OPMX.moe_route_select(x_dev, blk.gate.weight, E, k, gather=False) is not None)
         if dense:
             # the step's own kernels: router without the gather, gate/up from the un-permuted tokens
             _, _, ew, inv, off = stage("route_select", lambda: OPMX.moe_route_select(x_dev, blk.gate.weight, E, k,
                                                                                      gather=False))
+            one_launch = blk.one_launch_experts and dense_mlp_covers(shape.T, blk.wu.weight, blk.w2.weight, k)
+            if one_launch:
+                # the step's kernel for both projections; the two launches below are timed for comparison
+                stage("experts", lambda: OPMX.moe_dense_mlp(x_dev, inv, off, blk.wu.weight, blk.w2.weight))
             h = stage("gate_up", lambda: OPMX.moe_dense_gate_up(x_dev, inv, off, blk.wu.weight, None))
         else:
             if OPMX.moe_route_select(x_dev, blk.gate.weight, E, k) is not None:
@@ -541,6 +547,16 @@ def measure(ctx, shape, steps, warmup, regions, headline):
                 "peak_kind": "burst" if burst else "sustained"}
 
     roof = roofline_of("gate_up", "bytes_gate_up", "flops_gate_up")
+    if one_launch:
+        # the step runs both projections as one launch: that launch is the dominant kernel
+        t_exp = kernel_ms["experts"] * 1e-3
+        b_exp = work["bytes_gate_up"] + work["bytes_down"]
+        roof_experts = {"bound": "hbm", "achieved": b_exp / t_exp / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": b_exp / t_exp / 1e9 / peaks["hbm_gbs"], "kernel_ms": kernel_ms["experts"],
+                        "algorithmic_bytes": b_exp,
+                        "kernel": "both expert projections in one launch (expert_mlp_decode_kernel)"}
+    else:
+        roof_experts = None
     ratio = TRAFFIC_RATIO.get(roof["bound"])
     # DRAM traffic of the launch = algorithmic bytes x the ratio ncu measured on a
     # reduced-ffn case of the same kernel (profiles/grouped_gemm_tc_*.md); traffic is
@@ -561,12 +577,14 @@ def measure(ctx, shape, steps, warmup, regions, headline):
         "gpu_launches_per_step": int(launches_per_step),
         "clocks": clocks, "roofline": roof,
         "roofline_down": {k2: down[k2] for k2 in ("bound", "achieved", "unit", "frac")} if down else None,
+        "roofline_experts_one_launch": roof_experts,
         "layer": {"ms_floor": layer_floor_s * 1e3, "frac_of_roofline": layer_floor_s * 1e3 / ms_step,
                   "active_experts": active, "graph": not args.no_graph,
                   "allreduce": ((f"peer-memory kernel fused with the combine ({args.peer_algo})" if use_peer else "nccl")
                                 if ctx.world > 1 else None),
                   "allreduce_phases_ns": ar_phases,
                   "gate_up_from_unpermuted_tokens": bool(dense),
+                  "experts_in_one_launch": bool(one_launch),
                   "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items() if n in STAGES and v > 0}},
         "parity": parity,
     }
@@ -895,6 +913,11 @@ def main():
     ap.add_argument("--no-dense-decode", action="store_true",
                     help="decode-size batches: gather the routed rows first instead of the gate/up projection that "
                          "reads the un-permuted tokens and overlaps the router")
+    ap.add_argument("--l2-prefetch", type=int, default=None,
+                    help="k-blocks of weight tiles the weight-streaming GEMMs request into L2 in front of their "
+                         "shared-memory ring (library default 8; 0 = none)")
+    ap.add_argument("--no-one-launch", action="store_true",
+                    help="decode-size batches on thin shards: gate/up and down projection as two launches")
     ap.add_argument("--overlap-chunks", type=int, default=1,
                     help="N > 1, results too large for the peer kernel: hidden-column slices of the down projection "
                          "whose all-reduces overlap the next slice's GEMM (1: one GEMM, one all-reduce)")
@@ -947,6 +970,8 @@ def main():
     from ppl.pmx_b200 import _cabi
     if args.no_pdl:
         _cabi.lib.pmx_moe_set_programmatic_launch(0)
+    if args.l2_prefetch is not None:
+        _cabi.lib.pmx_moe_set_l2_prefetch(args.l2_prefetch)
     ctx.gemm_plan = parse_plan(args.gemm_plan)
 
     if args.attention_only:
@@ -1001,6 +1026,7 @@ def main():
                     "h2d_bytes_per_step": head["h2d"], "d2h_bytes_per_step": head["d2h"]},
             "gpu_launches": head["gpu_launches_per_step"] * args.steps,
             "programmatic_dependent_launch": not args.no_pdl,
+            "l2_prefetch_kblocks": args.l2_prefetch if args.l2_prefetch is not None else "library default",
             "clocks": head["clocks"],
             "roofline": head["roofline"],
             "roofline_down": head["roofline_down"],

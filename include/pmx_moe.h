@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define PMX_MOE_ABI_VERSION 2
+#define PMX_MOE_ABI_VERSION 3
 
 /* element type of activations and weights */
 typedef enum pmx_dtype {
@@ -84,6 +84,9 @@ typedef struct pmx_gemm_plan {
                            w points at a window of N feature rows inside a wider [E,pitch,K]
                            weight tensor, e.g. a slice of the hidden columns of the down
                            projection.  Not with SwiGLU, split-K or stream-K. */
+  int32_t l2_prefetch;  /* PMX_GEMM_TC_WEIGHTS_M only: the weight tiles of the k-block this many rounds in
+                           front of the shared-memory ring are requested into L2 (0 = the process-wide
+                           default, see pmx_moe_set_l2_prefetch; negative = none) */
 } pmx_gemm_plan;
 
 int pmx_moe_abi_version(void);
@@ -99,6 +102,12 @@ long long pmx_moe_kernel_launches(void);
  * their results or writes anything.  on = 0 switches to ordinary launches for the
  * whole process.  Returns the previous setting. */
 int pmx_moe_set_programmatic_launch(int on);
+/* L2 prefetch distance of the weight-streaming expert GEMMs (weight rows on MMA-M, the dense
+ * gate/up and the one-launch decode kernels), in k-blocks of 64 elements; 0 = no prefetch.
+ * A thin shard's weight stream is limited by the bytes the CTAs' shared-memory rings keep
+ * in flight (about 18 MB for 112 CTAs); requests into L2 cost no shared memory.  Process-wide;
+ * returns the previous value.  Default 8. */
+int pmx_moe_set_l2_prefetch(int32_t kblocks);
 
 /*
  * moe_select -- replaces MoeSelect.forward, torch_function/MoeSelect.py:36-64.
@@ -258,6 +267,28 @@ int pmx_moe_dense_gate_up(const void* x, const int64_t* invert_permutation,
                           const int64_t* expert_offset, const void* w, const void* bias, void* h,
                           int64_t T, int64_t N, int64_t K, int32_t E, int32_t k, int32_t dtype,
                           float beta, void* workspace, size_t workspace_bytes, void* stream);
+
+/* The two expert projections of a decode-size batch in ONE launch:
+ *   h[r,:] = SwiGLU(x[t,:] . wu[e]^T),   y[r,:] = h[r,:] . w2[e]^T
+ * for every token t and every expert e it was routed to (r as for pmx_moe_dense_gate_up):
+ * MoeColumnParallelLinear.py:58-69 + SwiGLU.py:15-16 + MoeRowParallelLinear.py:44-55 as
+ * called at Model.py:198-205, without the launch boundary between the projections (the w2
+ * stream is in flight while the last gate/up tiles finish).  x [T,H], wu [E,N,H] =
+ * [gate rows ; up rows], w2 [E,H,N/2], h [T*k,N/2] (an output too), y [T*k,H]; no bias.
+ * Same contract towards the routing kernel in front as pmx_moe_dense_gate_up.  Covers
+ * T <= 64, float16 / bfloat16, N % 16 == 0, H % 8 == 0.  Workspace
+ * (pmx_moe_dense_mlp_workspace_bytes, 16-byte aligned): status words + per-expert
+ * counters; it must be zero before the first launch that uses it, every completed launch
+ * leaves it zero, and launches that share it must not overlap on the GPU.
+ * pmx_moe_dense_mlp_check reads the status back (synchronising) like
+ * pmx_moe_grouped_linear_check and, after a failure, clears the workspace. */
+int pmx_moe_dense_mlp_covers(int64_t T, int64_t N, int64_t H, int32_t E, int32_t k, int32_t dtype);
+size_t pmx_moe_dense_mlp_workspace_bytes(int32_t E);
+int pmx_moe_dense_mlp(const void* x, const int64_t* invert_permutation,
+                      const int64_t* expert_offset, const void* wu, const void* w2, void* h, void* y,
+                      int64_t T, int64_t N, int64_t H, int32_t E, int32_t k, int32_t dtype, float beta,
+                      void* workspace, size_t workspace_bytes, void* stream);
+int pmx_moe_dense_mlp_check(void* workspace, int32_t E, int32_t out[4], void* stream);
 
 /* Reads back (synchronising `stream`) the self-check record a grouped-linear
  * launch left in its workspace: out[0] = 0 if clean, else a code; out[1..3] =

@@ -15,7 +15,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libpmx_moe_b200.so")
 
 DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
-ABI_VERSION = 2
+ABI_VERSION = 3
 EPILOGUE_NONE, EPILOGUE_SWIGLU = 0, 1
 GEMM_AUTO, GEMM_TC_TOKENS_M, GEMM_TC_WEIGHTS_M, GEMM_SIMT, GEMM_TC_TOKENS_M_PAIRED = 0, 1, 2, 3, 4
 
@@ -24,7 +24,8 @@ class GemmPlan(C.Structure):
     """Mirror of pmx_gemm_plan."""
     _fields_ = [("kernel", C.c_int32), ("tile_feat", C.c_int32), ("tile_tok", C.c_int32),
                 ("split_k", C.c_int32), ("stages", C.c_int32), ("max_ctas", C.c_int32), ("stream_k", C.c_int32),
-                ("cta_cap", C.c_int32), ("full_rounds", C.c_int32), ("balance", C.c_int32), ("w_expert_pitch", C.c_int32)]
+                ("cta_cap", C.c_int32), ("full_rounds", C.c_int32), ("balance", C.c_int32), ("w_expert_pitch", C.c_int32),
+                ("l2_prefetch", C.c_int32)]
 
 
 class PmxError(RuntimeError):
@@ -52,6 +53,7 @@ def _load() -> C.CDLL:
         "pmx_moe_route_select": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32, vp, sz, vp]),
         "pmx_moe_route_select_check": (C.c_int, [vp, vp]),
         "pmx_moe_set_programmatic_launch": (C.c_int, [C.c_int]),
+        "pmx_moe_set_l2_prefetch": (C.c_int, [i32]),
         "pmx_moe_norm_route_select_workspace_bytes": (sz, [i64, i64, i32, i32, i32]),
         "pmx_moe_norm_route_select": (C.c_int, [vp, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32,
                                                 vp, sz, vp]),
@@ -62,6 +64,10 @@ def _load() -> C.CDLL:
         "pmx_moe_grouped_linear_check": (C.c_int, [vp, C.POINTER(i32 * 4), vp]),
         "pmx_moe_dense_gate_up_covers": (C.c_int, [i64, i64, i64, i32, i32, i32]),
         "pmx_moe_dense_gate_up": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, f32, vp, sz, vp]),
+        "pmx_moe_dense_mlp_covers": (C.c_int, [i64, i64, i64, i32, i32, i32]),
+        "pmx_moe_dense_mlp_workspace_bytes": (sz, [i32]),
+        "pmx_moe_dense_mlp": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, f32, vp, sz, vp]),
+        "pmx_moe_dense_mlp_check": (C.c_int, [vp, i32, vp, vp]),
         "pmx_swiglu": (C.c_int, [vp, vp, i64, i64, f32, i32, vp]),
         "pmx_silu": (C.c_int, [vp, vp, vp, i64, i32, vp]),
         "pmx_skip_rms_norm": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, f32, i32, vp]),
@@ -107,17 +113,19 @@ ALLREDUCE_FLAG_STAMPS = 1
 _barrier_ws: dict = {}
 
 
-def barrier_workspace(nbytes: int, device) -> torch.Tensor:
-    """The workspace of the one-launch router + select kernels: its grid barrier words
-    must be zero before the first call and every completed call leaves them zero, so
-    ONE buffer per device is allocated (zeroed) on first use and kept.  Calls that
-    share it must not overlap on the GPU: callers that drive several streams of one
-    device concurrently pass a workspace of their own to the operators instead."""
+def barrier_workspace(nbytes: int, device, kind: str = "route") -> torch.Tensor:
+    """The workspace of the one-launch router + select kernels (kind "route") or of the
+    one-launch expert projections (kind "mlp"): its barrier words / counters must be zero
+    before the first call and every completed call leaves them zero, so ONE buffer per
+    device and kind is allocated (zeroed) on first use and kept.  Calls that share it must
+    not overlap on the GPU: callers that drive several streams of one device concurrently
+    pass a workspace of their own to the operators instead."""
     dev = torch.device(device)
-    t = _barrier_ws.get(dev.index)
+    key = (dev.index, kind)
+    t = _barrier_ws.get(key)
     if t is None or t.numel() < nbytes:
         t = torch.zeros(max(int(nbytes), 64 + 8 * 1024), dtype=torch.uint8, device=dev)
-        _barrier_ws[dev.index] = t
+        _barrier_ws[key] = t
     return t
 
 

@@ -10,7 +10,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libpmx_moe_b200.so")
-SOURCES = ["cabi.cu", "select.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "combine_allreduce.cu", "attention.cu"]
+SOURCES = ["cabi.cu", "select.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_pair.cu", "combine_allreduce.cu", "attention.cu", "mlp_tcgen05.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

@@ -68,7 +68,7 @@ decode_attention_kernel(const AttnParams p) {
   for (int g = 0; g < kMaxGroup; ++g) {
     if (g < G) {
       float f[8];
-      unpack16<T>(ld_nc16(q + (int64_t)g * D + sl * 8), f);
+      unpack16<T>(ld_stream16(q + (int64_t)g * D + sl * 8), f);
 #pragma unroll
       for (int v = 0; v < 8; ++v) qv[g][v] = f[v] * p.scale;
     }
@@ -77,7 +77,7 @@ decode_attention_kernel(const AttnParams p) {
   // slice 0 and taken from registers (not from the cache) by whoever owns position pos_new
   const T* kc = reinterpret_cast<const T*>(p.k_cur) + ((int64_t)b * p.Hkv + h) * D + sl * 8;
   const T* vc = reinterpret_cast<const T*>(p.v_cur) + ((int64_t)b * p.Hkv + h) * D + sl * 8;
-  const uint4 kn = ld_nc16(kc), vn = ld_nc16(vc);
+  const uint4 kn = ld_stream16(kc), vn = ld_stream16(vc);
   if (s == 0 && warp == 0 && sub == 0) {
     T* krow = cache + base + (row0 + pos_new) * p.row_stride;
     *reinterpret_cast<uint4*>(krow) = kn;
@@ -111,8 +111,8 @@ decode_attention_kernel(const AttnParams p) {
         vraw[u] = vn;
       } else {
         const T* krow = cache + base + (row0 + pos) * p.row_stride;
-        kraw[u] = __ldg(reinterpret_cast<const uint4*>(krow));
-        vraw[u] = __ldg(reinterpret_cast<const uint4*>(krow + p.kv_stride));
+        kraw[u] = __ldcg(reinterpret_cast<const uint4*>(krow));
+        vraw[u] = __ldcg(reinterpret_cast<const uint4*>(krow + p.kv_stride));
       }
     }
     float kf[kUnroll][8];
@@ -217,7 +217,7 @@ decode_attention_kernel(const AttnParams p) {
 
 // out[b, head, :] = sum over slices of acc * exp(max - global max) / sum of the same for l
 template <typename T>
-__global__ void decode_attention_merge_kernel(const float* __restrict__ part, T* __restrict__ out, int Hq, int Hkv,
+__global__ void decode_attention_merge_kernel(const float* part, T* __restrict__ out, int Hq, int Hkv,
                                               int splits, int D) {
   pdl_launch_dependents();
   pdl_wait();

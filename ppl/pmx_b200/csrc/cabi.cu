@@ -12,6 +12,7 @@ namespace {
 thread_local char g_error[512] = "";
 std::atomic<long long> g_launches{0};
 std::atomic<int> g_pdl{1};
+std::atomic<int> g_l2_prefetch{8};
 }
 
 int launch_pdl(const void* kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, void** args) {
@@ -29,6 +30,8 @@ int launch_pdl(const void* kern, dim3 grid, dim3 block, size_t smem, cudaStream_
   count_launches(1);
   return PMX_OK;
 }
+
+int default_l2_prefetch() { return g_l2_prefetch.load(std::memory_order_relaxed); }
 
 void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
@@ -246,6 +249,37 @@ int pmx_moe_dense_gate_up(const void* x, const int64_t* invert_permutation, cons
                           void* stream) {
   return launch_gemm_tc_dense(x, invert_permutation, expert_offset, w, bias, h, T, N, K, E, k, dtype, beta,
                               workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+int pmx_moe_set_l2_prefetch(int32_t kblocks) {
+  return g_l2_prefetch.exchange(kblocks < 0 ? 0 : (kblocks > 64 ? 64 : kblocks), std::memory_order_relaxed);
+}
+
+int pmx_moe_dense_mlp_covers(int64_t T, int64_t N, int64_t H, int32_t E, int32_t k, int32_t dtype) {
+  return dense_mlp_covers(T, N, H, E, k, dtype) ? 1 : 0;
+}
+
+size_t pmx_moe_dense_mlp_workspace_bytes(int32_t E) { return dense_mlp_workspace_bytes(E); }
+
+int pmx_moe_dense_mlp(const void* x, const int64_t* invert_permutation, const int64_t* expert_offset, const void* wu,
+                      const void* w2, void* h, void* y, int64_t T, int64_t N, int64_t H, int32_t E, int32_t k,
+                      int32_t dtype, float beta, void* workspace, size_t workspace_bytes, void* stream) {
+  return launch_dense_mlp(x, invert_permutation, expert_offset, wu, w2, h, y, T, N, H, E, k, dtype, beta, workspace,
+                          workspace_bytes, (cudaStream_t)stream);
+}
+
+int pmx_moe_dense_mlp_check(void* workspace, int32_t E, int32_t out[4], void* stream) {
+  if (!workspace || !out || E < 1) return fail(PMX_ERR_INVALID_ARGUMENT, "dense_mlp_check: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  PMX_CUDA_OK(cudaMemcpyAsync(out, workspace, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  PMX_CUDA_OK(cudaStreamSynchronize(s));
+  if (out[0] != 0) {
+    // a launch that gave up may have left its counters behind: put the workspace back to zero
+    PMX_CUDA_OK(cudaMemsetAsync(workspace, 0, dense_mlp_workspace_bytes(E), s));
+    PMX_CUDA_OK(cudaStreamSynchronize(s));
+    return fail(PMX_ERR_DEVICE_CHECK, "dense_mlp: a bounded wait ran out (role %d, work item %d, CTA %d)", out[1], out[2], out[3]);
+  }
+  return PMX_OK;
 }
 
 int pmx_moe_grouped_linear_check(const void* workspace, int32_t out[4], void* stream) {

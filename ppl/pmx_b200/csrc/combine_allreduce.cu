@@ -117,8 +117,8 @@ __device__ __forceinline__ bool slot_ready(const uint4& a, const uint4& b, unsig
 }
 
 template <typename T>
-__device__ __forceinline__ uint4 combine_item(const T* __restrict__ y, const T* __restrict__ w,
-                                              const int64_t* __restrict__ inv, int k, int64_t N,
+__device__ __forceinline__ uint4 combine_item(const T* y, const T* w,
+                                              const int64_t* inv, int k, int64_t N,
                                               int64_t t, int64_t c) {
   constexpr int V = kVec<T>;
   float acc[V];
@@ -128,7 +128,7 @@ __device__ __forceinline__ uint4 combine_item(const T* __restrict__ y, const T* 
     const int64_t r = inv[t * k + j];
     const float wj = Elem<T>::to_f(w[t * k + j]);
     float f[V];
-    unpack16<T>(ld_nc16(y + r * N + c * V), f);
+    unpack16<T>(ld_stream16(y + r * N + c * V), f);
 #pragma unroll
     for (int v = 0; v < V; ++v) acc[v] = fmaf(wj, f[v], acc[v]);
   }

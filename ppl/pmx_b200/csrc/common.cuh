@@ -99,8 +99,18 @@ __device__ __forceinline__ long long offset_at(const int64_t* off, int e, long l
   return off ? (long long)off[e] : (e == 0 ? 0ll : M);
 }
 
+// 16 bytes of a tensor that never changes while the library runs (weights): read-only path
 __device__ __forceinline__ uint4 ld_nc16(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
+}
+// 16 bytes of a tensor that a kernel in front on the stream (or a collective) produced.  Under
+// programmatic dependent launch this kernel is resident BEFORE its producers have finished,
+// so such data is not read-only for the kernel's lifetime and must not go through the
+// non-coherent path (ld.global.nc / __ldg, or a `const __restrict__` parameter, which lets
+// the compiler choose it): a line fetched into an SM's L1 by whatever ran there earlier
+// would be served stale.  ld.global.cg reads through L2, where the producers' stores land.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  return __ldcg(reinterpret_cast<const uint4*>(p));
 }
 
 __device__ __forceinline__ float swiglu_f(float gate, float up, float beta) {
@@ -173,7 +183,9 @@ struct TcPlan {
   int stream_k;
   int balanced;    // weight rows on MMA-M: contiguous whole-tile ranges per CTA, panels not shared
   int w_pitch;     // rows between experts in w (0: N)
+  int l2_ahead;    // k-blocks of weight tiles requested into L2 in front of the ring
 };
+int default_l2_prefetch();   // process-wide default for l2_ahead (pmx_moe_set_l2_prefetch)
 // Fills `plan` for the tensor-core kernel or returns false when the shape is
 // outside what it covers (the caller then uses the CUDA-core kernel).
 bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue,
@@ -189,6 +201,12 @@ bool dense_gate_up_covers(int64_t T, int64_t N, int64_t K, int E, int k, int dty
 int launch_gemm_tc_dense(const void* x, const int64_t* inv, const int64_t* off, const void* w, const void* bias,
                          void* h, int64_t T, int64_t N, int64_t K, int E, int k, int dtype, float beta, void* ws,
                          size_t ws_bytes, cudaStream_t s);
+
+bool dense_mlp_covers(int64_t T, int64_t N, int64_t H, int E, int k, int dtype);
+size_t dense_mlp_workspace_bytes(int E);
+int launch_dense_mlp(const void* x, const int64_t* inv, const int64_t* off, const void* wu, const void* w2, void* h,
+                     void* y, int64_t T, int64_t N, int64_t H, int E, int k, int dtype, float beta, void* ws,
+                     size_t ws_bytes, cudaStream_t s);
 
 bool plan_gemm_tc_pair(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue,
                        const pmx_gemm_plan* user, TcPlan* plan);

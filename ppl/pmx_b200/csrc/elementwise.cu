@@ -21,8 +21,8 @@ inline int grid_for(int64_t work_items) {
 // One thread produces 16 bytes of one output row.  The rows of up to 4 slots are
 // requested together so that their HBM latencies overlap.
 template <typename T, bool VEC>
-__device__ __forceinline__ void reduce_item(const T* __restrict__ y, const T* __restrict__ w,
-                                            const int64_t* __restrict__ inv, T* __restrict__ out,
+__device__ __forceinline__ void reduce_item(const T* y, const T* w,
+                                            const int64_t* inv, T* __restrict__ out,
                                             int k, int64_t N, int64_t chunks, int64_t i) {
   constexpr int V = VEC ? kVec<T> : 1;
   const int64_t t = i / chunks, c = i - t * chunks;
@@ -38,7 +38,7 @@ __device__ __forceinline__ void reduce_item(const T* __restrict__ y, const T* __
         if (j0 + j < k) {
           const int64_t r = inv[t * k + j0 + j];
           wj[j] = Elem<T>::to_f(w[t * k + j0 + j]);
-          raw[j] = ld_nc16(y + r * N + c * V);
+          raw[j] = ld_stream16(y + r * N + c * V);
         }
       }
 #pragma unroll
@@ -65,8 +65,8 @@ __device__ __forceinline__ void reduce_item(const T* __restrict__ y, const T* __
 }
 
 template <typename T, bool VEC>
-__global__ void reduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
-                              const int64_t* __restrict__ inv, T* __restrict__ out, int64_t Tn,
+__global__ void reduce_kernel(const T* y, const T* w,
+                              const int64_t* inv, T* __restrict__ out, int64_t Tn,
                               int k, int64_t N) {
   pdl_launch_dependents();
   pdl_wait();
@@ -83,7 +83,7 @@ __global__ void reduce_kernel(const T* __restrict__ y, const T* __restrict__ w,
 
 // y[m, j] = x[m, D/2 + j] * x[m, j] * sigmoid(beta * x[m, j])    (SwiGLU.py:15-16)
 template <typename T, bool VEC>
-__global__ void swiglu_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t M, int64_t D,
+__global__ void swiglu_kernel(const T* x, T* __restrict__ y, int64_t M, int64_t D,
                               float beta) {
   pdl_launch_dependents();
   pdl_wait();
@@ -94,8 +94,8 @@ __global__ void swiglu_kernel(const T* __restrict__ x, T* __restrict__ y, int64_
     const int64_t m = i / chunks, c = i - m * chunks;
     if (VEC) {
       float a[kVec<T>], g[kVec<T>];
-      unpack16<T>(ld_nc16(x + m * D + c * V), a);
-      unpack16<T>(ld_nc16(x + m * D + half + c * V), g);
+      unpack16<T>(ld_stream16(x + m * D + c * V), a);
+      unpack16<T>(ld_stream16(x + m * D + half + c * V), g);
 #pragma unroll
       for (int v = 0; v < V; ++v) a[v] = g[v] * a[v] / (1.0f + expf(-beta * a[v]));
       *reinterpret_cast<uint4*>(y + m * half + c * V) = pack16<T>(a);
@@ -108,7 +108,7 @@ __global__ void swiglu_kernel(const T* __restrict__ x, T* __restrict__ y, int64_
 
 // y = silu(x) (* gate)    (SiLU.py:18-21)
 template <typename T, bool VEC>
-__global__ void silu_kernel(const T* __restrict__ x, const T* __restrict__ gate, T* __restrict__ y,
+__global__ void silu_kernel(const T* x, const T* gate, T* __restrict__ y,
                             int64_t n) {
   pdl_launch_dependents();
   pdl_wait();
@@ -118,8 +118,8 @@ __global__ void silu_kernel(const T* __restrict__ x, const T* __restrict__ gate,
        i += (int64_t)gridDim.x * blockDim.x) {
     if (VEC) {
       float a[kVec<T>], g[kVec<T>];
-      unpack16<T>(ld_nc16(x + i * V), a);
-      if (gate) unpack16<T>(ld_nc16(gate + i * V), g);
+      unpack16<T>(ld_stream16(x + i * V), a);
+      if (gate) unpack16<T>(ld_stream16(gate + i * V), g);
 #pragma unroll
       for (int v = 0; v < V; ++v) {
         a[v] = a[v] / (1.0f + expf(-a[v]));
@@ -157,7 +157,7 @@ __device__ __forceinline__ float block_sum_256(float acc, float* warp_sums, floa
 
 template <typename T, bool VEC, bool REG>
 __global__ void __launch_bounds__(256)
-skip_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ skip, const T* __restrict__ weight,
+skip_rms_norm_kernel(const T* x, const T* skip, const T* weight,
                      T* __restrict__ y, T* __restrict__ skip_out, int64_t M, int64_t H, float eps) {
   pdl_launch_dependents();
   pdl_wait();
@@ -177,10 +177,10 @@ skip_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ skip, const 
       for (int r = 0; r < R; ++r) {
         const int64_t c = threadIdx.x + (int64_t)r * blockDim.x;
         if (c < chunks) {
-          unpack16<T>(ld_nc16(xr + c * kVec<T>), a[r]);
+          unpack16<T>(ld_stream16(xr + c * kVec<T>), a[r]);
           if (sr) {
             float b[kVec<T>];
-            unpack16<T>(ld_nc16(sr + c * kVec<T>), b);
+            unpack16<T>(ld_stream16(sr + c * kVec<T>), b);
 #pragma unroll
             for (int v = 0; v < kVec<T>; ++v) a[r][v] = Elem<T>::to_f(Elem<T>::from_f(a[r][v] + b[v]));
             *reinterpret_cast<uint4*>(so + c * kVec<T>) = pack16<T>(a[r]);
@@ -207,9 +207,9 @@ skip_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ skip, const 
     for (int64_t c = threadIdx.x; c < chunks; c += blockDim.x) {
       if (VEC) {
         float a[kVec<T>], b[kVec<T>];
-        unpack16<T>(ld_nc16(xr + c * V), a);
+        unpack16<T>(ld_stream16(xr + c * V), a);
         if (sr) {
-          unpack16<T>(ld_nc16(sr + c * V), b);
+          unpack16<T>(ld_stream16(sr + c * V), b);
 #pragma unroll
           for (int v = 0; v < V; ++v) a[v] = Elem<T>::to_f(Elem<T>::from_f(a[v] + b[v]));
           *reinterpret_cast<uint4*>(so + c * V) = pack16<T>(a);
@@ -249,7 +249,7 @@ skip_rms_norm_kernel(const T* __restrict__ x, const T* __restrict__ skip, const 
 // flight at once and the reduction is five shuffles.
 template <typename T>
 __global__ void __launch_bounds__(256)
-skip_rms_norm_warp_kernel(const T* __restrict__ x, const T* __restrict__ skip, const T* __restrict__ weight,
+skip_rms_norm_warp_kernel(const T* x, const T* skip, const T* weight,
                           T* __restrict__ y, T* __restrict__ skip_out, int64_t M, int64_t H, float eps) {
   pdl_launch_dependents();
   pdl_wait();
@@ -266,8 +266,8 @@ skip_rms_norm_warp_kernel(const T* __restrict__ x, const T* __restrict__ skip, c
     for (int r = 0; r < R; ++r) {
       const int c = lane + 32 * r;
       if (c < chunks) {
-        a[r] = __ldg(xr + c);
-        if (sr) b[r] = __ldg(sr + c);
+        a[r] = __ldcg(xr + c);
+        if (sr) b[r] = __ldcg(sr + c);
       }
     }
     float acc = 0.f;
@@ -310,7 +310,7 @@ skip_rms_norm_warp_kernel(const T* __restrict__ x, const T* __restrict__ skip, c
 // rows outside [off[0], off[E]) <- 0   (the zero-initialised output of
 // MoeColumnParallelLinear.py:59 / MoeRowParallelLinear.py:45)
 template <typename T>
-__global__ void zero_outside_kernel(T* __restrict__ y, const int64_t* __restrict__ off, int64_t M,
+__global__ void zero_outside_kernel(T* __restrict__ y, const int64_t* off, int64_t M,
                                     int64_t n_out, int E) {
   pdl_launch_dependents();
   pdl_wait();
@@ -330,8 +330,8 @@ __global__ void zero_outside_kernel(T* __restrict__ y, const int64_t* __restrict
 // With SWIGLU the partial rows hold [gate | up] (n_in = 2*n_out columns) and the
 // activation is applied to the finished sums: y = up * gate * sigmoid(beta*gate).
 template <typename T, bool SWIGLU>
-__global__ void splitk_finish_kernel(const float* __restrict__ partial,
-                                     const int64_t* __restrict__ off, const T* __restrict__ bias,
+__global__ void splitk_finish_kernel(const float* partial,
+                                     const int64_t* off, const T* bias,
                                      T* __restrict__ y, int64_t M, int64_t n_out, int E, int split,
                                      float beta) {
   pdl_launch_dependents();

@@ -174,10 +174,35 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       WorkIter work;
       work.init(p, total_items);
       bool ok = true;
+      // L2 prefetch: a second walk over this CTA's k-blocks, p.l2_ahead rounds in front of the
+      // ring's own weight loads (whose first `stages` rounds are requested at once anyway)
+      WorkIter ahead;
+      Item ait;
+      int aitem = 0, akb = 0;
+      bool ahave = false;
+      auto prefetch_step = [&](bool issue) {
+        if (!ahave) return;
+        if (issue) {
+          const int arow = ait.e * p.w_pitch + ait.f0;
+          tma_prefetch_l2_2d(&map_w, akb * kBlockK, arow);
+          if (SWIGLU) tma_prefetch_l2_2d(&map_w, akb * kBlockK, arow + p.N / 2);
+        }
+        if (++akb >= ait.kb1) {
+          ahave = ahead.next(p, total_items, s_off, s_prefix, ait, aitem);
+          akb = ahave ? ait.kb0 : 0;
+        }
+      };
+      if (MODE == 1 && p.l2_ahead > 0) {
+        ahead.init(p, total_items);
+        ahave = ahead.next(p, total_items, s_off, s_prefix, ait, aitem);
+        akb = ahave ? ait.kb0 : 0;
+        for (int i = 0; i < p.stages + p.l2_ahead; ++i) prefetch_step(i >= p.stages);
+      }
       while (ok && work.next(p, total_items, s_off, s_prefix, it, item)) {
         if (DENSE) it.row0 = 0;
         const int wrow = it.e * p.w_pitch + it.f0;
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
+          if (MODE == 1 && p.l2_ahead > 0) prefetch_step(true);
           if (pre_left > 0) {
             // the weights of this k-block are in flight (or there) already: add the token tile
             --pre_left;
@@ -533,6 +558,7 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   const int want_sk = user ? user->stream_k : 0;
   // Weight rows on MMA-M: deal the feature rows of all panels out evenly (8-row units)
   // instead of whole 128-row tiles, unless the caller asks for whole tiles or stream-K.
+  pl.l2_ahead = user && user->l2_prefetch ? (user->l2_prefetch < 0 ? 0 : user->l2_prefetch) : default_l2_prefetch();
   pl.balanced = pl.kernel == PMX_GEMM_TC_WEIGHTS_M && want_sk != 1 && !(user && user->balance == 2) ? 1 : 0;
   if (user && user->split_k) {
     pl.split_k = user->split_k;
@@ -658,6 +684,7 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   p.prefetch = plan.kernel == PMX_GEMM_TC_WEIGHTS_M && plan.balanced && plan.split_k == 1 && !plan.stream_k &&
                n_out >= 128;
   p.units_per_panel = (int)(n_out / 8);
+  p.l2_ahead = plan.kernel == PMX_GEMM_TC_WEIGHTS_M && !plan.stream_k ? plan.l2_ahead : 0;
   p.kblocks = (int)ceil_div(K, kBlockK);
   p.split_k = plan.split_k;
   p.kb_per_split = (int)ceil_div(p.kblocks, plan.split_k);
@@ -758,6 +785,7 @@ int launch_gemm_tc_dense(const void* x, const int64_t* inv, const int64_t* off, 
   p.feat_tiles = 1;
   p.balanced = 1;
   p.units_per_panel = (int)(n_out / 8);
+  p.l2_ahead = default_l2_prefetch();
   p.kblocks = (int)ceil_div(K, kBlockK);
   p.split_k = 1;
   p.kb_per_split = p.kblocks;

@@ -1,0 +1,484 @@
+// Decode-size expert feed-forward in ONE launch on the 5th-generation tensor cores:
+//   h[r,:] = SwiGLU(x[t,:] . wu[e]^T)      for every token t and every expert e it chose,
+//   y[r,:] = h[r,:] . w2[e]^T              r = the row of (t,e) in the expert-sorted order,
+// i.e. moe_column_parallel_linear + swiglu + moe_row_parallel_linear of the reference
+// (MoeColumnParallelLinear.py:58-69, SwiGLU.py:15-16, MoeRowParallelLinear.py:44-55) for a
+// batch of at most 64 tokens, without the launch boundary between the two projections.
+//
+// A thin tensor-parallel shard streams its weights in a few tens of microseconds, so the
+// fixed cost of a launch (set-up, first-load latency, the drain of the last tiles) is a
+// large part of each projection.  Here both projections are work items of one persistent
+// grid (one CTA per SM, weight rows on MMA-M, all T tokens on MMA-N as in the dense
+// gate/up kernel):
+//   phase 1  items (expert, 128 gate + 128 up rows of wu), K = hidden;
+//   phase 2  items (expert, 256 rows of w2),               K = this shard's intermediate dim.
+// A CTA works through its phase-1 items, then its phase-2 items, with ONE ring of
+// shared-memory stages: the producer keeps requesting weight tiles (they depend on
+// nothing) and adds the token-side tile of a stage (x, or the rows of h) separately, so
+// the w2 stream is already in flight while the last gate/up tiles are finished elsewhere.
+// The rows of h for expert e are complete when all its gate/up tiles have counted
+// themselves in done[e] (4 epilogue warps per tile); the producer polls that counter
+// before it requests the first h tile of a phase-2 item of e.  Phase-1 items wait for
+// nothing, and a CTA finishes them before its phase-2 items, so the waits cannot form a
+// cycle; the grid is at most one CTA per SM, so all CTAs are resident.  The last CTA to
+// leave clears the counters: they are zero before the first launch and after every one.
+//
+// Roles, barriers, bounded waits and the abort path are those of grouped_gemm_tc_kernel.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace pmx {
+namespace {
+
+#include "tcgen05_common.cuh"
+
+struct MlpParams {
+  const int64_t* off;   // [E+1]
+  const int64_t* inv;   // [T,k]
+  void* h;              // [T*k, I]
+  void* y;              // [T*k, H]
+  int* status;          // 4 ints: code, role, item, aux
+  unsigned int* done;   // [E] gate/up epilogue warps finished per expert; [E] = CTAs that have left
+  int T, E, k;
+  int I, H;             // this shard's intermediate features, hidden features
+  int tile_tok;         // tokens on MMA-N: T rounded up to 16
+  int stages;
+  int f1, f2;           // work items per expert: ceil(I/128), ceil(H/256)
+  int kb1, kb2;         // k-blocks per item: ceil(H/64), ceil(I/64)
+  int g1, g2;           // CTAs that take phase-1 / phase-2 items
+  int l2_ahead;         // weight tiles are requested into L2 this many k-blocks in front of the ring
+  float beta;
+};
+
+// The work of one CTA: items [a1,b1) of phase 1, then [a2,b2) of phase 2, each a run of k-blocks.
+struct Cursor {
+  int phase;            // 1, 2; 3 = finished
+  int item, end, kb;
+  int a2, b2;
+  __device__ __forceinline__ void init(const MlpParams& p) {
+    const int c = (int)blockIdx.x;
+    const int n1 = p.E * p.f1, n2 = p.E * p.f2;
+    int a1 = 0, b1 = 0;
+    a2 = b2 = 0;
+    if (c < p.g1) {
+      a1 = (int)((long long)c * n1 / p.g1);
+      b1 = (int)((long long)(c + 1) * n1 / p.g1);
+    }
+    if (c < p.g2) {
+      a2 = (int)((long long)c * n2 / p.g2);
+      b2 = (int)((long long)(c + 1) * n2 / p.g2);
+    }
+    kb = 0;
+    phase = 1; item = a1; end = b1;
+    if (item >= end) { phase = 2; item = a2; end = b2; }
+    if (item >= end) phase = 3;
+  }
+  __device__ __forceinline__ void next_item() {
+    kb = 0;
+    if (++item < end) return;
+    if (phase == 1) {
+      phase = 2; item = a2; end = b2;
+      if (item >= end) phase = 3;
+    } else {
+      phase = 3;
+    }
+  }
+  __device__ __forceinline__ void next_kblock(const MlpParams& p) {
+    if (++kb == (phase == 1 ? p.kb1 : p.kb2)) next_item();
+  }
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// orders this thread's earlier generic-proxy accesses of global memory against later
+// accesses through the async proxy (TMA): h is written with plain stores and read by TMA
+__device__ __forceinline__ void fence_proxy_async_global() {
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wu,
+                         const __grid_constant__ CUtensorMap map_h, const __grid_constant__ CUtensorMap map_w2,
+                         const MlpParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tt = p.tile_tok;
+  const uint32_t tok_bytes = tt * 128, w_bytes = 256 * 128;
+  const uint32_t stage_bytes = tok_bytes + w_bytes;
+  Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)p.stages * stage_bytes);
+  int* s_rowmap = reinterpret_cast<int*>(sh + 1);    // [4 warps][128]: output row of every token for the current expert
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- set-up: nothing here touches memory another kernel writes ---------------
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < p.stages; ++i) {
+      mbar_init(&sh->full[i], 1);
+      mbar_init(&sh->empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh->acc_full[i], 1);
+      mbar_init(&sh->acc_empty[i], 4);
+    }
+    sh->abort = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&map_wu);
+    prefetch_tensormap(&map_h);
+    prefetch_tensormap(&map_w2);
+  }
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+  const uint32_t smem_base = smem_u32(smem);
+  const unsigned int tiles_done = 4u * (unsigned int)p.f1;   // value of done[e] once h of expert e is complete
+
+  if (warp == 0) {
+    // ========================= TMA producer =================================
+    // Two cursors over the same sequence of k-blocks: `w` requests weight tiles as soon as a
+    // stage is free, `t` follows with the token-side tile of the same stage (at most `stages`
+    // behind) once what it reads exists.
+    if (lane == 0) {
+      Cursor w, t, pf;
+      w.init(p);
+      t.init(p);
+      pf.init(p);
+      // L2 prefetch cursor, p.l2_ahead k-blocks in front of `w` (the ring itself covers the first `stages`)
+      auto prefetch_step = [&](bool issue) {
+        if (pf.phase == 3) return;
+        if (issue) {
+          if (pf.phase == 1) {
+            const int e = pf.item / p.f1, f = pf.item - e * p.f1;
+            const int row = e * 2 * p.I + f * 128;
+            tma_prefetch_l2_2d(&map_wu, pf.kb * kBlockK, row);
+            tma_prefetch_l2_2d(&map_wu, pf.kb * kBlockK, row + p.I);
+          } else {
+            const int e = pf.item / p.f2, f = pf.item - e * p.f2;
+            const int row = e * p.H + f * 256;
+            tma_prefetch_l2_2d(&map_w2, pf.kb * kBlockK, row);
+            tma_prefetch_l2_2d(&map_w2, pf.kb * kBlockK, row + 128);
+          }
+        }
+        pf.next_kblock(p);
+      };
+      if (p.l2_ahead > 0)
+        for (int i = 0; i < p.stages + p.l2_ahead; ++i) prefetch_step(i >= p.stages);
+      int w_stage = 0, t_stage = 0, pending = 0;
+      uint32_t w_phase = 0;
+      int ready_e = -1;          // expert whose rows of h are known to be complete
+      bool routed = false;       // pdl_wait() done: expert_offset may be read
+      bool ok = true;
+      while (ok && t.phase != 3) {
+        while (pending > 0) {
+          int e = 0;
+          if (t.phase == 2) {
+            e = t.item / p.f2;
+            if (e != ready_e) {
+              const bool must = pending == p.stages || w.phase == 3;   // nothing else to request
+              if (!routed) {
+                // The counters belong to this launch only once every kernel in front has
+                // finished (an earlier launch of this kernel clears them as it leaves), and
+                // expert_offset is the routing kernel's: wait for them -- but not while
+                // there are weight tiles to request.
+                if (!must) break;
+                pdl_wait();
+                routed = true;
+              }
+              bool ready = ld_acquire_gpu_u32(p.done + e) >= tiles_done;
+              if (!ready && must) {
+                // nothing else to request: wait (bounded) for the gate/up tiles of expert e
+                const unsigned long long t0 = global_ns();
+                for (unsigned int spin = 1;; ++spin) {
+                  if (ld_acquire_gpu_u32(p.done + e) >= tiles_done) { ready = true; break; }
+                  if ((spin & 15u) == 0u) {
+                    if (sh->abort) break;
+                    if (global_ns() - t0 > kWaitLimitNs) {
+                      sh->abort = 1;
+                      if (atomicExch(p.status, 1) != 1) { p.status[1] = 5; p.status[2] = t.item; p.status[3] = (int)blockIdx.x; }
+                      break;
+                    }
+                  }
+                }
+                if (!ready) { ok = false; break; }
+              }
+              if (!ready) break;
+              fence_proxy_async_global();
+              ready_e = e;
+            }
+          }
+          const uint32_t dst = smem_base + t_stage * stage_bytes;
+          mbar_expect_tx(&sh->full[t_stage], tok_bytes);
+          if (t.phase == 1) {
+            tma_load_2d(dst, &map_x, &sh->full[t_stage], t.kb * kBlockK, 0);
+          } else {
+            long long r0 = p.off[e];
+            r0 = r0 < 0 ? 0 : (r0 > (long long)p.T * p.k ? (long long)p.T * p.k : r0);
+            tma_load_2d(dst, &map_h, &sh->full[t_stage], t.kb * kBlockK, (int)r0);
+          }
+          t.next_kblock(p);
+          if (++t_stage == p.stages) t_stage = 0;
+          --pending;
+        }
+        if (!ok) break;
+        if (w.phase != 3 && pending < p.stages) {
+          ok = wait_barrier(&sh->empty[w_stage], w_phase ^ 1u, sh, p.status, 0, w.item);
+          if (!ok) break;
+          const uint32_t dst = smem_base + w_stage * stage_bytes + tok_bytes;
+          if (p.l2_ahead > 0) prefetch_step(true);
+          mbar_expect_tx_only(&sh->full[w_stage], w_bytes);
+          if (w.phase == 1) {
+            const int e = w.item / p.f1, f = w.item - e * p.f1;
+            const int row = e * 2 * p.I + f * 128;
+            tma_load_2d(dst, &map_wu, &sh->full[w_stage], w.kb * kBlockK, row);
+            tma_load_2d(dst + 128 * 128, &map_wu, &sh->full[w_stage], w.kb * kBlockK, row + p.I);
+          } else {
+            const int e = w.item / p.f2, f = w.item - e * p.f2;
+            const int row = e * p.H + f * 256;
+            tma_load_2d(dst, &map_w2, &sh->full[w_stage], w.kb * kBlockK, row);
+            tma_load_2d(dst + 128 * 128, &map_w2, &sh->full[w_stage], w.kb * kBlockK, row + 128);
+          }
+          w.next_kblock(p);
+          if (++w_stage == p.stages) { w_stage = 0; w_phase ^= 1u; }
+          ++pending;
+        }
+      }
+      if (!ok) {
+        // leave time for copies already in flight to land before the CTA exits
+        const unsigned long long t0 = global_ns();
+        while (global_ns() - t0 < 1000000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ========================= MMA issuer ===================================
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc<T>(128, tt);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      Cursor c;
+      c.init(p);
+      bool ok = true;
+      while (ok && c.phase != 3) {
+        ok = wait_barrier(&sh->acc_empty[acc], acc_phase ^ 1u, sh, p.status, 1, c.item);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kAccStride;
+        const int nkb = c.phase == 1 ? p.kb1 : p.kb2;
+        for (int kb = 0; kb < nkb; ++kb) {
+          ok = wait_barrier(&sh->full[stage], phase, sh, p.status, 2, c.item);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t tok_addr = smem_base + stage * stage_bytes;
+          const uint32_t w_addr = tok_addr + tok_bytes;
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            const uint32_t koff = kk * kUmmaK * 2;  // bytes inside the 128-byte row
+            const uint32_t accum = (kb > 0 || kk > 0) ? 1u : 0u;
+            const uint64_t bdesc = smem_desc_sw128(tok_addr + koff);
+            umma_f16(d_tmem, smem_desc_sw128(w_addr + koff), bdesc, idesc, accum);
+            umma_f16(d_tmem + tt, smem_desc_sw128(w_addr + 128 * 128 + koff), bdesc, idesc, accum);
+          }
+          umma_commit(&sh->empty[stage]);
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&sh->acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        c.next_item();
+      }
+    }
+  } else {
+    // ========================= epilogue (warps 2..5) ========================
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    Cursor c;
+    c.init(p);
+    T* h = reinterpret_cast<T*>(p.h);
+    T* y = reinterpret_cast<T*>(p.y);
+    int map_expert = -1;
+    pdl_wait();   // the routing (invert_permutation, expert_offset) is complete from here on
+    if (blockIdx.x == 0 && warp == 2 && lane < 4) p.status[lane] = 0;
+    while (c.phase != 3) {
+      const bool gate_up = c.phase == 1;
+      const int per = gate_up ? p.f1 : p.f2;
+      const int e = c.item / per, f = c.item - e * per;
+      const long long lo = p.off[e], hi = p.off[e + 1];
+      if (gate_up && e != map_expert) {
+        // which row of the expert-sorted order holds token t for this expert (-1: not routed here)
+        __syncwarp();
+        for (int t = lane; t < 128; t += 32) {
+          int r = -1;
+          if (t < p.T) {
+            for (int j = 0; j < p.k; ++j) {
+              const long long v = p.inv[(long long)t * p.k + j];
+              if (v >= lo && v < hi) r = (int)v;
+            }
+          }
+          s_rowmap[q * 128 + t] = r;
+        }
+        __syncwarp();
+        map_expert = e;
+      }
+      bool ok = wait_barrier(&sh->acc_full[acc], acc_phase, sh, p.status, 3, c.item);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * kAccStride + (static_cast<uint32_t>(q * 32) << 16);
+      if (gate_up) {
+        const int col = f * 128 + q * 32 + lane;   // feature of h this thread owns
+        const bool col_ok = col < p.I;
+        for (int c0 = 0; c0 < tt && c0 < p.T; c0 += 16) {
+          float g[16], u[16];
+          __syncwarp();
+          tmem_ld16(taddr + c0, g);
+          tmem_ld16(taddr + tt + c0, u);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int row = s_rowmap[q * 128 + c0 + i];
+            if (row >= 0 && col_ok) h[(int64_t)row * p.I + col] = Elem<T>::from_f(swiglu_f(g[i], u[i], p.beta));
+          }
+        }
+        // this warp's part of the tile is in global memory: count it for the down projection
+        __threadfence();
+        fence_proxy_async_global();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.done + e, 1u);
+      } else {
+        const int rows = (int)(hi - lo < 0 ? 0 : (hi - lo > tt ? tt : hi - lo));
+        const int col0 = f * 256 + q * 32 + lane, col1 = col0 + 128;   // features of y this thread owns
+        for (int c0 = 0; c0 < rows; c0 += 16) {
+          float a[16], b[16];
+          __syncwarp();
+          tmem_ld16(taddr + c0, a);
+          tmem_ld16(taddr + tt + c0, b);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (c0 + i < rows) {
+              T* dst = y + (int64_t)(lo + c0 + i) * p.H;
+              if (col0 < p.H) dst[col0] = Elem<T>::from_f(a[i]);
+              if (col1 < p.H) dst[col1] = Elem<T>::from_f(b[i]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      c.next_item();
+    }
+  }
+
+  // ---- common exit ------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 64) {
+    // the last CTA to leave puts the counters back to zero for the next launch
+    __threadfence();
+    if (atomicAdd(p.done + p.E, 1u) == gridDim.x - 1) {
+      for (int e = 0; e <= p.E; ++e) p.done[e] = 0u;
+    }
+  }
+}
+
+constexpr size_t kRowMapBytes = 4 * 128 * sizeof(int);
+constexpr int kMlpMaxTokens = 64;
+constexpr int kMlpCtaCap = 128;
+
+// CTAs that take the n items of a phase: the smallest grid that needs no more rounds than
+// `cap` CTAs would, so that every round is full
+int full_round_grid(int n, int cap) {
+  if (n <= 0) return 0;
+  const int rounds = (n + cap - 1) / cap;
+  return (n + rounds - 1) / rounds;
+}
+
+}  // namespace
+
+bool dense_mlp_covers(int64_t T, int64_t N, int64_t H, int E, int k, int dtype) {
+  return T >= 1 && T <= kMlpMaxTokens && E >= 1 && E <= kMaxExperts && k >= 1 && k <= E && N >= 16 && N % 16 == 0 &&
+         H >= 8 && H % 8 == 0 && (dtype == PMX_DTYPE_F16 || dtype == PMX_DTYPE_BF16) &&
+         (int64_t)E * N < (1ll << 31) && (int64_t)E * H < (1ll << 31);
+}
+
+size_t dense_mlp_workspace_bytes(int E) { return kStatusBytes + (size_t)(E + 1) * sizeof(unsigned int); }
+
+int launch_dense_mlp(const void* x, const int64_t* inv, const int64_t* off, const void* wu, const void* w2, void* h,
+                     void* y, int64_t T, int64_t N, int64_t H, int E, int k, int dtype, float beta, void* ws,
+                     size_t ws_bytes, cudaStream_t s) {
+  if (!x || !inv || !off || !wu || !w2 || !h || !y) return fail(PMX_ERR_INVALID_ARGUMENT, "dense_mlp: null pointer");
+  if (!dense_mlp_covers(T, N, H, E, k, dtype))
+    return fail(PMX_ERR_UNSUPPORTED, "dense_mlp: covers 1..%d tokens, float16 / bfloat16, N a multiple of 16 and H of 8 (T=%lld N=%lld H=%lld)", kMlpMaxTokens, (long long)T, (long long)N, (long long)H);
+  if (!aligned16(x) || !aligned16(wu) || !aligned16(w2) || !aligned16(h) || !aligned16(y))
+    return fail(PMX_ERR_ALIGNMENT, "dense_mlp: x, wu, w2, h and y must be 16-byte aligned");
+  if (!ws || ws_bytes < dense_mlp_workspace_bytes(E) || !aligned16(ws))
+    return fail(PMX_ERR_WORKSPACE, "dense_mlp: a 16-byte aligned workspace of %zu bytes is needed", dense_mlp_workspace_bytes(E));
+  const int64_t I = N / 2;
+  MlpParams p{};
+  p.off = off;
+  p.inv = inv;
+  p.h = h;
+  p.y = y;
+  p.status = reinterpret_cast<int*>(ws);
+  p.done = reinterpret_cast<unsigned int*>(reinterpret_cast<uint8_t*>(ws) + kStatusBytes);
+  p.T = (int)T; p.E = E; p.k = k;
+  p.I = (int)I; p.H = (int)H;
+  p.tile_tok = (int)(ceil_div(T, 16) * 16);
+  p.f1 = (int)ceil_div(I, 128);
+  p.f2 = (int)ceil_div(H, 256);
+  p.kb1 = (int)ceil_div(H, kBlockK);
+  p.kb2 = (int)ceil_div(I, kBlockK);
+  const int sms = sm_count();
+  const int cap = sms < kMlpCtaCap ? sms : kMlpCtaCap;
+  p.g1 = full_round_grid(E * p.f1, cap);
+  p.g2 = full_round_grid(E * p.f2, cap);
+  p.beta = beta;
+  p.l2_ahead = default_l2_prefetch();
+  const size_t stage = (size_t)(p.tile_tok + 256) * 128;
+  const size_t fixed = 1024 + sizeof(Shared) + kRowMapBytes;
+  // 24 KB of every SM's shared memory stay free, so that a CTA of the routing kernel and a
+  // CTA of this one fit on an SM together
+  int st_n = (int)((203 * 1024 - fixed) / stage);
+  if (st_n > kMaxStages) st_n = kMaxStages;
+  if (st_n < 2) return fail(PMX_ERR_UNSUPPORTED, "dense_mlp: the stage does not fit in shared memory");
+  p.stages = st_n;
+
+  CUtensorMap mx, mwu, mh, mw2;
+  int st = make_map(&mx, x, (uint64_t)T, (uint64_t)H, (uint32_t)p.tile_tok, dtype);
+  if (st != PMX_OK) return st;
+  st = make_map(&mwu, wu, (uint64_t)E * N, (uint64_t)H, 128u, dtype);
+  if (st != PMX_OK) return st;
+  st = make_map(&mh, h, (uint64_t)T * k, (uint64_t)I, (uint32_t)p.tile_tok, dtype);
+  if (st != PMX_OK) return st;
+  st = make_map(&mw2, w2, (uint64_t)E * H, (uint64_t)I, 128u, dtype);
+  if (st != PMX_OK) return st;
+
+  const size_t smem = fixed + stage * (size_t)p.stages;
+  const void* kern = dtype == PMX_DTYPE_BF16 ? (const void*)expert_mlp_decode_kernel<__nv_bfloat16>
+                                             : (const void*)expert_mlp_decode_kernel<__half>;
+  PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int grid = p.g1 > p.g2 ? p.g1 : p.g2;
+  void* args[] = {(void*)&mx, (void*)&mwu, (void*)&mh, (void*)&mw2, (void*)&p};
+  return launch_pdl(kern, dim3(grid), dim3(kThreads), smem, s, args);
+}
+
+}  // namespace pmx

@@ -44,7 +44,7 @@ __device__ __forceinline__ uint32_t score_key(float s) {
 }
 
 template <typename T>
-__global__ void route_count_kernel(const T* __restrict__ scores, int64_t T_tokens, int E, int k,
+__global__ void route_count_kernel(const T* scores, int64_t T_tokens, int E, int k,
                                    int tpb, T* __restrict__ weights, int* __restrict__ ids,
                                    int* __restrict__ block_counts) {
   pdl_launch_dependents();
@@ -152,9 +152,9 @@ __global__ void scan_kernel(int* __restrict__ block_counts, int nblk, int E, int
 }
 
 template <typename T, bool VEC>
-__global__ void place_gather_kernel(const T* __restrict__ x, const int* __restrict__ ids,
-                                    const int* __restrict__ block_base,
-                                    const int64_t* __restrict__ expert_offset, int64_t T_tokens,
+__global__ void place_gather_kernel(const T* x, const int* ids,
+                                    const int* block_base,
+                                    const int64_t* expert_offset, int64_t T_tokens,
                                     int64_t H, int E, int k, int tpb, T* __restrict__ xp,
                                     int64_t* __restrict__ inv) {
   pdl_launch_dependents();
@@ -200,7 +200,7 @@ __global__ void place_gather_kernel(const T* __restrict__ x, const int* __restri
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int i = i0 + u * blockDim.x;
-        if (i < total) v[u] = __ldg(src + i);
+        if (i < total) v[u] = __ldcg(src + i);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -235,7 +235,7 @@ constexpr int kSmallMaxExperts = 64;
 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
-select_small_kernel(const T* __restrict__ x, const T* __restrict__ scores, int Tn, int64_t H, int E,
+select_small_kernel(const T* x, const T* scores, int Tn, int64_t H, int E,
                     int k, int tpb, T* __restrict__ xp, T* __restrict__ weights,
                     int64_t* __restrict__ inv, int64_t* __restrict__ expert_offset) {
   pdl_launch_dependents();
@@ -329,7 +329,7 @@ select_small_kernel(const T* __restrict__ x, const T* __restrict__ scores, int T
     uint4* dst = reinterpret_cast<uint4*>(xp);
     for (int i = threadIdx.x; i < ntok * chunks; i += blockDim.x) {
       const int tl = i / chunks, c = i - tl * chunks;
-      const uint4 v = __ldg(src + (int64_t)tl * chunks + c);
+      const uint4 v = __ldcg(src + (int64_t)tl * chunks + c);
       for (int j = 0; j < k; ++j) dst[(int64_t)pos[tl * k + j] * chunks + c] = v;
     }
   } else {
@@ -395,7 +395,7 @@ struct NormArgs {
 
 template <typename T, bool NORM>
 __global__ void __launch_bounds__(256)
-route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, int64_t H, int E, int k,
+route_select_kernel(const T* x, const T* wr, int Tn, int64_t H, int E, int k,
                     int tpb, T* __restrict__ scores, T* __restrict__ xp, T* __restrict__ weights,
                     int64_t* __restrict__ inv, int64_t* __restrict__ expert_offset,
                     unsigned long long* __restrict__ masks, unsigned int* __restrict__ counter,
@@ -435,10 +435,10 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
       float acc = 0.f;
       for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
         float a[V];
-        unpack16<T>(__ldg(xr + c), a);
+        unpack16<T>(__ldcg(xr + c), a);
         if (sr) {
           float b[V];
-          unpack16<T>(__ldg(sr + c), b);
+          unpack16<T>(__ldcg(sr + c), b);
 #pragma unroll
           for (int v = 0; v < V; ++v) a[v] = Elem<T>::to_f(Elem<T>::from_f(a[v] + b[v]));
           so[c] = pack16<T>(a);
@@ -476,7 +476,7 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
       for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
         float a[V];
-        unpack16<T>(NORM ? rows[(size_t)tl * chunks + c] : __ldg(xr + c), a);
+        unpack16<T>(NORM ? rows[(size_t)tl * chunks + c] : __ldcg(xr + c), a);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           if (e0 + j < E) {
@@ -604,7 +604,7 @@ route_select_kernel(const T* __restrict__ x, const T* __restrict__ wr, int Tn, i
   uint4* dst = reinterpret_cast<uint4*>(xp);
   for (int i = threadIdx.x; i < ntok * chunks; i += blockDim.x) {
     const int tl = i / chunks, c = i - tl * chunks;
-    const uint4 v = NORM ? rows[i] : __ldg(src + (int64_t)tl * chunks + c);
+    const uint4 v = NORM ? rows[i] : __ldcg(src + (int64_t)tl * chunks + c);
     for (int j = 0; j < k; ++j) dst[(int64_t)pos[tl * k + j] * chunks + c] = v;
   }
 }
@@ -640,7 +640,7 @@ constexpr int kWideMaxTokensPerBlock = 1024;
 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(kWideThreads)
-select_wide_kernel(const T* __restrict__ x, const T* __restrict__ scores, int64_t Tn, int64_t H, int E, int k,
+select_wide_kernel(const T* x, const T* scores, int64_t Tn, int64_t H, int E, int k,
                    int tpb, T* __restrict__ xp, T* __restrict__ weights, int64_t* __restrict__ inv,
                    int64_t* __restrict__ expert_offset, unsigned int* __restrict__ barrier,
                    int* __restrict__ block_counts, int* __restrict__ status, unsigned long long wait_ns) {
@@ -781,7 +781,7 @@ select_wide_kernel(const T* __restrict__ x, const T* __restrict__ scores, int64_
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int i = i0 + u * blockDim.x;
-        if (i < total) v[u] = __ldg(src + i);
+        if (i < total) v[u] = __ldcg(src + i);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {

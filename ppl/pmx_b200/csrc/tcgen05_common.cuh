@@ -41,6 +41,8 @@ struct Params {
                         // whole panels, cut into pieces of at most 128 rows in 8-row units
                         // (feat_tiles is 1 then: a work "item" of the prefix table is a panel)
   int units_per_panel;  // n_out / 8
+  int l2_ahead;         // weight rows on MMA-M: the producer asks for the weight tiles of the k-block this
+                        // many rounds in front of the ring to be brought into L2 (0: no prefetch)
 };
 
 // tensor maps over the weights with boxes of 64, 32, 16 and 8 rows: a range of feature
@@ -94,6 +96,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
       "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+// asks for a tile to be brought into L2 (no shared memory, no barrier): the weight stream of a
+// thin shard is limited by the bytes a CTA's ring keeps in flight, not by HBM
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y)
+               : "memory");
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

@@ -22,7 +22,7 @@ from torch import nn
 from . import torch_function as OPMX
 from ._cabi import GemmPlan
 from .torch_function.moe import (moe_grouped_linear, moe_route_select, moe_norm_route_select, moe_dense_gate_up,
-                                 dense_gate_up_covers)
+                                 dense_gate_up_covers, moe_dense_mlp, dense_mlp_covers, dense_mlp_check)
 
 # below this many bytes of [T,H] result one all-reduce is cheaper than overlapped slices
 OVERLAP_MIN_BYTES = 8 << 20
@@ -169,7 +169,7 @@ class MoeFeedForward(nn.Module):
     def __init__(self, hidden_dim: int, intermediate_dim: int, num_experts: int,
                  num_experts_per_token: int, proc_group=None, linear_bias_term: bool = False,
                  fused: bool = True, peer_reduce_tokens: int = 0, peer_algorithm: str = "auto",
-                 overlap_chunks: int = 1, dense_decode: bool = True) -> None:
+                 overlap_chunks: int = 1, dense_decode: bool = True, one_launch_experts: bool = True) -> None:
         super().__init__()
         self.num_experts = num_experts
         self.num_experts_per_token = num_experts_per_token
@@ -188,6 +188,9 @@ class MoeFeedForward(nn.Module):
         self.overlap_chunks = overlap_chunks
         # decode-size batches: gate/up projection from the un-permuted tokens, overlapping the router
         self.dense_decode = dense_decode
+        # ... and, where it is covered, both expert projections in one launch
+        self.one_launch_experts = one_launch_experts
+        self._mlp_ws = None
         self._peer = None
         self._last_workspaces = ()     # status words of the last step's expert GEMMs, for check()
         self.gate = Linear(hidden_dim, num_experts, bias_term=False)
@@ -226,6 +229,13 @@ class MoeFeedForward(nn.Module):
                 routed = moe_route_select(x, self.gate.weight, E, k, gather=False)
             if routed is not None:
                 _, _, expert_weights, invert_permutation, expert_offset = routed
+                if (self.one_launch_experts and self.wu.bias is None and self.w2.bias is None
+                        and dense_mlp_covers(tokens, self.wu.weight, self.w2.weight, k)):
+                    with _range("moe.experts(one launch)"):
+                        y, self._mlp_ws = moe_dense_mlp(x, invert_permutation, expert_offset, self.wu.weight,
+                                                        self.w2.weight, return_workspace=True)
+                    self._last_workspaces = ()
+                    return self._combine(y, expert_weights, invert_permutation)
                 with _range("moe.gate_up_swiglu(dense)"):
                     h, ws1 = moe_dense_gate_up(x, invert_permutation, expert_offset, self.wu.weight, self.wu.bias,
                                                return_workspace=True)
@@ -271,6 +281,13 @@ class MoeFeedForward(nn.Module):
             y, ws2 = moe_grouped_linear(h, expert_offset, self.w2.weight, bias2, zero_outside=False,
                                         return_workspace=True)
         self._last_workspaces = (ws1, ws2)
+        self._mlp_ws = None
+        return self._combine(y, expert_weights, invert_permutation)
+
+    def _combine(self, y, expert_weights, invert_permutation):
+        """combine (+ exchange over TP) of the down projection's rows y [T*k, H]."""
+        k = self.num_experts_per_token
+        world = _world(self.proc_group)
         with _range("moe.combine_allreduce"):
             if world > 1 and self.peer_reduce_tokens > 0:
                 if self._peer is None:
@@ -325,6 +342,8 @@ class MoeFeedForward(nn.Module):
         for ws in self._last_workspaces:
             if ws is not None:
                 grouped_linear_check(ws)
+        if self._mlp_ws is not None:
+            dense_mlp_check(self._mlp_ws, self.num_experts)
         route_select_check(device=self.gate.weight.device)
         if self._peer is not None:
             self._peer.check()

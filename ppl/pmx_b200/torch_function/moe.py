@@ -119,7 +119,7 @@ def route_select_check(workspace: torch.Tensor | None = None, device=None) -> No
         ws = workspace
     else:
         index = torch.device(device).index if device is not None else None
-        ws = _cabi._barrier_ws.get(torch.cuda.current_device() if index is None else index)
+        ws = _cabi._barrier_ws.get((torch.cuda.current_device() if index is None else index, "route"))
     if ws is None:
         return
     with torch.cuda.device(ws.device):
@@ -321,6 +321,56 @@ def moe_dense_gate_up(X: torch.Tensor, invert_permutation: torch.Tensor, expert_
         check(lib.pmx_moe_dense_gate_up(ptr(x2), ptr(inv), ptr(off), ptr(w), ptr(b), ptr(h), T, N, K, E, k, code,
                                         float(beta), ptr(ws), ws.numel(), stream_of(X)))
     return (h, ws) if return_workspace else h
+
+
+def dense_mlp_covers(T: int, Wu: torch.Tensor, W2: torch.Tensor, k: int) -> bool:
+    """Whether moe_dense_mlp takes this shape and pays: the shapes dense_gate_up_covers accepts
+    (decode batches on thin tensor-parallel shards, where the fixed cost of a launch is a large
+    part of each projection), without bias."""
+    E, N, H = Wu.shape
+    code = DTYPE_CODE.get(Wu.dtype)
+    if code is None or tuple(W2.shape) != (E, H, N // 2) or W2.dtype != Wu.dtype:
+        return False
+    return bool(dense_gate_up_covers(T, Wu, k) and lib.pmx_moe_dense_mlp_covers(T, N, H, E, k, code))
+
+
+def moe_dense_mlp(X: torch.Tensor, invert_permutation: torch.Tensor, expert_offset: torch.Tensor,
+                  Wu: torch.Tensor, W2: torch.Tensor, beta: float = 1.0, workspace: torch.Tensor | None = None,
+                  return_workspace: bool = False):
+    """Y[r] = SwiGLU(X[t] @ Wu[e].T) @ W2[e].T for every (token t, chosen expert e), r = the row of
+    that pair in the expert-sorted order: moe_column_parallel_linear + swiglu +
+    moe_row_parallel_linear (before its all-reduce) of the reference for the rows moe_select
+    gathers (Model.py:198-205), from the un-permuted X [T,H], in one launch (see
+    pmx_moe_dense_mlp).  -> Y [T*k, H].  Launch it directly behind moe_route_select on the
+    same stream.  `workspace`: see _cabi.barrier_workspace (default: one kept buffer per device)."""
+    _require_cuda("moe_dense_mlp", X=X, Wu=Wu, W2=W2, invert_permutation=invert_permutation)
+    E, N, H = Wu.shape
+    T = X.numel() // H
+    k = invert_permutation.shape[-1]
+    code = _dtype_code("moe_dense_mlp", X)
+    if Wu.dtype != X.dtype or W2.dtype != X.dtype:
+        raise TypeError("X, Wu and W2 must have the same dtype")
+    if tuple(W2.shape) != (E, H, N // 2):
+        raise ValueError(f"W2 must be [{E}, {H}, {N // 2}], got {tuple(W2.shape)}")
+    dev = X.device
+    h = torch.empty(T * k, N // 2, dtype=X.dtype, device=dev)
+    y = torch.empty(T * k, H, dtype=X.dtype, device=dev)
+    nbytes = lib.pmx_moe_dense_mlp_workspace_bytes(E)
+    ws = workspace if workspace is not None else _cabi.barrier_workspace(nbytes, dev, kind="mlp")
+    x2, wu, w2 = X.contiguous().view(T, H), Wu.contiguous(), W2.contiguous()
+    inv = invert_permutation.contiguous()
+    off = _offsets_on(expert_offset, dev, E)
+    with torch.cuda.device(dev):
+        check(lib.pmx_moe_dense_mlp(ptr(x2), ptr(inv), ptr(off), ptr(wu), ptr(w2), ptr(h), ptr(y), T, N, H, E, k,
+                                    code, float(beta), ptr(ws), ws.numel(), stream_of(X)))
+    return (y, ws) if return_workspace else y
+
+
+def dense_mlp_check(ws: torch.Tensor, num_experts: int) -> None:
+    """Synchronises and raises if the moe_dense_mlp launch that used `ws` recorded a wait that ran out."""
+    out = (C.c_int32 * 4)()
+    with torch.cuda.device(ws.device):
+        check(lib.pmx_moe_dense_mlp_check(ptr(ws), int(num_experts), C.byref(out), stream_of(ws)))
 
 
 def grouped_linear_check(ws: torch.Tensor) -> None:

@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol(lib):
     raw = C.CDLL(os.path.join(ROOT, "ppl", "pmx_b200", "libpmx_moe_b200.so"))
     for n in names:
         assert hasattr(raw, n), f"{n} declared in pmx_moe.h but not exported"
-    assert lib.pmx_moe_abi_version() == 2
+    assert lib.pmx_moe_abi_version() == 3
     assert lib.pmx_moe_status_string(-4) == b"workspace missing or too small"
 
 

@@ -422,6 +422,86 @@ def test_dense_gate_up_matches_the_routed_projection(F, T, H, E, k, N, dtype):
     assert h.shape == (T * k, N // 2)
 
 
+@pytest.mark.parametrize("T,H,E,k,N,dtype", [(64, 512, 8, 2, 1024, "f16"), (16, 256, 8, 2, 3584, "f16"),
+                                             (33, 1024, 4, 2, 784, "bf16"), (64, 4096, 8, 2, 3584, "f16"),
+                                             (1, 256, 4, 1, 272, "f16"), (48, 328, 16, 4, 528, "bf16"),
+                                             (64, 2048, 8, 8, 512, "bf16")])
+def test_dense_mlp_matches_two_launches_and_the_oracle(F, T, H, E, k, N, dtype):
+    """Both expert projections in one launch against the oracle, against the dense gate/up
+    launch followed by the routed down projection, and against itself when launches follow
+    each other directly on the stream (each must see the counters of its own launch only);
+    one expert is left without tokens, H and N/2 need not be multiples of the tile sizes."""
+    from ppl.pmx_b200.torch_function.moe import moe_grouped_linear, dense_mlp_check
+    rng = np.random.default_rng(T + N + H)
+    x = orc.round_to_dtype(rng.standard_normal((T, H)).astype(np.float32), dtype)
+    sc = rng.standard_normal((T, E)).astype(np.float32)
+    if E > k:
+        sc[:, E // 2] = -1e4                       # nobody picks this expert
+    sc, _ = orc.detie_scores(sc, dtype)
+    wu = orc.round_to_dtype((rng.standard_normal((E, N, H)) / np.sqrt(H)).astype(np.float32), dtype)
+    w2 = orc.round_to_dtype((rng.standard_normal((E, H, N // 2)) / np.sqrt(N // 2)).astype(np.float32), dtype)
+    xd, wud, w2d = dev(x, dtype), dev(wu, dtype), dev(w2, dtype)
+    _, ew, inv, off = F.moe_select(xd, dev(sc, dtype), E, k)
+    y, ws = F.moe_dense_mlp(xd, inv, off, wud, w2d, return_workspace=True)
+    dense_mlp_check(ws, E)
+    assert y.shape == (T * k, H)
+    assert int(ws[256:256 + 4 * (E + 1)].view(torch.int32).abs().sum()) == 0, "the counters must be left zero"
+    h = F.moe_dense_gate_up(xd, inv, off, wud, None)
+    two = moe_grouped_linear(h, off, w2d, None, zero_outside=False)
+    oxe, _, _, ooff = orc.moe_select(x, sc, E, k, dtype)
+    oh = orc.round_to_dtype(orc.swiglu(orc.moe_grouped_linear(oxe, ooff, wu, None)), dtype)
+    ref = orc.moe_grouped_linear(oh, ooff, w2, None)
+    assert_close(y, ref, dtype)
+    assert_close(y, host(two), dtype)
+    # launches directly behind one another
+    ys = [F.moe_dense_mlp(xd, inv, off, wud, w2d) for _ in range(4)]
+    torch.cuda.synchronize()
+    dense_mlp_check(ws, E)
+    for other in ys:
+        assert torch.equal(other, y)
+
+
+def test_block_one_launch_experts_equals_two_launches(F):
+    """MoeFeedForward with both expert projections in one launch against the same block with
+    the dense gate/up launch + the down launch, eagerly and replayed from a CUDA graph."""
+    from ppl.pmx_b200 import workloads as W
+    from ppl.pmx_b200.moe_layers import MoeFeedForward
+    from ppl.pmx_b200.torch_function.moe import dense_mlp_covers
+    sh = W.scaled(W.WORKLOADS["decode_t64"], H=1024, I=1792)
+    x, wr, _, _ = W.make_activations(sh)
+    wu, w2 = W.make_expert_weights(sh, "cuda")
+    assert dense_mlp_covers(sh.T, wu, w2, sh.k), "this shape must take the one-launch path"
+    blocks = []
+    for one in (True, False):
+        blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, None, False, one_launch_experts=one).cuda().half()
+        with torch.no_grad():
+            blk.gate.weight.copy_(wr)
+            blk.wu.weight.copy_(wu)
+            blk.w2.weight.copy_(w2)
+        blocks.append(blk)
+    xd = x.cuda()
+    with torch.no_grad():
+        a, b = blocks[0](xd), blocks[1](xd)
+        torch.cuda.synchronize()
+        blocks[0].check()
+        assert blocks[0]._mlp_ws is not None and blocks[1]._mlp_ws is None
+        torch.testing.assert_close(a.float(), b.float(), atol=2e-3, rtol=2e-3)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            blocks[0](xd)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = blocks[0](xd)
+        for _ in range(20):
+            g.replay()
+        torch.cuda.synchronize()
+        blocks[0].check()
+        assert torch.equal(out, a)
+        g.reset()
+
+
 def test_block_dense_decode_path_equals_the_routed_path(F):
     """MoeFeedForward with the router + dense gate/up path (decode-size batch) against the
     same block with that path switched off, eagerly and replayed from a CUDA graph."""
