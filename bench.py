@@ -259,6 +259,52 @@ def capture(fn):
     return g, out
 
 
+STAMP_KERNELS = {1: "route_select", 2: "grouped_gemm", 3: "dense_gate_up", 4: "experts_one_launch"}
+STAMP_WORDS = ["entry", "setup_done", "first_tile", "last_mma", "epilogue_free", "epilogue_done", "exit",
+               "first_h_tile_or_last_accumulator"]
+
+
+def record_stamps(ctx, step):
+    """One replay of the step's CUDA graph with the kernels' %globaltimer stamps switched on
+    (pmx_moe_set_stamp_buffer): per instrumented launch, the minimum / median / maximum over
+    its CTAs of every stamp, in microseconds after the first stamp of the replay."""
+    from ppl.pmx_b200 import _cabi
+    import ctypes as C
+    import numpy as np
+    buf = torch.zeros(64 * 160 * 8, dtype=torch.int64, device=ctx.device)
+    _cabi.lib.pmx_moe_set_stamp_buffer(C.c_void_p(buf.data_ptr()), buf.numel() * 8)
+    try:
+        g, _ = capture(step)            # slots: one eager run, then the captured launches
+        ids = (C.c_int32 * 256)()
+        used = _cabi.lib.pmx_moe_stamp_slots(ids, 256)
+    finally:
+        _cabi.lib.pmx_moe_set_stamp_buffer(None, 0)
+    for _ in range(5):
+        g.replay()
+    torch.cuda.synchronize()
+    buf.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    data = buf.cpu().numpy().reshape(64, 160, 8)
+    g.reset()
+    per = used // 2
+    slots = range(per, used)
+    t0 = min(int(data[s][data[s] > 0].min()) for s in slots if (data[s] > 0).any())
+    rec = []
+    for s in slots:
+        d = data[s]
+        row = {"kernel": STAMP_KERNELS.get(ids[s], str(ids[s])), "ctas": int((d[:, 0] > 0).sum())}
+        for w, name in enumerate(STAMP_WORDS):
+            v = d[:, w][d[:, w] > 0]
+            if v.size:
+                row[name] = [round((int(x) - t0) / 1e3, 2) for x in (v.min(), np.median(v), v.max())]
+        if ctx.args.stamps_raw:
+            row["per_cta"] = {name: [round((int(x) - t0) / 1e3, 1) if x > 0 else None for x in d[:, w]]
+                              for w, name in enumerate(STAMP_WORDS) if (d[:, w] > 0).any()}
+        rec.append(row)
+    return rec
+
+
 def get_block(ctx, shape, full: bool, w_router=None):
     """The MoE block of this rank for `shape` (cached by architecture and dtype: the decode
     workloads share one set of weights).  full=True: the whole weights, no process group."""
@@ -278,7 +324,8 @@ def get_block(ctx, shape, full: bool, w_router=None):
                          peer_reduce_tokens=peer_tokens, peer_algorithm=ctx.args.peer_algo,
                          overlap_chunks=ctx.args.overlap_chunks,
                          dense_decode=not ctx.args.no_dense_decode,
-                         one_launch_experts=not ctx.args.no_one_launch).to(ctx.device, dt)
+                         one_launch_experts=not ctx.args.no_one_launch,
+                         token_microbatches=ctx.args.token_microbatches).to(ctx.device, dt)
     wu, w2 = W.make_expert_weights(shape, ctx.device, tp_rank=0 if full else ctx.rank, tp_size=tp)
     if w_router is None:
         _, w_router, _, _ = W.make_activations(shape, detie=False)
@@ -499,6 +546,9 @@ def measure(ctx, shape, steps, warmup, regions, headline):
         for g in keep:
             g.reset()
         del keep
+    stamps_rec = None
+    if args.stamps and headline and not args.no_graph:
+        stamps_rec = record_stamps(ctx, step)
     active = int((off[1:] - off[:-1]).gt(0).sum().item())
     # phase boundaries inside the fused combine + all-reduce (one extra call with stamps on)
     ar_phases = None
@@ -585,6 +635,7 @@ def measure(ctx, shape, steps, warmup, regions, headline):
                   "allreduce_phases_ns": ar_phases,
                   "gate_up_from_unpermuted_tokens": bool(dense),
                   "experts_in_one_launch": bool(one_launch),
+                  "stamps": stamps_rec,
                   "kernel_ms": {n: round(v, 5) for n, v in kernel_ms.items() if n in STAGES and v > 0}},
         "parity": parity,
     }
@@ -915,7 +966,16 @@ def main():
                          "reads the un-permuted tokens and overlaps the router")
     ap.add_argument("--l2-prefetch", type=int, default=None,
                     help="k-blocks of weight tiles the weight-streaming GEMMs request into L2 in front of their "
-                         "shared-memory ring (library default 8; 0 = none)")
+                         "shared-memory ring (library default 0 = none)")
+    ap.add_argument("--attention-kernel", default="mma", choices=["mma", "simt"],
+                    help="decode attention: tensor-core kernel or CUDA-core kernel")
+    ap.add_argument("--stamps", action="store_true",
+                    help="headline step: record %%globaltimer stamps inside the router and expert GEMM kernels of one "
+                         "graph replay and print the timeline under layer.stamps")
+    ap.add_argument("--token-microbatches", type=int, default=1,
+                    help="N > 1, results too large for the peer kernel: runs of tokens whose all-reduce overlaps "
+                         "the next run's kernels")
+    ap.add_argument("--stamps-raw", action="store_true", help="with --stamps: also the per-CTA values")
     ap.add_argument("--no-one-launch", action="store_true",
                     help="decode-size batches on thin shards: gate/up and down projection as two launches")
     ap.add_argument("--overlap-chunks", type=int, default=1,
@@ -972,6 +1032,7 @@ def main():
         _cabi.lib.pmx_moe_set_programmatic_launch(0)
     if args.l2_prefetch is not None:
         _cabi.lib.pmx_moe_set_l2_prefetch(args.l2_prefetch)
+    _cabi.lib.pmx_decode_cache_attention_set_kernel(["mma", "simt"].index(args.attention_kernel))
     ctx.gemm_plan = parse_plan(args.gemm_plan)
 
     if args.attention_only:

@@ -86,7 +86,7 @@ typedef struct pmx_gemm_plan {
                            projection.  Not with SwiGLU, split-K or stream-K. */
   int32_t l2_prefetch;  /* PMX_GEMM_TC_WEIGHTS_M only: the weight tiles of the k-block this many rounds in
                            front of the shared-memory ring are requested into L2 (0 = the process-wide
-                           default, see pmx_moe_set_l2_prefetch; negative = none) */
+                           default, none unless pmx_moe_set_l2_prefetch changed it; negative = none) */
 } pmx_gemm_plan;
 
 int pmx_moe_abi_version(void);
@@ -106,8 +106,21 @@ int pmx_moe_set_programmatic_launch(int on);
  * gate/up and the one-launch decode kernels), in k-blocks of 64 elements; 0 = no prefetch.
  * A thin shard's weight stream is limited by the bytes the CTAs' shared-memory rings keep
  * in flight (about 18 MB for 112 CTAs); requests into L2 cost no shared memory.  Process-wide;
- * returns the previous value.  Default 8. */
+ * returns the previous value.  Default 0: on B200 the requests compete with the ring's own
+ * loads in the TMA unit and every distance measured was slower (8 k-blocks: the 64-token Mixtral
+ * decode step 0.68 ms against 0.47 ms, its 1/8 shard 116 against 94 us). */
 int pmx_moe_set_l2_prefetch(int32_t kblocks);
+/* Diagnostic: while a device buffer is set, every launch of the router + select kernel and of
+ * the weight-streaming expert GEMMs (also when recorded into a CUDA graph) takes the next slot
+ * of 160 x 8 uint64 in it and its CTAs store %globaltimer values there: [cta][0] entry,
+ * [1] set-up done, [2] first tile arrived, [3] last MMA issued, [4] epilogue free to store
+ * (its dependency wait is over), [5] epilogue done, [6] CTA leaves (router: [1] dependency
+ * wait over, [2] grid barrier passed).  Returns the number of slots the buffer holds (at
+ * most 256); buffer = NULL switches the stamps off.  pmx_moe_stamp_slots: which kernel
+ * took each slot so far (1 router + select, 2 grouped GEMM, 3 dense gate/up, 4 both
+ * projections in one launch); returns the number of slots taken. */
+int pmx_moe_set_stamp_buffer(void* buffer, size_t bytes);
+int pmx_moe_stamp_slots(int32_t* kernel_ids, int32_t max_ids);
 
 /*
  * moe_select -- replaces MoeSelect.forward, torch_function/MoeSelect.py:36-64.
@@ -341,6 +354,10 @@ int pmx_moe_reduce(const void* y, const void* expert_weights,
  * of the result.  float16 / bfloat16, head_dim 64 or 128, at most 8 query heads per kv head.
  * Workspace: pmx_decode_cache_attention_workspace_bytes(...) bytes, 16-byte aligned.
  */
+/* Which kernel pmx_decode_cache_attention runs: 0 (default) the tensor-core kernel (mma.sync
+ * m16n8k16 on tiles staged in shared memory with cp.async), 1 the CUDA-core kernel (16-byte
+ * loads straight into registers).  Process-wide; returns the previous value. */
+int pmx_decode_cache_attention_set_kernel(int32_t kernel);
 size_t pmx_decode_cache_attention_workspace_bytes(int64_t B, int32_t num_heads, int32_t num_kv_heads,
                                                   int32_t head_dim, int64_t max_kvlen);
 int pmx_decode_cache_attention(const void* query, const void* current_key, const void* current_value,

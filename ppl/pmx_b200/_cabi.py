@@ -54,6 +54,9 @@ def _load() -> C.CDLL:
         "pmx_moe_route_select_check": (C.c_int, [vp, vp]),
         "pmx_moe_set_programmatic_launch": (C.c_int, [C.c_int]),
         "pmx_moe_set_l2_prefetch": (C.c_int, [i32]),
+        "pmx_moe_set_stamp_buffer": (C.c_int, [vp, sz]),
+        "pmx_moe_stamp_slots": (C.c_int, [vp, i32]),
+        "pmx_decode_cache_attention_set_kernel": (C.c_int, [i32]),
         "pmx_moe_norm_route_select_workspace_bytes": (sz, [i64, i64, i32, i32, i32]),
         "pmx_moe_norm_route_select": (C.c_int, [vp, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, i32, i32,
                                                 vp, sz, vp]),

@@ -14,10 +14,17 @@
 // instruction, several instructions in flight), with the running maximum / sum / weighted
 // value sum of an online softmax in registers.  The slices of a (sequence, kv head) are merged by a second,
 // tiny kernel.  All cache layouts of cache_mode 0 are covered through strides.
+#include <atomic>
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace pmx {
 namespace {
+
+__device__ __forceinline__ uint32_t smem_u32_attn(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
 
 constexpr int kAttnWarps = 4;
 constexpr int kGroupLimit = 8;     // query heads per kv head
@@ -215,6 +222,240 @@ decode_attention_kernel(const AttnParams p) {
   }
 }
 
+// ---- tensor-core variant ---------------------------------------------------------
+// The same work split, with the two small matrix products of a slice on the tensor cores
+// (mma.sync m16n8k16, fp32 accumulation): S = Q K^T with the query heads of the group on
+// MMA-M (padded to 16 rows) and 16 cached positions on MMA-N, O += P V with the head
+// dimension on MMA-N.  The kernel needs 2 FLOP per cache byte, so the legacy tensor path
+// is far from a limit; what it removes are the conversions and multiply-adds that kept
+// the CUDA-core version instruction-bound.  Every warp owns a ring of kMmaStages tiles
+// (16 positions x {keys, values}) in shared memory, filled with cp.async (16 bytes per
+// lane, zero fill behind the end of the slice) and read with ldmatrix (values transposed);
+// 16-byte chunks of a row are XOR-swizzled with the row index so that neither is bank
+// conflicted.  The S accumulator fragments are the A fragments of P as they are.
+constexpr int kMmaStages = 3;
+constexpr int kMmaTile = 16;          // cached positions per tile
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  if constexpr (sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  } else {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kAttnWarps * 32, 2)
+decode_attention_mma_kernel(const AttnParams p) {
+  constexpr int CH = D / 8;                       // 16-byte chunks per head row
+  constexpr int ROWB = D * 2;                     // bytes per head row
+  constexpr int TILEB = kMmaTile * ROWB;          // one tile of keys (or values)
+  constexpr int KS = D / 16;                      // k-steps of Q K^T
+  constexpr int NT = D / 8;                       // n-tiles of P V
+  extern __shared__ __align__(128) uint8_t attn_smem[];
+  __shared__ float sm_m[kAttnWarps][kGroupLimit], sm_l[kAttnWarps][kGroupLimit];
+  const int b = blockIdx.x, h = blockIdx.y, s = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = p.Hq / p.Hkv;
+  const int r = lane >> 2, cq = lane & 3;         // fragment row (query head of the group), column pair
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t pos_new = p.start_pos[b];
+  const int64_t kvlen = pos_new + 1;
+  const int64_t row0 = p.cachestarts[b];
+  const T* cache = reinterpret_cast<const T*>(p.cache);
+  const int64_t base = p.layer_off + (int64_t)h * p.head_stride;
+  const T* kc = reinterpret_cast<const T*>(p.k_cur) + ((int64_t)b * p.Hkv + h) * D;
+  const T* vc = reinterpret_cast<const T*>(p.v_cur) + ((int64_t)b * p.Hkv + h) * D;
+  if (s == 0 && warp == 0 && lane < 2 * CH) {
+    // the new key / value of this sequence and kv head go into the cache
+    const int which = lane / CH, c = lane % CH;
+    T* dst = reinterpret_cast<T*>(p.cache) + base + (row0 + pos_new) * p.row_stride + which * p.kv_stride + c * 8;
+    *reinterpret_cast<uint4*>(dst) = ld_stream16((which ? vc : kc) + c * 8);
+  }
+  // A fragments of Q (rows >= G and rows 8..15 are zero)
+  uint32_t qa[KS][2];
+  {
+    const T* q = reinterpret_cast<const T*>(p.q) + ((int64_t)b * p.Hq + (int64_t)h * G + r) * D;
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+      qa[kk][0] = r < G ? *reinterpret_cast<const uint32_t*>(q + kk * 16 + cq * 2) : 0u;
+      qa[kk][1] = r < G ? *reinterpret_cast<const uint32_t*>(q + kk * 16 + 8 + cq * 2) : 0u;
+    }
+  }
+  float o[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m_run = -INFINITY, l_run = 0.f;           // of row r; l_run is this lane's share of the row sum
+
+  const int64_t p_begin = (int64_t)s * p.chunk;
+  const int64_t p_end = min(kvlen, p_begin + p.chunk);
+  const int64_t n_pos = p_end > p_begin ? p_end - p_begin : 0;
+  const int tiles_cta = (int)((n_pos + kMmaTile - 1) / kMmaTile);
+  const int my_tiles = tiles_cta > warp ? (tiles_cta - warp + kAttnWarps - 1) / kAttnWarps : 0;
+  const uint32_t ring = smem_u32_attn(attn_smem) + warp * (kMmaStages * 2 * TILEB);
+
+  auto issue = [&](int i) {      // tile i of this warp -> stage i % kMmaStages
+    const int64_t pos0 = p_begin + ((int64_t)warp + (int64_t)i * kAttnWarps) * kMmaTile;
+    const uint32_t st = ring + (i % kMmaStages) * (2 * TILEB);
+#pragma unroll
+    for (int j = 0; j < kMmaTile * CH / 32; ++j) {
+      const int c = lane + 32 * j;
+      const int row = c / CH, ch = c % CH;
+      const int64_t pos = pos0 + row;
+      const uint32_t dst = st + row * ROWB + ((ch ^ (row & 7)) << 4);
+      const bool valid = pos < p_end;
+      const T* ksrc = pos == pos_new ? kc + ch * 8 : cache + base + (row0 + (valid ? pos : p_begin)) * p.row_stride + ch * 8;
+      const T* vsrc = pos == pos_new ? vc + ch * 8 : ksrc + p.kv_stride;
+      cp_async16(dst, ksrc, valid ? 16 : 0);
+      cp_async16(dst + TILEB, vsrc, valid ? 16 : 0);
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < kMmaStages - 1; ++i) {
+    if (i < my_tiles) issue(i);
+    cp_async_commit();
+  }
+  for (int i = 0; i < my_tiles; ++i) {
+    cp_async_wait<kMmaStages - 2>();
+    __syncwarp();                                   // tile i has landed; every lane is done with tile i - 1
+    if (i + kMmaStages - 1 < my_tiles) issue(i + kMmaStages - 1);   // into the stage tile i - 1 used
+    cp_async_commit();
+    const int64_t pos0 = p_begin + ((int64_t)warp + (int64_t)i * kAttnWarps) * kMmaTile;
+    const uint32_t st = ring + (i % kMmaStages) * (2 * TILEB);
+    // S = Q K^T for the tile's 16 positions (two n-tiles of 8)
+    float sc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
+    {
+      const int mi = lane >> 3;
+      const int row = 8 * (mi >> 1) + (lane & 7);
+#pragma unroll
+      for (int kk = 0; kk < KS; ++kk) {
+        uint32_t kb[4];
+        const int ch = 2 * kk + (mi & 1);
+        ldmatrix_x4(st + row * ROWB + ((ch ^ (row & 7)) << 4), kb);
+        mma16816<T>(sc[0], qa[kk][0], 0u, qa[kk][1], 0u, kb[0], kb[1]);
+        mma16816<T>(sc[1], qa[kk][0], 0u, qa[kk][1], 0u, kb[2], kb[3]);
+      }
+    }
+    // online softmax of row r over the tile (this lane holds positions 8j + 2cq, +1)
+    float pr[2][2];
+    float tmax = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const bool valid = pos0 + 8 * j + 2 * cq + e < p_end;
+        pr[j][e] = valid ? sc[j][e] * p.scale : -INFINITY;
+        tmax = fmaxf(tmax, pr[j][e]);
+      }
+    }
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, 2));
+    const float m_new = fmaxf(m_run, tmax);        // finite: every tile holds at least one position
+    const float corr = __expf(m_run - m_new);
+    float psum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        pr[j][e] = __expf(pr[j][e] - m_new);
+        psum += pr[j][e];
+      }
+    }
+    l_run = l_run * corr + psum;
+    m_run = m_new;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { o[j][0] *= corr; o[j][1] *= corr; }
+    // O += P V: the S fragments are the A fragments of P (rows of padding stay zero)
+    const uint32_t pa0 = r < G ? pack2<T>(pr[0][0], pr[0][1]) : 0u;
+    const uint32_t pa2 = r < G ? pack2<T>(pr[1][0], pr[1][1]) : 0u;
+    {
+      const int mi = lane >> 3;
+      const int row = 8 * (mi & 1) + (lane & 7);
+#pragma unroll
+      for (int jn = 0; jn < NT; jn += 2) {
+        uint32_t vb[4];
+        const int ch = jn + (mi >> 1);
+        ldmatrix_x4_trans(st + TILEB + row * ROWB + ((ch ^ (row & 7)) << 4), vb);
+        mma16816<T>(o[jn], pa0, 0u, pa2, 0u, vb[0], vb[1]);
+        mma16816<T>(o[jn + 1], pa0, 0u, pa2, 0u, vb[2], vb[3]);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  // the row sum of this warp, then the warps of the CTA meet in shared memory (the ring is free now)
+  l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 1);
+  l_run += __shfl_xor_sync(0xFFFFFFFFu, l_run, 2);
+  __syncthreads();
+  float* sm_acc = reinterpret_cast<float*>(attn_smem);          // [warps][kGroupLimit][D]
+  if (r < G) {
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      float* dst = sm_acc + ((size_t)warp * kGroupLimit + r) * D + 8 * j + 2 * cq;
+      dst[0] = o[j][0];
+      dst[1] = o[j][1];
+    }
+    if (cq == 0) {
+      sm_m[warp][r] = m_run;
+      sm_l[warp][r] = l_run;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+    const int g = i / D, d = i - g * D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, sm_m[w][g]);
+    float ll = 0.f, a = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float c = sm_m[w][g] == -INFINITY ? 0.f : __expf(sm_m[w][g] - mm);
+      ll += sm_l[w][g] * c;
+      a += sm_acc[((size_t)w * kGroupLimit + g) * D + d] * c;
+    }
+    if (p.splits == 1) {
+      reinterpret_cast<T*>(p.out)[((int64_t)b * p.Hq + (int64_t)h * G + g) * D + d] = Elem<T>::from_f(a / ll);
+    } else {
+      float* dst = p.part + ((((int64_t)b * p.Hkv + h) * p.splits + s) * G + g) * (D + 2);
+      dst[d] = a;
+      if (d == 0) {
+        dst[D] = mm;
+        dst[D + 1] = ll;
+      }
+    }
+  }
+}
+
 // out[b, head, :] = sum over slices of acc * exp(max - global max) / sum of the same for l
 template <typename T>
 __global__ void decode_attention_merge_kernel(const float* part, T* __restrict__ out, int Hq, int Hkv,
@@ -239,11 +480,14 @@ __global__ void decode_attention_merge_kernel(const float* part, T* __restrict__
   }
 }
 
-int pick_splits(int64_t B, int Hkv, int64_t max_kvlen) {
-  // enough CTAs for twelve 4-warp CTAs per SM (the kernel hides latency with warps, not
-  // with bytes in flight per warp), slices of at least 64 positions
-  const int64_t want = ceil_div(12 * (int64_t)sm_count(), B * Hkv);
-  int64_t cap = ceil_div(max_kvlen, 64);
+std::atomic<int> g_variant{0};   // 0: tensor-core kernel, 1: CUDA-core kernel
+
+int pick_splits(int64_t B, int Hkv, int64_t max_kvlen, int variant) {
+  // CUDA-core kernel: enough CTAs for twelve 4-warp CTAs per SM (it hides latency with warps,
+  // not with bytes in flight per warp), slices of at least 64 positions.  Tensor-core kernel:
+  // two CTAs per SM with a ring of tiles per warp; three waves, at least four tiles per warp.
+  const int64_t want = ceil_div((variant == 1 ? 12 : 6) * (int64_t)sm_count(), B * Hkv);
+  int64_t cap = ceil_div(max_kvlen, variant == 1 ? 64 : 4 * kAttnWarps * kMmaTile);
   int64_t s = want < cap ? want : cap;
   if (s < 1) s = 1;
   if (s > 64) s = 64;
@@ -252,10 +496,14 @@ int pick_splits(int64_t B, int Hkv, int64_t max_kvlen) {
 
 }  // namespace
 
+int decode_attention_set_variant(int variant) {
+  return g_variant.exchange(variant == 1 ? 1 : 0, std::memory_order_relaxed);
+}
+
 size_t decode_attention_workspace_bytes(int64_t B, int Hq, int Hkv, int D, int64_t max_kvlen) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || max_kvlen <= 0) return 0;
-  const int splits = pick_splits(B, Hkv, max_kvlen);
-  return 256 + (size_t)B * Hq * splits * (D + 2) * sizeof(float);
+  const int a = pick_splits(B, Hkv, max_kvlen, 0), b = pick_splits(B, Hkv, max_kvlen, 1);
+  return 256 + (size_t)B * Hq * (a > b ? a : b) * (D + 2) * sizeof(float);
 }
 
 int launch_decode_attention(const void* q, const void* k_cur, const void* v_cur, void* cache,
@@ -284,7 +532,8 @@ int launch_decode_attention(const void* q, const void* k_cur, const void* v_cur,
   p.part = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + 256);
   p.layer_off = layer_off; p.row_stride = row_stride; p.kv_stride = kv_stride; p.head_stride = head_stride;
   p.B = (int)B; p.Hq = Hq; p.Hkv = Hkv;
-  p.splits = pick_splits(B, Hkv, max_kvlen);
+  const int variant = g_variant.load(std::memory_order_relaxed);
+  p.splits = pick_splits(B, Hkv, max_kvlen, variant);
   p.chunk = (int)ceil_div(max_kvlen, p.splits);
   p.scale = 1.0f / sqrtf((float)D);
   const dim3 grid((unsigned)B, (unsigned)Hkv, (unsigned)p.splits);
@@ -298,8 +547,17 @@ int launch_decode_attention(const void* q, const void* k_cur, const void* v_cur,
                         : (const void*)decode_attention_kernel<__half, 64, GM>)
   if (G == 1) { PMX_ATTN_PICK(1); } else if (G == 2) { PMX_ATTN_PICK(2); } else if (G <= 4) { PMX_ATTN_PICK(4); } else { PMX_ATTN_PICK(8); }
 #undef PMX_ATTN_PICK
+  size_t smem = 0;
+  if (variant == 0) {
+    kern = D == 128 ? (bf ? (const void*)decode_attention_mma_kernel<__nv_bfloat16, 128>
+                          : (const void*)decode_attention_mma_kernel<__half, 128>)
+                    : (bf ? (const void*)decode_attention_mma_kernel<__nv_bfloat16, 64>
+                          : (const void*)decode_attention_mma_kernel<__half, 64>);
+    smem = (size_t)kAttnWarps * kMmaStages * 2 * kMmaTile * D * 2;
+    PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  }
   void* args[] = {(void*)&p};
-  int st = launch_pdl(kern, grid, dim3(kAttnWarps * 32), 0, s, args);
+  int st = launch_pdl(kern, grid, dim3(kAttnWarps * 32), smem, s, args);
   if (st != PMX_OK || p.splits == 1) return st;
   const dim3 mgrid((unsigned)B, (unsigned)Hq);
   if (bf)

@@ -1,6 +1,8 @@
 // extern "C" entry points declared in include/pmx_moe.h: argument checks,
 // kernel choice, error text.  No torch types, no allocation, no host sync.
 #include <atomic>
+#include <mutex>
+#include <unordered_set>
 #include <cstdarg>
 #include <cstdio>
 
@@ -12,10 +14,33 @@ namespace {
 thread_local char g_error[512] = "";
 std::atomic<long long> g_launches{0};
 std::atomic<int> g_pdl{1};
-std::atomic<int> g_l2_prefetch{8};
+std::atomic<int> g_l2_prefetch{0};
+std::mutex g_stamp_mutex;
+unsigned long long* g_stamp_buf = nullptr;
+int g_stamp_slots = 0, g_stamp_used = 0;
+int g_stamp_kernel[256];
+}
+
+// Every kernel asks for the largest shared-memory carve-out, also those that need next to
+// none: an SM whose L1 / shared-memory split was set for a small kernel cannot take a CTA of
+// an expert GEMM (200 KB) until it has drained, so the GEMM CTAs that should start beside
+// the CTAs of the kernel in front (programmatic launch) would wait for them to leave --
+// seen on B200 as GEMM CTAs entering 8 us late on exactly the SMs the router occupied.
+static int prefer_max_shared(const void* kern) {
+  static std::mutex m;
+  static std::unordered_set<const void*> done;
+  std::lock_guard<std::mutex> lock(m);
+  if (done.count(kern)) return PMX_OK;
+  PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+  done.insert(kern);
+  return PMX_OK;
 }
 
 int launch_pdl(const void* kern, dim3 grid, dim3 block, size_t smem, cudaStream_t s, void** args) {
+  {
+    const int st = prefer_max_shared(kern);
+    if (st != PMX_OK) return st;
+  }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -29,6 +54,13 @@ int launch_pdl(const void* kern, dim3 grid, dim3 block, size_t smem, cudaStream_
   PMX_CUDA_OK(cudaLaunchKernelExC(&cfg, kern, args));
   count_launches(1);
   return PMX_OK;
+}
+
+unsigned long long* next_stamp_slot(int kernel_id) {
+  std::lock_guard<std::mutex> lock(g_stamp_mutex);
+  if (!g_stamp_buf || g_stamp_used >= g_stamp_slots) return nullptr;
+  g_stamp_kernel[g_stamp_used] = kernel_id;
+  return g_stamp_buf + (size_t)(g_stamp_used++) * kStampCtas * kStampWords;
 }
 
 int default_l2_prefetch() { return g_l2_prefetch.load(std::memory_order_relaxed); }
@@ -251,6 +283,21 @@ int pmx_moe_dense_gate_up(const void* x, const int64_t* invert_permutation, cons
                               workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+int pmx_moe_set_stamp_buffer(void* buffer, size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_stamp_mutex);
+  const size_t slot = (size_t)kStampCtas * kStampWords * sizeof(unsigned long long);
+  g_stamp_buf = reinterpret_cast<unsigned long long*>(buffer);
+  g_stamp_slots = buffer ? (int)(bytes / slot < 256 ? bytes / slot : 256) : 0;
+  g_stamp_used = 0;
+  return g_stamp_slots;
+}
+
+int pmx_moe_stamp_slots(int32_t* kernel_ids, int32_t max_ids) {
+  std::lock_guard<std::mutex> lock(g_stamp_mutex);
+  for (int i = 0; i < g_stamp_used && i < max_ids; ++i) kernel_ids[i] = g_stamp_kernel[i];
+  return g_stamp_used;
+}
+
 int pmx_moe_set_l2_prefetch(int32_t kblocks) {
   return g_l2_prefetch.exchange(kblocks < 0 ? 0 : (kblocks > 64 ? 64 : kblocks), std::memory_order_relaxed);
 }
@@ -309,6 +356,8 @@ int pmx_moe_reduce(const void* y, const void* expert_weights, const int64_t* inv
                    void* out, int64_t T, int32_t k, int64_t N, int32_t dtype, void* stream) {
   return launch_reduce(y, expert_weights, invert_permutation, out, T, k, N, dtype, (cudaStream_t)stream);
 }
+
+int pmx_decode_cache_attention_set_kernel(int32_t kernel) { return decode_attention_set_variant(kernel); }
 
 size_t pmx_decode_cache_attention_workspace_bytes(int64_t B, int32_t num_heads, int32_t num_kv_heads,
                                                   int32_t head_dim, int64_t max_kvlen) {

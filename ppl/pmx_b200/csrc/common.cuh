@@ -155,6 +155,7 @@ int launch_reduce_allreduce_emulated(const void* const* y, const void* const* w,
                                      long long wait_limit_ns, cudaStream_t s);
 int reduce_allreduce_check(void* my_buffer, int out[4], cudaStream_t s);
 int reduce_allreduce_phases(const void* my_buffer, unsigned long long out[8], cudaStream_t s);
+int decode_attention_set_variant(int variant);
 size_t decode_attention_workspace_bytes(int64_t B, int Hq, int Hkv, int D, int64_t max_kvlen);
 int launch_decode_attention(const void* q, const void* k_cur, const void* v_cur, void* cache,
                             const int64_t* cachestarts, const int64_t* start_pos, void* out, int64_t B, int Hq,
@@ -185,7 +186,12 @@ struct TcPlan {
   int w_pitch;     // rows between experts in w (0: N)
   int l2_ahead;    // k-blocks of weight tiles requested into L2 in front of the ring
 };
-int default_l2_prefetch();   // process-wide default for l2_ahead (pmx_moe_set_l2_prefetch)
+int default_l2_prefetch();
+// Diagnostic time stamps (pmx_moe_set_stamp_buffer): the next slot of kStampCtas x kStampWords
+// %globaltimer values for one launch of an instrumented kernel, or null when switched off.
+constexpr int kStampWords = 8;
+constexpr int kStampCtas = 160;
+unsigned long long* next_stamp_slot(int kernel_id);   // process-wide default for l2_ahead (pmx_moe_set_l2_prefetch)
 // Fills `plan` for the tensor-core kernel or returns false when the shape is
 // outside what it covers (the caller then uses the CUDA-core kernel).
 bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogue,

@@ -66,6 +66,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   // programmatic dependent launch it overlaps the tail of the kernel in front.
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
+    stamp(p.stamps, 0);
     for (int i = 0; i < p.stages; ++i) {
       mbar_init(&sh->full[i], 1);
       mbar_init(&sh->empty[i], 1);
@@ -158,6 +159,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
   const int total_items = s_prefix[p.E];
+  if (threadIdx.x == 0) stamp(p.stamps, 1);
 
   if (warp == 0) {
     // ========================= TMA producer =================================
@@ -260,6 +262,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       WorkIter work;
       work.init(p, total_items);
       bool ok = true;
+      bool first_tile = true;
       if (MODE == 1 && !DENSE && p.prefetch) {
         // stages the producer filled for an item this CTA does not have: wait for the copies, hand them back
         for (int d = sh->discard; d > 0 && ok; --d) {
@@ -277,6 +280,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         for (int kb = it.kb0; kb < it.kb1; ++kb) {
           ok = wait_barrier(&sh->full[stage], phase, sh, p.status, 2, item);
           if (!ok) break;
+          if (p.stamps && first_tile) { stamp(p.stamps, 2); first_tile = false; }
           tc_fence_after();
           const uint32_t tok_addr = smem_base + stage * stage_bytes;
           const uint32_t w_addr = tok_addr + tok_bytes;
@@ -300,6 +304,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
         umma_commit(&sh->acc_full[acc]);   // accumulator complete
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
+      stamp(p.stamps, 3);
     }
   } else {
     // ========================= epilogue (warps 2..5) ========================
@@ -321,6 +326,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       pdl_wait();   // the routing (invert_permutation, expert_offset) is complete from here on
       if (blockIdx.x == 0 && warp == 2 && lane < 4) p.status[lane] = 0;
     }
+    if (warp == 2 && lane == 0) stamp(p.stamps, 4);
     while (work.next(p, total_items, s_off, s_prefix, it, item)) {
       if (DENSE) {
         it.row0 = 0;
@@ -347,6 +353,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       ok = wait_barrier(&sh->acc_full[acc], acc_phase, sh, p.status, 3, item);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
+      if (warp == 2 && lane == 0) stamp(p.stamps, 7);   // (last item: its accumulator is complete)
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * kAccStride + (static_cast<uint32_t>(q * 32) << 16);
       if (p.stream_k && it.kb0 > 0) {
@@ -493,6 +500,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
+    if (warp == 2 && lane == 0) stamp(p.stamps, 5);
   }
 
   // ---- common exit ------------------------------------------------------------
@@ -502,6 +510,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) stamp(p.stamps, 6);
 }
 
 // ----------------------------------------------------------------------------- host side
@@ -685,6 +694,7 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
                n_out >= 128;
   p.units_per_panel = (int)(n_out / 8);
   p.l2_ahead = plan.kernel == PMX_GEMM_TC_WEIGHTS_M && !plan.stream_k ? plan.l2_ahead : 0;
+  p.stamps = next_stamp_slot(2);
   p.kblocks = (int)ceil_div(K, kBlockK);
   p.split_k = plan.split_k;
   p.kb_per_split = (int)ceil_div(p.kblocks, plan.split_k);
@@ -786,6 +796,7 @@ int launch_gemm_tc_dense(const void* x, const int64_t* inv, const int64_t* off, 
   p.balanced = 1;
   p.units_per_panel = (int)(n_out / 8);
   p.l2_ahead = default_l2_prefetch();
+  p.stamps = next_stamp_slot(3);
   p.kblocks = (int)ceil_div(K, kBlockK);
   p.split_k = 1;
   p.kb_per_split = p.kblocks;

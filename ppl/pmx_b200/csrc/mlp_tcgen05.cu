@@ -50,6 +50,7 @@ struct MlpParams {
   int f1, f2;           // work items per expert: ceil(I/128), ceil(H/256)
   int kb1, kb2;         // k-blocks per item: ceil(H/64), ceil(I/64)
   int g1, g2;           // CTAs that take phase-1 / phase-2 items
+  unsigned long long* stamps;   // diagnostic: [cta][8] %globaltimer values, or null
   int l2_ahead;         // weight tiles are requested into L2 this many k-blocks in front of the ring
   float beta;
 };
@@ -120,6 +121,7 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   // ---- set-up: nothing here touches memory another kernel writes ---------------
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
+    stamp(p.stamps, 0);
     for (int i = 0; i < p.stages; ++i) {
       mbar_init(&sh->full[i], 1);
       mbar_init(&sh->empty[i], 1);
@@ -144,6 +146,7 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
   const uint32_t smem_base = smem_u32(smem);
+  if (threadIdx.x == 0) stamp(p.stamps, 1);
   const unsigned int tiles_done = 4u * (unsigned int)p.f1;   // value of done[e] once h of expert e is complete
 
   if (warp == 0) {
@@ -270,6 +273,7 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       Cursor c;
       c.init(p);
       bool ok = true;
+      bool first_tile = true, first_down = true;
       while (ok && c.phase != 3) {
         ok = wait_barrier(&sh->acc_empty[acc], acc_phase ^ 1u, sh, p.status, 1, c.item);
         if (!ok) break;
@@ -279,6 +283,10 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         for (int kb = 0; kb < nkb; ++kb) {
           ok = wait_barrier(&sh->full[stage], phase, sh, p.status, 2, c.item);
           if (!ok) break;
+          if (p.stamps) {
+            if (first_tile) { stamp(p.stamps, 2); first_tile = false; }
+            if (c.phase == 2 && kb == 0 && first_down) { stamp(p.stamps, 7); first_down = false; }   // first tile of h arrived
+          }
           tc_fence_after();
           const uint32_t tok_addr = smem_base + stage * stage_bytes;
           const uint32_t w_addr = tok_addr + tok_bytes;
@@ -298,6 +306,7 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         c.next_item();
       }
+      stamp(p.stamps, 3);
     }
   } else {
     // ========================= epilogue (warps 2..5) ========================
@@ -311,6 +320,7 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     int map_expert = -1;
     pdl_wait();   // the routing (invert_permutation, expert_offset) is complete from here on
     if (blockIdx.x == 0 && warp == 2 && lane < 4) p.status[lane] = 0;
+    if (warp == 2 && lane == 0) stamp(p.stamps, 4);
     while (c.phase != 3) {
       const bool gate_up = c.phase == 1;
       const int per = gate_up ? p.f1 : p.f2;
@@ -382,6 +392,7 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       c.next_item();
     }
+    if (warp == 2 && lane == 0) stamp(p.stamps, 5);
   }
 
   // ---- common exit ------------------------------------------------------------
@@ -391,6 +402,7 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (threadIdx.x == 0) stamp(p.stamps, 6);
   if (threadIdx.x == 64) {
     // the last CTA to leave puts the counters back to zero for the next launch
     __threadfence();
@@ -453,6 +465,7 @@ int launch_dense_mlp(const void* x, const int64_t* inv, const int64_t* off, cons
   p.g2 = full_round_grid(E * p.f2, cap);
   p.beta = beta;
   p.l2_ahead = default_l2_prefetch();
+  p.stamps = next_stamp_slot(4);
   const size_t stage = (size_t)(p.tile_tok + 256) * 128;
   const size_t fixed = 1024 + sizeof(Shared) + kRowMapBytes;
   // 24 KB of every SM's shared memory stay free, so that a CTA of the routing kernel and a

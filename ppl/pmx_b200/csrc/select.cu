@@ -393,13 +393,20 @@ struct NormArgs {
   float eps;
 };
 
+__device__ __forceinline__ unsigned long long route_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
 template <typename T, bool NORM>
 __global__ void __launch_bounds__(256)
 route_select_kernel(const T* x, const T* wr, int Tn, int64_t H, int E, int k,
                     int tpb, T* __restrict__ scores, T* __restrict__ xp, T* __restrict__ weights,
                     int64_t* __restrict__ inv, int64_t* __restrict__ expert_offset,
                     unsigned long long* __restrict__ masks, unsigned int* __restrict__ counter,
-                    int* __restrict__ status, NormArgs norm, unsigned long long wait_ns) {
+                    int* __restrict__ status, NormArgs norm, unsigned long long wait_ns,
+                    unsigned long long* stamps) {
   extern __shared__ unsigned int sm_rs[];
   const int groups = (Tn + 31) / 32;
   unsigned int* ballots = sm_rs;                                        // [groups][E]
@@ -419,10 +426,12 @@ route_select_kernel(const T* x, const T* wr, int Tn, int64_t H, int E, int k,
   constexpr int V = kVec<T>;
   const int chunks = (int)(H / V);
   if (threadIdx.x == 0) s_abort = 0;
+  if (stamps && threadIdx.x == 0 && blockIdx.x < 160) stamps[blockIdx.x * 8 + 0] = route_ns();
   // The dependent kernel may read x while this one runs (the dense gate/up projection does):
   // it is released only after this kernel's own predecessors, which produced x, are complete.
   pdl_wait();   // x (and skip) come from the kernel in front of this one
   pdl_launch_dependents();
+  if (stamps && threadIdx.x == 0 && blockIdx.x < 160) stamps[blockIdx.x * 8 + 1] = route_ns();
 
   // A0. (NORM) normalise my tokens into shared memory
   if (NORM) {
@@ -558,6 +567,7 @@ route_select_kernel(const T* x, const T* wr, int Tn, int64_t H, int E, int k,
   }
   __syncthreads();
   if (s_abort) return;
+  if (stamps && threadIdx.x == 0 && blockIdx.x < 160) stamps[blockIdx.x * 8 + 2] = route_ns();
 
   // B. ballots over all tokens from the masks
   for (int g = warp; g < groups; g += nwarps) {
@@ -598,6 +608,7 @@ route_select_kernel(const T* x, const T* wr, int Tn, int64_t H, int E, int k,
     inv[(int64_t)t0 * k + i] = p;
   }
   __syncthreads();
+  if (stamps && threadIdx.x == 0 && blockIdx.x < 160) stamps[blockIdx.x * 8 + 6] = route_ns();
   // C. gather my tokens (not wanted by callers that feed the un-permuted tokens to the experts)
   if (xp == nullptr) return;
   const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)t0 * H);
@@ -937,9 +948,10 @@ int launch_route_select_impl(const void* x, const void* wr, void* scores, void* 
   unsigned long long* masks = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(ws) + 64);
   int Tn = (int)T;
   unsigned long long wait_ns = 1000000000ull;   // 1 s
+  unsigned long long* stamps = next_stamp_slot(1);
   void* args[] = {(void*)&x, (void*)&wr, (void*)&Tn, (void*)&H, (void*)&E, (void*)&k, (void*)&g.tpb, (void*)&scores,
                   (void*)&xp, (void*)&w, (void*)&inv, (void*)&off, (void*)&masks, (void*)&counter, (void*)&status,
-                  (void*)&norm, (void*)&wait_ns};
+                  (void*)&norm, (void*)&wait_ns, (void*)&stamps};
   const void* kern = nullptr;
   switch (dtype) {
     case PMX_DTYPE_F16: kern = with_norm ? (const void*)route_select_kernel<__half, true> : (const void*)route_select_kernel<__half, false>; break;

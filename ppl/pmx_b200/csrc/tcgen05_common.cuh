@@ -41,6 +41,7 @@ struct Params {
                         // whole panels, cut into pieces of at most 128 rows in 8-row units
                         // (feat_tiles is 1 then: a work "item" of the prefix table is a panel)
   int units_per_panel;  // n_out / 8
+  unsigned long long* stamps;   // diagnostic: [cta][8] %globaltimer values, or null
   int l2_ahead;         // weight rows on MMA-M: the producer asks for the weight tiles of the k-block this
                         // many rounds in front of the ring to be brought into L2 (0: no prefetch)
 };
@@ -85,6 +86,9 @@ __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
+}
+__device__ __forceinline__ void stamp(unsigned long long* stamps, int word) {
+  if (stamps && blockIdx.x < 160) stamps[blockIdx.x * 8 + word] = global_ns();
 }
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

@@ -169,7 +169,8 @@ class MoeFeedForward(nn.Module):
     def __init__(self, hidden_dim: int, intermediate_dim: int, num_experts: int,
                  num_experts_per_token: int, proc_group=None, linear_bias_term: bool = False,
                  fused: bool = True, peer_reduce_tokens: int = 0, peer_algorithm: str = "auto",
-                 overlap_chunks: int = 1, dense_decode: bool = True, one_launch_experts: bool = True) -> None:
+                 overlap_chunks: int = 1, dense_decode: bool = True, one_launch_experts: bool = True,
+                 token_microbatches: int = 1) -> None:
         super().__init__()
         self.num_experts = num_experts
         self.num_experts_per_token = num_experts_per_token
@@ -191,6 +192,13 @@ class MoeFeedForward(nn.Module):
         # ... and, where it is covered, both expert projections in one launch
         self.one_launch_experts = one_launch_experts
         self._mlp_ws = None
+        # tensor-parallel batches too large for the peer kernel: the batch is cut into this many
+        # runs of tokens; the all-reduce of one run (NCCL, on the process group's own stream)
+        # overlaps the whole block of the next run.  Routing is per token, so the result is the
+        # same as for the whole batch.
+        self.token_microbatches = token_microbatches
+        self._defer_allreduce = False
+        self._pending = []
         self._peer = None
         self._last_workspaces = ()     # status words of the last step's expert GEMMs, for check()
         self.gate = Linear(hidden_dim, num_experts, bias_term=False)
@@ -221,6 +229,12 @@ class MoeFeedForward(nn.Module):
         E, k = self.num_experts, self.num_experts_per_token
         routed = None
         tokens = x.numel() // x.shape[-1] if x.shape[-1] else 0
+        n_mb = self.token_microbatches
+        if (n_mb > 1 and self.fused and not self._defer_allreduce
+                and _world(self.proc_group) > 1 and tokens % n_mb == 0
+                and tokens // n_mb * self.hidden_dim * x.element_size() >= OVERLAP_MIN_BYTES
+                and not (self.peer_reduce_tokens >= tokens and self._peer_fits(tokens, x.dtype))):
+            return self._forward_microbatched(x, router_logits, n_mb)
         if (router_logits is None and self.fused and self.dense_decode and tokens > 0
                 and dense_gate_up_covers(tokens, self.wu.weight, k)):
             # decode-size batch with (almost surely) every expert in use: the gate/up projection
@@ -298,8 +312,28 @@ class MoeFeedForward(nn.Module):
                     return self._peer.combine_allreduce(y, expert_weights, invert_permutation, k)
             out = OPMX.moe_reduce(y.view(*expert_weights.shape, -1), expert_weights, invert_permutation, k)
             if world > 1:
-                dist.all_reduce(out, group=self.proc_group)
+                if self._defer_allreduce:
+                    self._pending.append(dist.all_reduce(out, group=self.proc_group, async_op=True))
+                else:
+                    dist.all_reduce(out, group=self.proc_group)
         return out
+
+    def _forward_microbatched(self, x: torch.Tensor, router_logits, n_mb: int) -> torch.Tensor:
+        """The block on n_mb runs of tokens, each followed by an asynchronous all-reduce of its
+        result that overlaps the next run's kernels."""
+        flat = x.reshape(-1, self.hidden_dim)
+        logits = router_logits.reshape(flat.shape[0], -1) if router_logits is not None else None
+        step = flat.shape[0] // n_mb
+        self._defer_allreduce, self._pending = True, []
+        try:
+            outs = [self.forward(flat[i * step:(i + 1) * step],
+                                 logits[i * step:(i + 1) * step] if logits is not None else None)
+                    for i in range(n_mb)]
+            for work in self._pending:
+                work.wait()
+        finally:
+            self._defer_allreduce, self._pending = False, []
+        return torch.cat(outs).view(*x.shape[:-1], self.hidden_dim)
 
     def _peer_fits(self, tokens: int, dtype) -> bool:
         from .peer_reduce import ONE_SHOT_LIMIT_BYTES

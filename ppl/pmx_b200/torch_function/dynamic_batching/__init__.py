@@ -20,6 +20,14 @@ from ..._cabi import lib, check, ptr, stream_of, workspace, DTYPE_CODE
 from ..moe import _require_cuda
 
 
+def set_decode_attention_kernel(kind: str) -> str:
+    """Which kernel the decode-step attention runs: "mma" (default; tensor-core products on
+    tiles staged in shared memory) or "simt" (CUDA cores, loads straight into registers).
+    Process-wide; returns the previous choice."""
+    names = ("mma", "simt")
+    return names[lib.pmx_decode_cache_attention_set_kernel(names.index(kind))]
+
+
 def cache_strides(cache: torch.Tensor, cache_layout: int, num_layer: int, layer_idx: int):
     """-> (layer_offset, row_stride, kv_stride, head_stride, total_rows) in elements for the
     four cache layouts of cache_mode 0 (Pipeline.py:80-89 of the Mixtral model):

@@ -18,6 +18,14 @@ def DB():
     return F.dynamic_batching
 
 
+@pytest.fixture(autouse=True, params=["mma", "simt"])
+def attention_kernel(request, DB):
+    """Every test runs once per attention kernel."""
+    old = DB.set_decode_attention_kernel(request.param)
+    yield request.param
+    DB.set_decode_attention_kernel(old)
+
+
 def run_op(DB, q, k, v, cache, cachestarts, start_pos, layout, layers, layer_idx, Hq, Hkv, D):
     B = q.shape[0]
     kvlens = start_pos + 1

@@ -76,12 +76,15 @@ def _worker(rank, world, port, q):
                             bias_u_full[:, sh.I + rank * Il: sh.I + (rank + 1) * Il]], 1)
         ref_b = None
         import ppl.pmx_b200.moe_layers as layers_mod
-        for fused in (True, False, "sliced"):
+        for fused in (True, False, "sliced", "runs"):
             # "sliced": the fused block with the down projection, combine and all-reduce done
-            # per slice of the hidden columns (the all-reduces overlap the next slice's GEMM)
-            layers_mod.OVERLAP_MIN_BYTES = 0 if fused == "sliced" else 1 << 60
+            # per slice of the hidden columns (the all-reduces overlap the next slice's GEMM);
+            # "runs": the block per run of tokens, a run's all-reduce overlapping the next run
+            layers_mod.OVERLAP_MIN_BYTES = 0 if fused in ("sliced", "runs") else 1 << 60
             for with_bias in (False, True):
-                blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, with_bias, fused=bool(fused), overlap_chunks=2)
+                blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, with_bias, fused=bool(fused),
+                                     overlap_chunks=2 if fused == "sliced" else 1,
+                                     token_microbatches=2 if fused == "runs" else 1)
                 u, d = W.make_expert_weights(sh, "cpu", tp_rank=rank, tp_size=world)
                 assert blk.wu.weight.shape == u.shape and blk.w2.weight.shape == d.shape
                 with torch.no_grad():

@@ -38,12 +38,15 @@ def _worker(rank, world, port, q):
             ref = orc.moe_block(f(x), f(wr), f(full_u), f(full_d), sh.E, sh.k, sh.dtype, scores=f(sc),
                                 round_intermediates=False)
             import ppl.pmx_b200.moe_layers as layers_mod
-            for fused, peer in ((True, 0), (False, 0), (True, sh.T), ("sliced", 0)):
+            for fused, peer in ((True, 0), (False, 0), (True, sh.T), ("sliced", 0), ("runs", 0)):
                 # "sliced": down projection + combine + all-reduce per slice of the hidden columns,
-                # the all-reduce of a slice overlapping the GEMM of the next one
-                layers_mod.OVERLAP_MIN_BYTES = 0 if fused == "sliced" else 1 << 60
+                # the all-reduce of a slice overlapping the GEMM of the next one; "runs": the
+                # block per run of tokens, a run's all-reduce overlapping the next run's kernels
+                layers_mod.OVERLAP_MIN_BYTES = 0 if fused in ("sliced", "runs") else 1 << 60
                 blk = MoeFeedForward(sh.H, sh.I, sh.E, sh.k, group, False, fused=bool(fused),
-                                     peer_reduce_tokens=peer, overlap_chunks=2).to(dev, W.TORCH_DTYPE[sh.dtype])
+                                     peer_reduce_tokens=peer, overlap_chunks=2 if fused == "sliced" else 1,
+                                     token_microbatches=2 if fused == "runs" else 1
+                                     ).to(dev, W.TORCH_DTYPE[sh.dtype])
                 u, d = W.make_expert_weights(sh, dev, tp_rank=rank, tp_size=world)
                 xd, scd = x.to(dev), sc.to(dev)
                 with torch.no_grad():
