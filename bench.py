@@ -507,14 +507,15 @@ def measure(ctx, shape, steps, warmup, regions, headline):
         sync_all(ctx)
         plan = ctx.gemm_plan
         from ppl.pmx_b200.torch_function.moe import dense_gate_up_covers, dense_mlp_covers
-        one_launch = False
-        dense = (blk.dense_decode and dense_gate_up_covers(shape.T, blk.wu.weight, k)
+        one_launch = bool(blk.dense_decode and blk.one_launch_experts
+                          and dense_mlp_covers(shape.T, blk.wu.weight, blk.w2.weight, k))
+        dense = (blk.dense_decode and (one_launch or dense_gate_up_covers(shape.T, blk.wu.weight, k))
                  and OPMX.moe_route_select(x_dev, blk.gate.weight, E, k, gather=False) is not None)
+        one_launch = one_launch and dense
         if dense:
             # the step's own kernels: router without the gather, gate/up from the un-permuted tokens
             _, _, ew, inv, off = stage("route_select", lambda: OPMX.moe_route_select(x_dev, blk.gate.weight, E, k,
                                                                                      gather=False))
-            one_launch = blk.one_launch_experts and dense_mlp_covers(shape.T, blk.wu.weight, blk.w2.weight, k)
             if one_launch:
                 # the step's kernel for both projections; the two launches below are timed for comparison
                 stage("experts", lambda: OPMX.moe_dense_mlp(x_dev, inv, off, blk.wu.weight, blk.w2.weight))
@@ -976,6 +977,11 @@ def main():
                     help="N > 1, results too large for the peer kernel: runs of tokens whose all-reduce overlaps "
                          "the next run's kernels")
     ap.add_argument("--stamps-raw", action="store_true", help="with --stamps: also the per-CTA values")
+    ap.add_argument("--mlp-rows", type=int, default=None,
+                    help="one-launch expert kernel: gate (= up) rows per work item of the first projection (64..128)")
+    ap.add_argument("--one-launch-max-tiles", type=int, default=None,
+                    help="largest number of 128-row gate/up tiles (all experts) for which decode batches run both "
+                         "expert projections in one launch (library default 256: the 1/4 shard)")
     ap.add_argument("--no-one-launch", action="store_true",
                     help="decode-size batches on thin shards: gate/up and down projection as two launches")
     ap.add_argument("--overlap-chunks", type=int, default=1,
@@ -1030,6 +1036,11 @@ def main():
     from ppl.pmx_b200 import _cabi
     if args.no_pdl:
         _cabi.lib.pmx_moe_set_programmatic_launch(0)
+    if args.mlp_rows is not None:
+        _cabi.lib.pmx_moe_dense_mlp_set_rows(args.mlp_rows)
+    if args.one_launch_max_tiles is not None:
+        import ppl.pmx_b200.torch_function.moe as moe_mod
+        moe_mod.ONE_LAUNCH_MAX_TILES = args.one_launch_max_tiles
     if args.l2_prefetch is not None:
         _cabi.lib.pmx_moe_set_l2_prefetch(args.l2_prefetch)
     _cabi.lib.pmx_decode_cache_attention_set_kernel(["mma", "simt"].index(args.attention_kernel))

@@ -295,6 +295,10 @@ int pmx_moe_dense_gate_up(const void* x, const int64_t* invert_permutation,
  * leaves it zero, and launches that share it must not overlap on the GPU.
  * pmx_moe_dense_mlp_check reads the status back (synchronising) like
  * pmx_moe_grouped_linear_check and, after a failure, clears the workspace. */
+/* Tuning switch: gate (= up) rows per work item of the first projection, 64..128 in steps of 8;
+ * 0 (default) = chosen per shape so that as many CTAs as possible stream with as deep a ring
+ * as fits.  Process-wide; returns the previous value. */
+int pmx_moe_dense_mlp_set_rows(int32_t rows);
 int pmx_moe_dense_mlp_covers(int64_t T, int64_t N, int64_t H, int32_t E, int32_t k, int32_t dtype);
 size_t pmx_moe_dense_mlp_workspace_bytes(int32_t E);
 int pmx_moe_dense_mlp(const void* x, const int64_t* invert_permutation,

@@ -67,6 +67,7 @@ def _load() -> C.CDLL:
         "pmx_moe_grouped_linear_check": (C.c_int, [vp, C.POINTER(i32 * 4), vp]),
         "pmx_moe_dense_gate_up_covers": (C.c_int, [i64, i64, i64, i32, i32, i32]),
         "pmx_moe_dense_gate_up": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, f32, vp, sz, vp]),
+        "pmx_moe_dense_mlp_set_rows": (C.c_int, [i32]),
         "pmx_moe_dense_mlp_covers": (C.c_int, [i64, i64, i64, i32, i32, i32]),
         "pmx_moe_dense_mlp_workspace_bytes": (sz, [i32]),
         "pmx_moe_dense_mlp": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, i32, i32, i32, f32, vp, sz, vp]),

@@ -302,6 +302,8 @@ int pmx_moe_set_l2_prefetch(int32_t kblocks) {
   return g_l2_prefetch.exchange(kblocks < 0 ? 0 : (kblocks > 64 ? 64 : kblocks), std::memory_order_relaxed);
 }
 
+int pmx_moe_dense_mlp_set_rows(int32_t rows) { return dense_mlp_set_rows(rows); }
+
 int pmx_moe_dense_mlp_covers(int64_t T, int64_t N, int64_t H, int32_t E, int32_t k, int32_t dtype) {
   return dense_mlp_covers(T, N, H, E, k, dtype) ? 1 : 0;
 }

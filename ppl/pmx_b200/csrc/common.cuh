@@ -208,6 +208,7 @@ int launch_gemm_tc_dense(const void* x, const int64_t* inv, const int64_t* off, 
                          void* h, int64_t T, int64_t N, int64_t K, int E, int k, int dtype, float beta, void* ws,
                          size_t ws_bytes, cudaStream_t s);
 
+int dense_mlp_set_rows(int rows);
 bool dense_mlp_covers(int64_t T, int64_t N, int64_t H, int E, int k, int dtype);
 size_t dense_mlp_workspace_bytes(int E);
 int launch_dense_mlp(const void* x, const int64_t* inv, const int64_t* off, const void* wu, const void* w2, void* h,

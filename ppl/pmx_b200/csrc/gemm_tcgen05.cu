@@ -474,23 +474,37 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
           bg = Elem<T>::to_f(bias[(int64_t)it.e * p.w_pitch + f]);
           if (SWIGLU) bu = Elem<T>::to_f(bias[(int64_t)it.e * p.w_pitch + p.n_out + f]);
         }
-        for (int c = 0; c < tt; c += 16) {
+        // up to 32 token columns per round: their tensor-memory loads are all in flight before
+        // the one wait (a tcgen05.ld round trip costs several hundred ns).  Not more: the
+        // registers of 64 columns would keep a CTA of this kernel from sharing an SM with a
+        // CTA of the routing kernel (two warps of each per sub-partition's register file).
+        for (int c = 0; c < tt; c += 32) {
           if (it.row0 + c >= it.row_end || q * 32 >= it.fn) break;  // same for the whole warp
-          float g[16], u[16];
+          float g[2][16], u[2][16];
           __syncwarp();
-          tmem_ld16(taddr + c, g);
-          if (SWIGLU) tmem_ld16(taddr + tt + c, u);
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            if (c + ch * 16 < tt && it.row0 + c + ch * 16 < it.row_end) {
+              tmem_ld16(taddr + c + ch * 16, g[ch]);
+              if (SWIGLU) tmem_ld16(taddr + tt + c + ch * 16, u[ch]);
+            }
+          }
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int row = DENSE ? s_rowmap[q * 128 + c + i] : it.row0 + c + i;
-            if ((DENSE ? row >= 0 : row < it.row_end) && f_ok) {
-              float v = g[i] + bg;
-              if (SWIGLU) v = swiglu_f(v, u[i] + bu, p.beta);
-              if (partial)
-                yp[((int64_t)it.ks * p.M + row) * p.n_out + f] = v;
-              else
-                y[(int64_t)row * p.n_out + f] = Elem<T>::from_f(v);
+          for (int ch = 0; ch < 2; ++ch) {
+            if (c + ch * 16 < tt && it.row0 + c + ch * 16 < it.row_end) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const int row = DENSE ? s_rowmap[q * 128 + c + ch * 16 + i] : it.row0 + c + ch * 16 + i;
+                if ((DENSE ? row >= 0 : row < it.row_end) && f_ok) {
+                  float v = g[ch][i] + bg;
+                  if (SWIGLU) v = swiglu_f(v, u[ch][i] + bu, p.beta);
+                  if (partial)
+                    yp[((int64_t)it.ks * p.M + row) * p.n_out + f] = v;
+                  else
+                    y[(int64_t)row * p.n_out + f] = Elem<T>::from_f(v);
+                }
+              }
             }
           }
         }

@@ -27,6 +27,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -35,6 +36,8 @@ namespace pmx {
 namespace {
 
 #include "tcgen05_common.cuh"
+
+constexpr int kMlpMaxTokens = 64;   // tokens on MMA-N; the epilogue keeps all their accumulator columns in registers
 
 struct MlpParams {
   const int64_t* off;   // [E+1]
@@ -46,8 +49,11 @@ struct MlpParams {
   int T, E, k;
   int I, H;             // this shard's intermediate features, hidden features
   int tile_tok;         // tokens on MMA-N: T rounded up to 16
-  int stages;
-  int f1, f2;           // work items per expert: ceil(I/128), ceil(H/256)
+  int r1;               // phase 1: gate rows (= up rows) per work item, a multiple of 8, <= 128
+  int stages1, stages2; // ring depth in phase 1 (stages of tile_tok + 2 r1 rows) and phase 2 (tile_tok + 256 rows)
+  int ring_bytes;       // shared memory the ring may use (the larger of the two shapes, plus what the
+                        // 128-row MMA operand of a shorter tile reads behind the last stage)
+  int f1, f2;           // work items per expert: ceil(I/r1), ceil(H/256)
   int kb1, kb2;         // k-blocks per item: ceil(H/64), ceil(I/64)
   int g1, g2;           // CTAs that take phase-1 / phase-2 items
   unsigned long long* stamps;   // diagnostic: [cta][8] %globaltimer values, or null
@@ -60,6 +66,13 @@ struct Cursor {
   int phase;            // 1, 2; 3 = finished
   int item, end, kb;
   int a2, b2;
+  int e, f;             // expert and tile of the current item (divisions once per item, not per k-block)
+  __device__ __forceinline__ void locate(const MlpParams& p) {
+    if (phase == 3) return;
+    const int per = phase == 1 ? p.f1 : p.f2;
+    e = item / per;
+    f = item - e * per;
+  }
   __device__ __forceinline__ void init(const MlpParams& p) {
     const int c = (int)blockIdx.x;
     const int n1 = p.E * p.f1, n2 = p.E * p.f2;
@@ -77,19 +90,23 @@ struct Cursor {
     phase = 1; item = a1; end = b1;
     if (item >= end) { phase = 2; item = a2; end = b2; }
     if (item >= end) phase = 3;
+    e = f = 0;
+    locate(p);
   }
-  __device__ __forceinline__ void next_item() {
+  __device__ __forceinline__ void next_item(const MlpParams& p) {
     kb = 0;
-    if (++item < end) return;
-    if (phase == 1) {
-      phase = 2; item = a2; end = b2;
-      if (item >= end) phase = 3;
-    } else {
-      phase = 3;
+    if (++item >= end) {
+      if (phase == 1) {
+        phase = 2; item = a2; end = b2;
+        if (item >= end) phase = 3;
+      } else {
+        phase = 3;
+      }
     }
+    locate(p);
   }
   __device__ __forceinline__ void next_kblock(const MlpParams& p) {
-    if (++kb == (phase == 1 ? p.kb1 : p.kb2)) next_item();
+    if (++kb == (phase == 1 ? p.kb1 : p.kb2)) next_item(p);
   }
 };
 
@@ -112,9 +129,16 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tt = p.tile_tok;
-  const uint32_t tok_bytes = tt * 128, w_bytes = 256 * 128;
-  const uint32_t stage_bytes = tok_bytes + w_bytes;
-  Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)p.stages * stage_bytes);
+  // The ring has one shape per phase (same shared memory, barriers 0.. for phase 1 and
+  // kBar2.. for phase 2): phase 1 stages hold the token tile and r1 gate + r1 up rows, phase 2
+  // stages the token tile and 256 rows of w2.  r1 < 128 is how 128 (or more) CTAs get a whole
+  // item each when the shard has fewer than 128 tiles of 128 rows -- more CTAs streaming and a
+  // deeper ring mean more bytes in flight, which is what the rate of a thin shard depends on.
+  constexpr int kBar2 = 8;
+  const uint32_t tok_bytes = tt * 128;
+  const uint32_t half1 = p.r1 * 128;                 // bytes of the gate (or up) rows of a phase-1 stage
+  const uint32_t sb1 = tok_bytes + 2 * half1, sb2 = tok_bytes + 256 * 128;
+  Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)p.ring_bytes);
   int* s_rowmap = reinterpret_cast<int*>(sh + 1);    // [4 warps][128]: output row of every token for the current expert
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -122,7 +146,7 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
     stamp(p.stamps, 0);
-    for (int i = 0; i < p.stages; ++i) {
+    for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(&sh->full[i], 1);
       mbar_init(&sh->empty[i], 1);
     }
@@ -164,13 +188,11 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         if (pf.phase == 3) return;
         if (issue) {
           if (pf.phase == 1) {
-            const int e = pf.item / p.f1, f = pf.item - e * p.f1;
-            const int row = e * 2 * p.I + f * 128;
+            const int row = pf.e * 2 * p.I + pf.f * p.r1;
             tma_prefetch_l2_2d(&map_wu, pf.kb * kBlockK, row);
             tma_prefetch_l2_2d(&map_wu, pf.kb * kBlockK, row + p.I);
           } else {
-            const int e = pf.item / p.f2, f = pf.item - e * p.f2;
-            const int row = e * p.H + f * 256;
+            const int row = pf.e * p.H + pf.f * 256;
             tma_prefetch_l2_2d(&map_w2, pf.kb * kBlockK, row);
             tma_prefetch_l2_2d(&map_w2, pf.kb * kBlockK, row + 128);
           }
@@ -178,19 +200,22 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         pf.next_kblock(p);
       };
       if (p.l2_ahead > 0)
-        for (int i = 0; i < p.stages + p.l2_ahead; ++i) prefetch_step(i >= p.stages);
+        for (int i = 0; i < p.stages1 + p.l2_ahead; ++i) prefetch_step(i >= p.stages1);
       int w_stage = 0, t_stage = 0, pending = 0;
       uint32_t w_phase = 0;
+      int ring = w.phase == 2 ? 2 : 1;            // the shape the ring has now
+      int nst = ring == 1 ? p.stages1 : p.stages2, bar0 = ring == 1 ? 0 : kBar2;
+      uint32_t sb = ring == 1 ? sb1 : sb2;
       int ready_e = -1;          // expert whose rows of h are known to be complete
+      int ready_row = 0;         // ... and its first row in h
       bool routed = false;       // pdl_wait() done: expert_offset may be read
       bool ok = true;
       while (ok && t.phase != 3) {
         while (pending > 0) {
-          int e = 0;
+          const int e = t.e;
           if (t.phase == 2) {
-            e = t.item / p.f2;
             if (e != ready_e) {
-              const bool must = pending == p.stages || w.phase == 3;   // nothing else to request
+              const bool must = pending == nst || w.phase == 3;   // nothing else to request
               if (!routed) {
                 // The counters belong to this launch only once every kernel in front has
                 // finished (an earlier launch of this kernel clears them as it leaves), and
@@ -220,41 +245,54 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
               if (!ready) break;
               fence_proxy_async_global();
               ready_e = e;
+              long long r0 = p.off[e];      // first row of expert e in h (once per expert, not per k-block)
+              ready_row = (int)(r0 < 0 ? 0 : (r0 > (long long)p.T * p.k ? (long long)p.T * p.k : r0));
             }
           }
-          const uint32_t dst = smem_base + t_stage * stage_bytes;
-          mbar_expect_tx(&sh->full[t_stage], tok_bytes);
+          const uint32_t dst = smem_base + t_stage * sb;
+          uint64_t* bar = &sh->full[bar0 + t_stage];
+          mbar_expect_tx(bar, tok_bytes);
           if (t.phase == 1) {
-            tma_load_2d(dst, &map_x, &sh->full[t_stage], t.kb * kBlockK, 0);
+            tma_load_2d(dst, &map_x, bar, t.kb * kBlockK, 0);
           } else {
-            long long r0 = p.off[e];
-            r0 = r0 < 0 ? 0 : (r0 > (long long)p.T * p.k ? (long long)p.T * p.k : r0);
-            tma_load_2d(dst, &map_h, &sh->full[t_stage], t.kb * kBlockK, (int)r0);
+            tma_load_2d(dst, &map_h, bar, t.kb * kBlockK, ready_row);
           }
           t.next_kblock(p);
-          if (++t_stage == p.stages) t_stage = 0;
+          if (++t_stage == nst) t_stage = 0;
           --pending;
         }
         if (!ok) break;
-        if (w.phase != 3 && pending < p.stages) {
-          ok = wait_barrier(&sh->empty[w_stage], w_phase ^ 1u, sh, p.status, 0, w.item);
+        if (w.phase != 3 && pending < nst) {
+          if (w.phase != ring) {
+            // Phase 1 is requested completely (and, x being there from the start, `t` has caught
+            // up: pending is 0).  The ring takes its phase-2 shape once the MMAs have read every
+            // phase-1 stage: stage s was last filled in this pass over the ring if s < w_stage,
+            // in the pass before otherwise.
+            for (int s = 0; s < p.stages1 && ok; ++s)
+              ok = wait_barrier(&sh->empty[s], s < w_stage ? w_phase : w_phase ^ 1u, sh, p.status, 0, w.item);
+            if (!ok) break;
+            ring = 2; nst = p.stages2; bar0 = kBar2; sb = sb2;
+            w_stage = t_stage = 0;
+            w_phase = 0;
+          }
+          ok = wait_barrier(&sh->empty[bar0 + w_stage], w_phase ^ 1u, sh, p.status, 0, w.item);
           if (!ok) break;
-          const uint32_t dst = smem_base + w_stage * stage_bytes + tok_bytes;
+          const uint32_t dst = smem_base + w_stage * sb + tok_bytes;
+          uint64_t* bar = &sh->full[bar0 + w_stage];
           if (p.l2_ahead > 0) prefetch_step(true);
-          mbar_expect_tx_only(&sh->full[w_stage], w_bytes);
           if (w.phase == 1) {
-            const int e = w.item / p.f1, f = w.item - e * p.f1;
-            const int row = e * 2 * p.I + f * 128;
-            tma_load_2d(dst, &map_wu, &sh->full[w_stage], w.kb * kBlockK, row);
-            tma_load_2d(dst + 128 * 128, &map_wu, &sh->full[w_stage], w.kb * kBlockK, row + p.I);
+            const int row = w.e * 2 * p.I + w.f * p.r1;
+            mbar_expect_tx_only(bar, 2 * half1);
+            tma_load_2d(dst, &map_wu, bar, w.kb * kBlockK, row);
+            tma_load_2d(dst + half1, &map_wu, bar, w.kb * kBlockK, row + p.I);
           } else {
-            const int e = w.item / p.f2, f = w.item - e * p.f2;
-            const int row = e * p.H + f * 256;
-            tma_load_2d(dst, &map_w2, &sh->full[w_stage], w.kb * kBlockK, row);
-            tma_load_2d(dst + 128 * 128, &map_w2, &sh->full[w_stage], w.kb * kBlockK, row + 128);
+            const int row = w.e * p.H + w.f * 256;
+            mbar_expect_tx_only(bar, 256 * 128);
+            tma_load_2d(dst, &map_w2, bar, w.kb * kBlockK, row);
+            tma_load_2d(dst + 128 * 128, &map_w2, bar, w.kb * kBlockK, row + 128);
           }
           w.next_kblock(p);
-          if (++w_stage == p.stages) { w_stage = 0; w_phase ^= 1u; }
+          if (++w_stage == nst) { w_stage = 0; w_phase ^= 1u; }
           ++pending;
         }
       }
@@ -274,21 +312,25 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       c.init(p);
       bool ok = true;
       bool first_tile = true, first_down = true;
+      int ring = c.phase == 2 ? 2 : 1;
       while (ok && c.phase != 3) {
+        if (c.phase != ring) { ring = 2; stage = 0; phase = 0; }     // the ring's phase-2 shape and barriers
+        const int nst = ring == 1 ? p.stages1 : p.stages2, bar0 = ring == 1 ? 0 : kBar2;
+        const uint32_t sb = ring == 1 ? sb1 : sb2, second = ring == 1 ? half1 : 128u * 128u;
         ok = wait_barrier(&sh->acc_empty[acc], acc_phase ^ 1u, sh, p.status, 1, c.item);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kAccStride;
         const int nkb = c.phase == 1 ? p.kb1 : p.kb2;
         for (int kb = 0; kb < nkb; ++kb) {
-          ok = wait_barrier(&sh->full[stage], phase, sh, p.status, 2, c.item);
+          ok = wait_barrier(&sh->full[bar0 + stage], phase, sh, p.status, 2, c.item);
           if (!ok) break;
           if (p.stamps) {
             if (first_tile) { stamp(p.stamps, 2); first_tile = false; }
             if (c.phase == 2 && kb == 0 && first_down) { stamp(p.stamps, 7); first_down = false; }   // first tile of h arrived
           }
           tc_fence_after();
-          const uint32_t tok_addr = smem_base + stage * stage_bytes;
+          const uint32_t tok_addr = smem_base + stage * sb;
           const uint32_t w_addr = tok_addr + tok_bytes;
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
@@ -296,15 +338,15 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             const uint32_t accum = (kb > 0 || kk > 0) ? 1u : 0u;
             const uint64_t bdesc = smem_desc_sw128(tok_addr + koff);
             umma_f16(d_tmem, smem_desc_sw128(w_addr + koff), bdesc, idesc, accum);
-            umma_f16(d_tmem + tt, smem_desc_sw128(w_addr + 128 * 128 + koff), bdesc, idesc, accum);
+            umma_f16(d_tmem + tt, smem_desc_sw128(w_addr + second + koff), bdesc, idesc, accum);
           }
-          umma_commit(&sh->empty[stage]);
-          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+          umma_commit(&sh->empty[bar0 + stage]);
+          if (++stage == nst) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         umma_commit(&sh->acc_full[acc]);
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
-        c.next_item();
+        c.next_item(p);
       }
       stamp(p.stamps, 3);
     }
@@ -323,8 +365,7 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     if (warp == 2 && lane == 0) stamp(p.stamps, 4);
     while (c.phase != 3) {
       const bool gate_up = c.phase == 1;
-      const int per = gate_up ? p.f1 : p.f2;
-      const int e = c.item / per, f = c.item - e * per;
+      const int e = c.e, f = c.f;
       const long long lo = p.off[e], hi = p.off[e + 1];
       if (gate_up && e != map_expert) {
         // which row of the expert-sorted order holds token t for this expert (-1: not routed here)
@@ -347,50 +388,58 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * kAccStride + (static_cast<uint32_t>(q * 32) << 16);
-      if (gate_up) {
-        const int col = f * 128 + q * 32 + lane;   // feature of h this thread owns
-        const bool col_ok = col < p.I;
-        for (int c0 = 0; c0 < tt && c0 < p.T; c0 += 16) {
-          float g[16], u[16];
-          __syncwarp();
-          tmem_ld16(taddr + c0, g);
-          tmem_ld16(taddr + tt + c0, u);
-          tmem_wait_ld();
+      // Up to 32 columns of both halves per round: their tensor-memory loads are all in flight
+      // before the one wait (a tcgen05.ld round trip costs several hundred ns).  Not more: with
+      // all 64 columns in registers the kernel needs > 200 registers per thread, and two of its
+      // warps no longer fit beside two warps of the routing kernel in an SM sub-partition's
+      // register file -- the CTAs on the router's SMs then start 9 us late.
+      const int rows = (int)(hi - lo < 0 ? 0 : (hi - lo > tt ? tt : hi - lo));
+      const int ncol = gate_up ? (p.T < tt ? p.T : tt) : rows;     // accumulator columns that matter
+      const int colg = f * p.r1 + q * 32 + lane;                   // phase 1: feature of h this thread owns
+      const bool colg_ok = q * 32 + lane < p.r1 && colg < p.I;
+      const int col0 = f * 256 + q * 32 + lane, col1 = col0 + 128; // phase 2: features of y this thread owns
+      for (int c0 = 0; c0 < ncol; c0 += 32) {
+        float a[2][16], b[2][16];
+        __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int row = s_rowmap[q * 128 + c0 + i];
-            if (row >= 0 && col_ok) h[(int64_t)row * p.I + col] = Elem<T>::from_f(swiglu_f(g[i], u[i], p.beta));
+        for (int ch = 0; ch < 2; ++ch) {
+          if (c0 + ch * 16 < ncol) {
+            tmem_ld16(taddr + c0 + ch * 16, a[ch]);
+            tmem_ld16(taddr + tt + c0 + ch * 16, b[ch]);
           }
         }
+        tmem_wait_ld();
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          if (c0 + ch * 16 < ncol) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int cc = c0 + ch * 16 + i;
+              if (gate_up) {
+                const int row = s_rowmap[q * 128 + cc];
+                if (row >= 0 && colg_ok)
+                  h[(int64_t)row * p.I + colg] = Elem<T>::from_f(swiglu_f(a[ch][i], b[ch][i], p.beta));
+              } else if (cc < rows) {
+                T* dst = y + (int64_t)(lo + cc) * p.H;
+                if (col0 < p.H) dst[col0] = Elem<T>::from_f(a[ch][i]);
+                if (col1 < p.H) dst[col1] = Elem<T>::from_f(b[ch][i]);
+              }
+            }
+          }
+        }
+      }
+      if (gate_up) {
         // this warp's part of the tile is in global memory: count it for the down projection
         __threadfence();
         fence_proxy_async_global();
         __syncwarp();
         if (lane == 0) atomicAdd(p.done + e, 1u);
-      } else {
-        const int rows = (int)(hi - lo < 0 ? 0 : (hi - lo > tt ? tt : hi - lo));
-        const int col0 = f * 256 + q * 32 + lane, col1 = col0 + 128;   // features of y this thread owns
-        for (int c0 = 0; c0 < rows; c0 += 16) {
-          float a[16], b[16];
-          __syncwarp();
-          tmem_ld16(taddr + c0, a);
-          tmem_ld16(taddr + tt + c0, b);
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            if (c0 + i < rows) {
-              T* dst = y + (int64_t)(lo + c0 + i) * p.H;
-              if (col0 < p.H) dst[col0] = Elem<T>::from_f(a[i]);
-              if (col1 < p.H) dst[col1] = Elem<T>::from_f(b[i]);
-            }
-          }
-        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
-      c.next_item();
+      c.next_item(p);
     }
     if (warp == 2 && lane == 0) stamp(p.stamps, 5);
   }
@@ -413,8 +462,6 @@ expert_mlp_decode_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 }
 
 constexpr size_t kRowMapBytes = 4 * 128 * sizeof(int);
-constexpr int kMlpMaxTokens = 64;
-constexpr int kMlpCtaCap = 128;
 
 // CTAs that take the n items of a phase: the smallest grid that needs no more rounds than
 // `cap` CTAs would, so that every round is full
@@ -424,7 +471,13 @@ int full_round_grid(int n, int cap) {
   return (n + rounds - 1) / rounds;
 }
 
+std::atomic<int> g_mlp_rows{0};
+
 }  // namespace
+
+int dense_mlp_set_rows(int rows) {
+  return g_mlp_rows.exchange(rows >= 64 && rows <= 128 && rows % 8 == 0 ? rows : 0, std::memory_order_relaxed);
+}
 
 bool dense_mlp_covers(int64_t T, int64_t N, int64_t H, int E, int k, int dtype) {
   return T >= 1 && T <= kMlpMaxTokens && E >= 1 && E <= kMaxExperts && k >= 1 && k <= E && N >= 16 && N % 16 == 0 &&
@@ -455,37 +508,60 @@ int launch_dense_mlp(const void* x, const int64_t* inv, const int64_t* off, cons
   p.T = (int)T; p.E = E; p.k = k;
   p.I = (int)I; p.H = (int)H;
   p.tile_tok = (int)(ceil_div(T, 16) * 16);
-  p.f1 = (int)ceil_div(I, 128);
   p.f2 = (int)ceil_div(H, 256);
   p.kb1 = (int)ceil_div(H, kBlockK);
   p.kb2 = (int)ceil_div(I, kBlockK);
-  const int sms = sm_count();
-  const int cap = sms < kMlpCtaCap ? sms : kMlpCtaCap;
-  p.g1 = full_round_grid(E * p.f1, cap);
-  p.g2 = full_round_grid(E * p.f2, cap);
   p.beta = beta;
   p.l2_ahead = default_l2_prefetch();
   p.stamps = next_stamp_slot(4);
-  const size_t stage = (size_t)(p.tile_tok + 256) * 128;
+  const int sms = sm_count();
+  const size_t tok = (size_t)p.tile_tok * 128;
   const size_t fixed = 1024 + sizeof(Shared) + kRowMapBytes;
-  // 24 KB of every SM's shared memory stay free, so that a CTA of the routing kernel and a
-  // CTA of this one fit on an SM together
-  int st_n = (int)((203 * 1024 - fixed) / stage);
-  if (st_n > kMaxStages) st_n = kMaxStages;
-  if (st_n < 2) return fail(PMX_ERR_UNSUPPORTED, "dense_mlp: the stage does not fit in shared memory");
-  p.stages = st_n;
+  // 4 KB of every SM's shared memory stay free, so that a CTA of the routing kernel (which asks
+  // for the same carve-out) and a CTA of this one fit on an SM together
+  const size_t budget = 223 * 1024 - fixed;
+  // Phase 1: rows per item.  The rate of a thin shard's weight stream grows with the bytes in
+  // flight (CTAs x ring depth x weight bytes per stage) until about 26 MB; a CTA's time is
+  // its rows x k-blocks.  Model: time ~ rounds x rows x CTAs / min(in flight, 26 MB).
+  double best = 0.0;
+  p.r1 = 0;
+  const int forced = g_mlp_rows.load(std::memory_order_relaxed);
+  for (int r = 128; r >= 64; r -= 8) {
+    if (forced && r != forced) continue;
+    const int64_t items = (int64_t)E * ceil_div(I, r);
+    const int64_t rounds = ceil_div(items, sms);
+    const int64_t ctas = ceil_div(items, rounds);
+    const size_t stage = tok + 2 * (size_t)r * 128;
+    const size_t pad = (size_t)(128 - r) * 128;            // what the 128-row operand reads behind a short tile
+    if (budget < pad + 2 * stage) continue;
+    int st1 = (int)((budget - pad) / stage);
+    if (st1 > 8) st1 = 8;
+    const double flight = (double)ctas * st1 * 2.0 * r * 128.0;
+    const double t = (double)rounds * r * (double)ctas / (flight < 26e6 ? flight : 26e6);
+    if (p.r1 == 0 || t < best * 0.995) { best = t; p.r1 = r; p.stages1 = st1; p.g1 = (int)ctas; }
+  }
+  if (p.r1 == 0) return fail(PMX_ERR_UNSUPPORTED, "dense_mlp: the stage does not fit in shared memory");
+  p.f1 = (int)ceil_div(I, p.r1);
+  const size_t stage2 = tok + 256 * 128;
+  p.stages2 = (int)(budget / stage2);
+  if (p.stages2 > 8) p.stages2 = 8;
+  if (p.stages2 < 2) return fail(PMX_ERR_UNSUPPORTED, "dense_mlp: the stage does not fit in shared memory");
+  p.g2 = full_round_grid(E * p.f2, sms);
+  const size_t ring1 = (size_t)p.stages1 * (tok + 2 * (size_t)p.r1 * 128) + (size_t)(128 - p.r1) * 128;
+  const size_t ring2 = (size_t)p.stages2 * stage2;
+  p.ring_bytes = (int)(ring1 > ring2 ? ring1 : ring2);
 
   CUtensorMap mx, mwu, mh, mw2;
   int st = make_map(&mx, x, (uint64_t)T, (uint64_t)H, (uint32_t)p.tile_tok, dtype);
   if (st != PMX_OK) return st;
-  st = make_map(&mwu, wu, (uint64_t)E * N, (uint64_t)H, 128u, dtype);
+  st = make_map(&mwu, wu, (uint64_t)E * N, (uint64_t)H, (uint32_t)p.r1, dtype);
   if (st != PMX_OK) return st;
   st = make_map(&mh, h, (uint64_t)T * k, (uint64_t)I, (uint32_t)p.tile_tok, dtype);
   if (st != PMX_OK) return st;
   st = make_map(&mw2, w2, (uint64_t)E * H, (uint64_t)I, 128u, dtype);
   if (st != PMX_OK) return st;
 
-  const size_t smem = fixed + stage * (size_t)p.stages;
+  const size_t smem = fixed + (size_t)p.ring_bytes;
   const void* kern = dtype == PMX_DTYPE_BF16 ? (const void*)expert_mlp_decode_kernel<__nv_bfloat16>
                                              : (const void*)expert_mlp_decode_kernel<__half>;
   PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -235,16 +235,17 @@ class MoeFeedForward(nn.Module):
                 and tokens // n_mb * self.hidden_dim * x.element_size() >= OVERLAP_MIN_BYTES
                 and not (self.peer_reduce_tokens >= tokens and self._peer_fits(tokens, x.dtype))):
             return self._forward_microbatched(x, router_logits, n_mb)
+        one_launch = (self.one_launch_experts and self.wu.bias is None and self.w2.bias is None and tokens > 0
+                      and dense_mlp_covers(tokens, self.wu.weight, self.w2.weight, k))
         if (router_logits is None and self.fused and self.dense_decode and tokens > 0
-                and dense_gate_up_covers(tokens, self.wu.weight, k)):
+                and (one_launch or dense_gate_up_covers(tokens, self.wu.weight, k))):
             # decode-size batch with (almost surely) every expert in use: the gate/up projection
             # reads the un-permuted tokens and streams its weights while the router is running
             with _range("moe.route_select"):
                 routed = moe_route_select(x, self.gate.weight, E, k, gather=False)
             if routed is not None:
                 _, _, expert_weights, invert_permutation, expert_offset = routed
-                if (self.one_launch_experts and self.wu.bias is None and self.w2.bias is None
-                        and dense_mlp_covers(tokens, self.wu.weight, self.w2.weight, k)):
+                if one_launch:
                     with _range("moe.experts(one launch)"):
                         y, self._mlp_ws = moe_dense_mlp(x, invert_permutation, expert_offset, self.wu.weight,
                                                         self.w2.weight, return_workspace=True)

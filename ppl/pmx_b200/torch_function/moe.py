@@ -323,15 +323,20 @@ def moe_dense_gate_up(X: torch.Tensor, invert_permutation: torch.Tensor, expert_
     return (h, ws) if return_workspace else h
 
 
+ONE_LAUNCH_MAX_TILES = 2 * 128     # 128-row gate/up tiles of all experts up to which moe_dense_mlp is used
+
+
 def dense_mlp_covers(T: int, Wu: torch.Tensor, W2: torch.Tensor, k: int) -> bool:
-    """Whether moe_dense_mlp takes this shape and pays: the shapes dense_gate_up_covers accepts
-    (decode batches on thin tensor-parallel shards, where the fixed cost of a launch is a large
-    part of each projection), without bias."""
+    """Whether moe_dense_mlp takes this shape and pays: decode batches (at most 64 tokens, a
+    chance of an unused expert below 2 %: every expert's weights are read), without bias, up to
+    ONE_LAUNCH_MAX_TILES gate/up tiles."""
     E, N, H = Wu.shape
     code = DTYPE_CODE.get(Wu.dtype)
     if code is None or tuple(W2.shape) != (E, H, N // 2) or W2.dtype != Wu.dtype:
         return False
-    return bool(dense_gate_up_covers(T, Wu, k) and lib.pmx_moe_dense_mlp_covers(T, N, H, E, k, code))
+    if T > 64 or E * ((N // 2 + 127) // 128) > ONE_LAUNCH_MAX_TILES or ((E - k) / E) ** T >= 0.02:
+        return False
+    return bool(lib.pmx_moe_dense_mlp_covers(T, N, H, E, k, code))
 
 
 def moe_dense_mlp(X: torch.Tensor, invert_permutation: torch.Tensor, expert_offset: torch.Tensor,
