@@ -977,6 +977,8 @@ def main():
                     help="N > 1, results too large for the peer kernel: runs of tokens whose all-reduce overlaps "
                          "the next run's kernels")
     ap.add_argument("--stamps-raw", action="store_true", help="with --stamps: also the per-CTA values")
+    ap.add_argument("--no-weight-prefetch", action="store_true",
+                    help="routed decode GEMMs: do not request the first item's weight tiles ahead of the dependency wait")
     ap.add_argument("--mlp-rows", type=int, default=None,
                     help="one-launch expert kernel: gate (= up) rows per work item of the first projection (64..128)")
     ap.add_argument("--one-launch-max-tiles", type=int, default=None,
@@ -1036,6 +1038,8 @@ def main():
     from ppl.pmx_b200 import _cabi
     if args.no_pdl:
         _cabi.lib.pmx_moe_set_programmatic_launch(0)
+    if args.no_weight_prefetch:
+        _cabi.lib.pmx_moe_set_weight_prefetch(0)
     if args.mlp_rows is not None:
         _cabi.lib.pmx_moe_dense_mlp_set_rows(args.mlp_rows)
     if args.one_launch_max_tiles is not None:

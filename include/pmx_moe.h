@@ -110,6 +110,11 @@ int pmx_moe_set_programmatic_launch(int on);
  * loads in the TMA unit and every distance measured was slower (8 k-blocks: the 64-token Mixtral
  * decode step 0.68 ms against 0.47 ms, its 1/8 shard 116 against 94 us). */
 int pmx_moe_set_l2_prefetch(int32_t kblocks);
+/* Weight rows on MMA-M (routed decode GEMMs): whether a CTA requests the weight tiles of its
+ * guessed first work item before it waits for the kernel in front (the guess -- every expert
+ * owns rows -- is checked after the wait; a wrong guess hands the stages back unused).
+ * Process-wide; returns the previous setting. */
+int pmx_moe_set_weight_prefetch(int on);
 /* Diagnostic: while a device buffer is set, every launch of the router + select kernel and of
  * the weight-streaming expert GEMMs (also when recorded into a CUDA graph) takes the next slot
  * of 160 x 8 uint64 in it and its CTAs store %globaltimer values there: [cta][0] entry,

@@ -54,6 +54,7 @@ def _load() -> C.CDLL:
         "pmx_moe_route_select_check": (C.c_int, [vp, vp]),
         "pmx_moe_set_programmatic_launch": (C.c_int, [C.c_int]),
         "pmx_moe_set_l2_prefetch": (C.c_int, [i32]),
+        "pmx_moe_set_weight_prefetch": (C.c_int, [C.c_int]),
         "pmx_moe_set_stamp_buffer": (C.c_int, [vp, sz]),
         "pmx_moe_stamp_slots": (C.c_int, [vp, i32]),
         "pmx_decode_cache_attention_set_kernel": (C.c_int, [i32]),

@@ -15,6 +15,7 @@ thread_local char g_error[512] = "";
 std::atomic<long long> g_launches{0};
 std::atomic<int> g_pdl{1};
 std::atomic<int> g_l2_prefetch{0};
+std::atomic<int> g_weight_prefetch{1};
 std::mutex g_stamp_mutex;
 unsigned long long* g_stamp_buf = nullptr;
 int g_stamp_slots = 0, g_stamp_used = 0;
@@ -62,6 +63,8 @@ unsigned long long* next_stamp_slot(int kernel_id) {
   g_stamp_kernel[g_stamp_used] = kernel_id;
   return g_stamp_buf + (size_t)(g_stamp_used++) * kStampCtas * kStampWords;
 }
+
+int weight_prefetch_enabled() { return g_weight_prefetch.load(std::memory_order_relaxed); }
 
 int default_l2_prefetch() { return g_l2_prefetch.load(std::memory_order_relaxed); }
 
@@ -296,6 +299,10 @@ int pmx_moe_stamp_slots(int32_t* kernel_ids, int32_t max_ids) {
   std::lock_guard<std::mutex> lock(g_stamp_mutex);
   for (int i = 0; i < g_stamp_used && i < max_ids; ++i) kernel_ids[i] = g_stamp_kernel[i];
   return g_stamp_used;
+}
+
+int pmx_moe_set_weight_prefetch(int on) {
+  return g_weight_prefetch.exchange(on ? 1 : 0, std::memory_order_relaxed);
 }
 
 int pmx_moe_set_l2_prefetch(int32_t kblocks) {

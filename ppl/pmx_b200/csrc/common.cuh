@@ -187,6 +187,7 @@ struct TcPlan {
   int l2_ahead;    // k-blocks of weight tiles requested into L2 in front of the ring
 };
 int default_l2_prefetch();
+int weight_prefetch_enabled();   // pmx_moe_set_weight_prefetch
 // Diagnostic time stamps (pmx_moe_set_stamp_buffer): the next slot of kStampCtas x kStampWords
 // %globaltimer values for one launch of an instrumented kernel, or null when switched off.
 constexpr int kStampWords = 8;

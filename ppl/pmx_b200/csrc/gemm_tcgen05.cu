@@ -704,7 +704,7 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
   p.tile_feat = plan.tile_feat;
   p.feat_tiles = plan.balanced ? 1 : (int)ceil_div(n_out, plan.tile_feat);
   p.balanced = plan.balanced;
-  p.prefetch = plan.kernel == PMX_GEMM_TC_WEIGHTS_M && plan.balanced && plan.split_k == 1 && !plan.stream_k &&
+  p.prefetch = weight_prefetch_enabled() && plan.kernel == PMX_GEMM_TC_WEIGHTS_M && plan.balanced && plan.split_k == 1 && !plan.stream_k &&
                n_out >= 128;
   p.units_per_panel = (int)(n_out / 8);
   p.l2_ahead = plan.kernel == PMX_GEMM_TC_WEIGHTS_M && !plan.stream_k ? plan.l2_ahead : 0;
