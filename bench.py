@@ -977,13 +977,17 @@ def main():
                     help="N > 1, results too large for the peer kernel: runs of tokens whose all-reduce overlaps "
                          "the next run's kernels")
     ap.add_argument("--stamps-raw", action="store_true", help="with --stamps: also the per-CTA values")
-    ap.add_argument("--no-weight-prefetch", action="store_true",
-                    help="routed decode GEMMs: do not request the first item's weight tiles ahead of the dependency wait")
+    ap.add_argument("--weight-prefetch", action="store_true",
+                    help="routed decode GEMMs: request the first item's weight tiles ahead of the dependency wait "
+                         "(off by default: measured slower)")
     ap.add_argument("--mlp-rows", type=int, default=None,
                     help="one-launch expert kernel: gate (= up) rows per work item of the first projection (64..128)")
     ap.add_argument("--one-launch-max-tiles", type=int, default=None,
                     help="largest number of 128-row gate/up tiles (all experts) for which decode batches run both "
                          "expert projections in one launch (library default 256: the 1/4 shard)")
+    ap.add_argument("--one-launch-max-tokens", type=int, default=None,
+                    help="largest decode batch that runs both expert projections in one launch (library default 64; "
+                         "the kernel takes up to 128)")
     ap.add_argument("--no-one-launch", action="store_true",
                     help="decode-size batches on thin shards: gate/up and down projection as two launches")
     ap.add_argument("--overlap-chunks", type=int, default=1,
@@ -1038,13 +1042,16 @@ def main():
     from ppl.pmx_b200 import _cabi
     if args.no_pdl:
         _cabi.lib.pmx_moe_set_programmatic_launch(0)
-    if args.no_weight_prefetch:
-        _cabi.lib.pmx_moe_set_weight_prefetch(0)
+    if args.weight_prefetch:
+        _cabi.lib.pmx_moe_set_weight_prefetch(1)
     if args.mlp_rows is not None:
         _cabi.lib.pmx_moe_dense_mlp_set_rows(args.mlp_rows)
     if args.one_launch_max_tiles is not None:
         import ppl.pmx_b200.torch_function.moe as moe_mod
         moe_mod.ONE_LAUNCH_MAX_TILES = args.one_launch_max_tiles
+    if args.one_launch_max_tokens is not None:
+        import ppl.pmx_b200.torch_function.moe as moe_mod
+        moe_mod.ONE_LAUNCH_MAX_TOKENS = args.one_launch_max_tokens
     if args.l2_prefetch is not None:
         _cabi.lib.pmx_moe_set_l2_prefetch(args.l2_prefetch)
     _cabi.lib.pmx_decode_cache_attention_set_kernel(["mma", "simt"].index(args.attention_kernel))

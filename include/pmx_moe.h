@@ -113,7 +113,10 @@ int pmx_moe_set_l2_prefetch(int32_t kblocks);
 /* Weight rows on MMA-M (routed decode GEMMs): whether a CTA requests the weight tiles of its
  * guessed first work item before it waits for the kernel in front (the guess -- every expert
  * owns rows -- is checked after the wait; a wrong guess hands the stages back unused).
- * Process-wide; returns the previous setting. */
+ * Off by default: measured on B200 on the 1/8 shard of the Mixtral layer it made the step
+ * SLOWER (64 tokens 99.5 against 96.1 us, 8 tokens 93.0 against 88.6 us: the two-step fill of
+ * the first stages and the wrong guesses cost more than the early requests gain) and changed
+ * nothing at full size.  Process-wide; returns the previous setting. */
 int pmx_moe_set_weight_prefetch(int on);
 /* Diagnostic: while a device buffer is set, every launch of the router + select kernel and of
  * the weight-streaming expert GEMMs (also when recorded into a CUDA graph) takes the next slot
@@ -294,7 +297,7 @@ int pmx_moe_dense_gate_up(const void* x, const int64_t* invert_permutation,
  * stream is in flight while the last gate/up tiles finish).  x [T,H], wu [E,N,H] =
  * [gate rows ; up rows], w2 [E,H,N/2], h [T*k,N/2] (an output too), y [T*k,H]; no bias.
  * Same contract towards the routing kernel in front as pmx_moe_dense_gate_up.  Covers
- * T <= 64, float16 / bfloat16, N % 16 == 0, H % 8 == 0.  Workspace
+ * T <= 128, float16 / bfloat16, N % 16 == 0, H % 8 == 0.  Workspace
  * (pmx_moe_dense_mlp_workspace_bytes, 16-byte aligned): status words + per-expert
  * counters; it must be zero before the first launch that uses it, every completed launch
  * leaves it zero, and launches that share it must not overlap on the GPU.

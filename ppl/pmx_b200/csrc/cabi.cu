@@ -15,7 +15,7 @@ thread_local char g_error[512] = "";
 std::atomic<long long> g_launches{0};
 std::atomic<int> g_pdl{1};
 std::atomic<int> g_l2_prefetch{0};
-std::atomic<int> g_weight_prefetch{1};
+std::atomic<int> g_weight_prefetch{0};
 std::mutex g_stamp_mutex;
 unsigned long long* g_stamp_buf = nullptr;
 int g_stamp_slots = 0, g_stamp_used = 0;

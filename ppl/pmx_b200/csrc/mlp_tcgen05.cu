@@ -37,7 +37,7 @@ namespace {
 
 #include "tcgen05_common.cuh"
 
-constexpr int kMlpMaxTokens = 64;   // tokens on MMA-N; the epilogue keeps all their accumulator columns in registers
+constexpr int kMlpMaxTokens = 128;  // tokens on MMA-N: two accumulator halves of that many columns fill a 256-column buffer
 
 struct MlpParams {
   const int64_t* off;   // [E+1]

@@ -324,6 +324,7 @@ def moe_dense_gate_up(X: torch.Tensor, invert_permutation: torch.Tensor, expert_
 
 
 ONE_LAUNCH_MAX_TILES = 2 * 128     # 128-row gate/up tiles of all experts up to which moe_dense_mlp is used
+ONE_LAUNCH_MAX_TOKENS = 64         # ... and tokens (the kernel itself takes up to 128)
 
 
 def dense_mlp_covers(T: int, Wu: torch.Tensor, W2: torch.Tensor, k: int) -> bool:
@@ -334,7 +335,8 @@ def dense_mlp_covers(T: int, Wu: torch.Tensor, W2: torch.Tensor, k: int) -> bool
     code = DTYPE_CODE.get(Wu.dtype)
     if code is None or tuple(W2.shape) != (E, H, N // 2) or W2.dtype != Wu.dtype:
         return False
-    if T > 64 or E * ((N // 2 + 127) // 128) > ONE_LAUNCH_MAX_TILES or ((E - k) / E) ** T >= 0.02:
+    if (T > ONE_LAUNCH_MAX_TOKENS or E * ((N // 2 + 127) // 128) > ONE_LAUNCH_MAX_TILES
+            or ((E - k) / E) ** T >= 0.02):
         return False
     return bool(lib.pmx_moe_dense_mlp_covers(T, N, H, E, k, code))
 

@@ -425,7 +425,8 @@ def test_dense_gate_up_matches_the_routed_projection(F, T, H, E, k, N, dtype):
 @pytest.mark.parametrize("T,H,E,k,N,dtype", [(64, 512, 8, 2, 1024, "f16"), (16, 256, 8, 2, 3584, "f16"),
                                              (33, 1024, 4, 2, 784, "bf16"), (64, 4096, 8, 2, 3584, "f16"),
                                              (1, 256, 4, 1, 272, "f16"), (48, 328, 16, 4, 528, "bf16"),
-                                             (64, 2048, 8, 8, 512, "bf16")])
+                                             (64, 2048, 8, 8, 512, "bf16"), (128, 1024, 8, 2, 768, "f16"),
+                                             (100, 512, 4, 2, 528, "bf16")])
 def test_dense_mlp_matches_two_launches_and_the_oracle(F, T, H, E, k, N, dtype):
     """Both expert projections in one launch against the oracle, against the dense gate/up
     launch followed by the routed down projection, and against itself when launches follow
@@ -500,6 +501,28 @@ def test_block_one_launch_experts_equals_two_launches(F):
         blocks[0].check()
         assert torch.equal(out, a)
         g.reset()
+
+
+def test_weight_prefetch_ahead_of_the_wait_gives_the_same_result(F):
+    """The optional request of the first item's weight tiles before the dependency wait
+    (pmx_moe_set_weight_prefetch, off by default), with a right guess (every expert owns
+    rows) and a wrong one (an empty expert): bit-identical to the plain path."""
+    from ppl.pmx_b200._cabi import lib, GemmPlan
+    from ppl.pmx_b200.torch_function.moe import moe_grouped_linear
+    rng = np.random.default_rng(77)
+    M, N, K, E = 96, 512, 1024, 8
+    x = dev(rng.standard_normal((M, K)).astype(np.float32), "f16")
+    w = dev((rng.standard_normal((E, N, K)) / np.sqrt(K)).astype(np.float32), "f16")
+    for empty in (0, 2):
+        off = torch.from_numpy(ragged_offsets(rng, M, E, empty=empty)).cuda()
+        plain = moe_grouped_linear(x, off, w, None, plan=GemmPlan(kernel=2))
+        old = lib.pmx_moe_set_weight_prefetch(1)
+        try:
+            ahead = moe_grouped_linear(x, off, w, None, plan=GemmPlan(kernel=2))
+            torch.cuda.synchronize()
+        finally:
+            lib.pmx_moe_set_weight_prefetch(old)
+        assert torch.equal(plain, ahead)
 
 
 def test_block_dense_decode_path_equals_the_routed_path(F):
