@@ -985,9 +985,12 @@ def main():
     ap.add_argument("--one-launch-max-tiles", type=int, default=None,
                     help="largest number of 128-row gate/up tiles (all experts) for which decode batches run both "
                          "expert projections in one launch (library default 256: the 1/4 shard)")
+    ap.add_argument("--one-launch-max-unused", type=float, default=None,
+                    help="one launch for both expert projections only while the chance of an expert without tokens, "
+                         "((E-k)/E)^T, is below this (library default 0.15)")
     ap.add_argument("--one-launch-max-tokens", type=int, default=None,
-                    help="largest decode batch that runs both expert projections in one launch (library default 64; "
-                         "the kernel takes up to 128)")
+                    help="largest decode batch that runs both expert projections in one launch (library default 128 = "
+                         "the kernel's limit)")
     ap.add_argument("--no-one-launch", action="store_true",
                     help="decode-size batches on thin shards: gate/up and down projection as two launches")
     ap.add_argument("--overlap-chunks", type=int, default=1,
@@ -1049,6 +1052,9 @@ def main():
     if args.one_launch_max_tiles is not None:
         import ppl.pmx_b200.torch_function.moe as moe_mod
         moe_mod.ONE_LAUNCH_MAX_TILES = args.one_launch_max_tiles
+    if args.one_launch_max_unused is not None:
+        import ppl.pmx_b200.torch_function.moe as moe_mod
+        moe_mod.ONE_LAUNCH_MAX_UNUSED = args.one_launch_max_unused
     if args.one_launch_max_tokens is not None:
         import ppl.pmx_b200.torch_function.moe as moe_mod
         moe_mod.ONE_LAUNCH_MAX_TOKENS = args.one_launch_max_tokens
