@@ -603,9 +603,12 @@ def measure(ctx, shape, steps, warmup, regions, headline):
         t_exp = kernel_ms["experts"] * 1e-3
         b_exp = work["bytes_gate_up"] + work["bytes_down"]
         roof_experts = {"bound": "hbm", "achieved": b_exp / t_exp / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                        "frac": b_exp / t_exp / 1e9 / peaks["hbm_gbs"], "kernel_ms": kernel_ms["experts"],
-                        "algorithmic_bytes": b_exp,
-                        "kernel": "both expert projections in one launch (expert_mlp_decode_kernel)"}
+                        "frac": b_exp / t_exp / 1e9 / peaks["hbm_gbs"], "traffic": b_exp * 1.01,
+                        "kernel_ms": kernel_ms["experts"], "algorithmic_bytes": b_exp, "peak_source": peaks["source"],
+                        "kernel": "both expert projections in one launch (expert_mlp_decode_kernel; traffic ratio "
+                                  "1.01 from profiles/expert_mlp_decode_tp8_shard.md)",
+                        "timing": "CUDA events around K back-to-back replays of a CUDA graph holding this launch "
+                                  "alone, same run"}
     else:
         roof_experts = None
     ratio = TRAFFIC_RATIO.get(roof["bound"])
@@ -626,9 +629,11 @@ def measure(ctx, shape, steps, warmup, regions, headline):
         "repeats": {"regions": regions, "steps_per_region": steps, "ms_per_step_median": ms_step,
                     "ms_per_step_min": min(region_ms) / steps, "ms_per_step_max": max(region_ms) / steps},
         "gpu_launches_per_step": int(launches_per_step),
-        "clocks": clocks, "roofline": roof,
+        # the dominant kernel of the step: the one-launch expert kernel where the step uses it
+        # (the gate/up and down launches it replaces are then timed for comparison only)
+        "clocks": clocks, "roofline": roof_experts if roof_experts else roof,
         "roofline_down": {k2: down[k2] for k2 in ("bound", "achieved", "unit", "frac")} if down else None,
-        "roofline_experts_one_launch": roof_experts,
+        "roofline_gate_up_as_its_own_launch": roof if roof_experts else None,
         "layer": {"ms_floor": layer_floor_s * 1e3, "frac_of_roofline": layer_floor_s * 1e3 / ms_step,
                   "active_experts": active, "graph": not args.no_graph,
                   "allreduce": ((f"peer-memory kernel fused with the combine ({args.peer_algo})" if use_peer else "nccl")
@@ -1119,6 +1124,7 @@ def main():
             "clocks": head["clocks"],
             "roofline": head["roofline"],
             "roofline_down": head["roofline_down"],
+            "roofline_gate_up_as_its_own_launch": head.get("roofline_gate_up_as_its_own_launch"),
             "layer": head["layer"],
             "parity": head["parity"],
             "workloads": extras,

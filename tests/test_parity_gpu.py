@@ -525,6 +525,50 @@ def test_weight_prefetch_ahead_of_the_wait_gives_the_same_result(F):
         assert torch.equal(plain, ahead)
 
 
+def test_tuning_switches_do_not_change_results_and_stamps_are_recorded(F):
+    """The L2 prefetch distance, the rows per gate/up item of the one-launch kernel and the
+    time stamps are diagnostics / tuning: same bits with any setting; a launch made while a
+    stamp buffer is set leaves increasing %globaltimer values in its slot."""
+    import ctypes as C
+    from ppl.pmx_b200._cabi import lib
+    from ppl.pmx_b200.torch_function.moe import moe_grouped_linear
+    rng = np.random.default_rng(5)
+    T, H, E, k, N = 32, 512, 8, 2, 768
+    x = dev(rng.standard_normal((T, H)).astype(np.float32), "f16")
+    sc, _ = orc.detie_scores(rng.standard_normal((T, E)).astype(np.float32), "f16")
+    wu = dev((rng.standard_normal((E, N, H)) / np.sqrt(H)).astype(np.float32), "f16")
+    w2 = dev((rng.standard_normal((E, H, N // 2)) / np.sqrt(N // 2)).astype(np.float32), "f16")
+    xe, ew, inv, off = F.moe_select(x, dev(sc, "f16"), E, k)
+    base_y = F.moe_dense_mlp(x, inv, off, wu, w2)
+    base_h = moe_grouped_linear(xe.view(-1, H), off, wu, None, swiglu=True, zero_outside=False)
+    old = lib.pmx_moe_set_l2_prefetch(4)
+    try:
+        assert torch.equal(F.moe_dense_mlp(x, inv, off, wu, w2), base_y)
+        assert torch.equal(moe_grouped_linear(xe.view(-1, H), off, wu, None, swiglu=True, zero_outside=False), base_h)
+    finally:
+        lib.pmx_moe_set_l2_prefetch(old)
+    for rows in (64, 96, 128):
+        lib.pmx_moe_dense_mlp_set_rows(rows)
+        try:
+            assert torch.equal(F.moe_dense_mlp(x, inv, off, wu, w2), base_y)
+        finally:
+            lib.pmx_moe_dense_mlp_set_rows(0)
+    buf = torch.zeros(4 * 160 * 8, dtype=torch.int64, device="cuda")
+    assert lib.pmx_moe_set_stamp_buffer(C.c_void_p(buf.data_ptr()), buf.numel() * 8) == 4
+    try:
+        y = F.moe_dense_mlp(x, inv, off, wu, w2)
+        torch.cuda.synchronize()
+        ids = (C.c_int32 * 8)()
+        assert lib.pmx_moe_stamp_slots(ids, 8) == 1 and ids[0] == 4
+    finally:
+        lib.pmx_moe_set_stamp_buffer(None, 0)
+    assert torch.equal(y, base_y)
+    s = buf.view(4, 160, 8)[0].cpu().numpy()
+    active = s[:, 0] > 0
+    assert active.sum() >= 1
+    assert (s[active, 6] >= s[active, 1]).all() and (s[active, 1] >= s[active, 0]).all()
+
+
 def test_block_dense_decode_path_equals_the_routed_path(F):
     """MoeFeedForward with the router + dense gate/up path (decode-size batch) against the
     same block with that path switched off, eagerly and replayed from a CUDA graph."""
