@@ -52,6 +52,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tt = p.tile_tok, ft = p.tile_feat;
   const int wrows = SWIGLU ? 2 * ft : ft;            // weight rows per stage
+  // weight rows on MMA-M without SwiGLU and ft = 256: two 128-row tiles of consecutive
+  // features per stage (one 256-row copy, two MMAs, accumulator columns [0,tt) and [tt,2tt))
+  const bool two_tiles = MODE == 1 && !SWIGLU && ft == 256;
   const uint32_t tok_bytes = tt * 128, w_bytes = wrows * 128;
   const uint32_t stage_bytes = tok_bytes + w_bytes;
   Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)p.stages * stage_bytes);
@@ -99,7 +102,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     sh->discard = 0;
     WorkIter guess;
     guess.init(p, p.E);
-    if (guess.next_item < guess.panel_end && guess.u_end - guess.u >= 16) {
+    if (guess.next_item < guess.panel_end && guess.u_end - guess.u >= ft / 8) {
       pre_e = guess.next_item;
       pre_f0 = (int)guess.u * 8;
       pre_n = p.stages < p.kblocks ? p.stages : p.kblocks;
@@ -293,7 +296,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
             } else {
               const uint64_t bdesc = smem_desc_sw128(tok_addr + koff);
               umma_f16(d_tmem, smem_desc_sw128(w_addr + koff), bdesc, idesc, accum);
-              if (SWIGLU)
+              if (SWIGLU || two_tiles)
                 umma_f16(d_tmem + tt, smem_desc_sw128(w_addr + 128 * 128 + koff), bdesc, idesc, accum);
             }
           }
@@ -320,7 +323,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
     T* y = reinterpret_cast<T*>(p.y);
     float* yp = reinterpret_cast<float*>(p.y);
     const T* bias = reinterpret_cast<const T*>(p.bias);
-    const int acc_cols = MODE == 0 ? wrows : (SWIGLU ? 2 * tt : tt);   // accumulator columns in use
+    const int acc_cols = MODE == 0 ? wrows : (SWIGLU || two_tiles ? 2 * tt : tt);   // accumulator columns in use
     int map_expert = -1;
     if (DENSE) {
       pdl_wait();   // the routing (invert_permutation, expert_offset) is complete from here on
@@ -469,11 +472,14 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
       } else {
         const int f = it.f0 + q * 32 + lane;  // output feature of this thread
         const bool f_ok = f < p.n_out && q * 32 + lane < it.fn;
+        const int f2 = f + 128;               // two tiles per stage: its feature in the second tile
+        const bool f2_ok = two_tiles && f2 < p.n_out && q * 32 + lane + 128 < it.fn;
         float bg = 0.f, bu = 0.f;
         if (bias && f_ok) {
           bg = Elem<T>::to_f(bias[(int64_t)it.e * p.w_pitch + f]);
           if (SWIGLU) bu = Elem<T>::to_f(bias[(int64_t)it.e * p.w_pitch + p.n_out + f]);
         }
+        if (bias && f2_ok) bu = Elem<T>::to_f(bias[(int64_t)it.e * p.w_pitch + f2]);
         // up to 32 token columns per round: their tensor-memory loads are all in flight before
         // the one wait (a tcgen05.ld round trip costs several hundred ns).  Not more: the
         // registers of 64 columns would keep a CTA of this kernel from sharing an SM with a
@@ -486,7 +492,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
           for (int ch = 0; ch < 2; ++ch) {
             if (c + ch * 16 < tt && it.row0 + c + ch * 16 < it.row_end) {
               tmem_ld16(taddr + c + ch * 16, g[ch]);
-              if (SWIGLU) tmem_ld16(taddr + tt + c + ch * 16, u[ch]);
+              if (SWIGLU || two_tiles) tmem_ld16(taddr + tt + c + ch * 16, u[ch]);
             }
           }
           tmem_wait_ld();
@@ -503,6 +509,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                     yp[((int64_t)it.ks * p.M + row) * p.n_out + f] = v;
                   else
                     y[(int64_t)row * p.n_out + f] = Elem<T>::from_f(v);
+                }
+                if (!DENSE && row < it.row_end && f2_ok) {
+                  const float v = u[ch][i] + bu;
+                  if (partial)
+                    yp[((int64_t)it.ks * p.M + row) * p.n_out + f2] = v;
+                  else
+                    y[(int64_t)row * p.n_out + f2] = Elem<T>::from_f(v);
                 }
               }
             }
@@ -625,6 +638,17 @@ bool plan_gemm_tc(int64_t M, int64_t N, int64_t K, int E, int dtype, int epilogu
   }
   if (pl.split_k > 1 && n_out % 4) return false;
   const bool kernel_swiglu = swiglu && pl.split_k == 1;
+  // Weight rows on MMA-M without the SwiGLU epilogue (down projection, dense linears): a stage
+  // of 128 rows is 16 KB, and a CTA's time is set by its number of k-block rounds (producer
+  // and MMA threads are single threads), so when every working CTA has at least 256 rows of
+  // one panel the stage holds two 128-row tiles: half as many rounds for the same bytes.
+  if (pl.kernel == PMX_GEMM_TC_WEIGHTS_M && !swiglu && pl.split_k == 1 && pl.balanced && want_sk != 1 &&
+      !(user && user->tile_feat) && pl.tile_tok <= 128 && n_out % 256 == 0) {
+    const int64_t act = M < E ? M : E;
+    const int64_t panels = act * (int64_t)ceil_div((int64_t)(avg_rows < 1 ? 1 : avg_rows), pl.tile_tok);
+    const int64_t ctas = sms < 128 ? sms : 128;
+    if (panels * (n_out / 8) >= 32 * ctas) pl.tile_feat = 256;
+  }
   if (!kernel_swiglu && pl.kernel == PMX_GEMM_TC_TOKENS_M && !(user && user->tile_feat) && swiglu)
     pl.tile_feat = pow2_at_least(N, 16, 256);
   const size_t stage = (size_t)(pl.tile_tok + (kernel_swiglu ? 2 : 1) * pl.tile_feat) * 128;

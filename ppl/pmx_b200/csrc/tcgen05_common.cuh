@@ -308,9 +308,10 @@ struct WorkIter {
           const int c2 = c - extra * (base + 1);
           panel = extra + c2 / base; idx = c2 % base; n = base;
         }
+        const long long tile_units = p.tile_feat / 8;      // 16, or 32 with two 128-row tiles per stage
         const long long share = (units + n - 1) / n;
-        const long long pieces = (share + 15) / 16;
-        const long long per_cta = 16 * pieces;
+        const long long pieces = (share + tile_units - 1) / tile_units;
+        const long long per_cta = tile_units * pieces;
         next_item = panel;
         panel_end = panel + 1;
         u = idx * per_cta;
@@ -357,9 +358,10 @@ struct WorkIter {
       it.row_end = s_off[e + 1];
       it.kb0 = it.ks * p.kb_per_split;
       it.kb1 = min(p.kblocks, it.kb0 + p.kb_per_split);
-      // my units of this panel, a whole 128-row tile (16 units) at a time
+      // my units of this panel, a whole tile (16 units of 8 rows, or 32) at a time
       const int seg = (int)(u_end - u);
-      const int take = seg < 16 ? seg : 16;
+      const int tile_units = p.tile_feat / 8;
+      const int take = seg < tile_units ? seg : tile_units;
       it.f0 = (int)u * 8;
       it.fn = take * 8;
       item = panel;
