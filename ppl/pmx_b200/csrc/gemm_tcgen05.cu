@@ -43,7 +43,7 @@ namespace {
 
 #include "tcgen05_common.cuh"
 
-template <typename T, int MODE, bool SWIGLU, bool DENSE = false>
+template <typename T, int MODE, bool SWIGLU, bool DENSE = false, bool TWO = false>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
                        const __grid_constant__ CUtensorMap map_w,
@@ -54,7 +54,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x,
   const int wrows = SWIGLU ? 2 * ft : ft;            // weight rows per stage
   // weight rows on MMA-M without SwiGLU and ft = 256: two 128-row tiles of consecutive
   // features per stage (one 256-row copy, two MMAs, accumulator columns [0,tt) and [tt,2tt))
-  const bool two_tiles = MODE == 1 && !SWIGLU && ft == 256;
+  // (a template flag: as a run-time test inside the MMA issuer's loop it made every launch of
+  // the one-tile kernel slower, 69 against 49 us for the one-token down projection)
+  constexpr bool two_tiles = TWO;
+  static_assert(!TWO || (MODE == 1 && !SWIGLU && !DENSE), "two tiles per stage: weight rows on MMA-M, no SwiGLU");
   const uint32_t tok_bytes = tt * 128, w_bytes = wrows * 128;
   const uint32_t stage_bytes = tok_bytes + w_bytes;
   Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)p.stages * stage_bytes);
@@ -548,10 +551,10 @@ size_t smem_bytes_for(const TcPlan& plan, bool swiglu, int E) {
   return 1024 + stage * plan.stages + sizeof(Shared) + 2 * (size_t)(E + 1) * sizeof(int) + kRowMapBytes;
 }
 
-template <typename T, int MODE, bool SWIGLU>
+template <typename T, int MODE, bool SWIGLU, bool TWO = false>
 int launch_inst(const CUtensorMap& mx, const CUtensorMap& mw, const SmallBoxMaps& mws, const Params& p, int grid,
                 size_t smem, cudaStream_t s) {
-  auto kern = grouped_gemm_tc_kernel<T, MODE, SWIGLU>;
+  auto kern = grouped_gemm_tc_kernel<T, MODE, SWIGLU, false, TWO>;
   PMX_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   void* args[] = {(void*)&mx, (void*)&mw, (void*)&mws, (void*)&p};
   return launch_pdl((const void*)kern, dim3(grid), dim3(kThreads), smem, s, args);
@@ -759,6 +762,10 @@ int launch_gemm_tc(const void* x, const int64_t* off, const void* w, const void*
     else        { if (bf) PMX_TC_LAUNCH(__nv_bfloat16, 0, false); else PMX_TC_LAUNCH(__half, 0, false); }
   } else {
     if (swiglu) { if (bf) PMX_TC_LAUNCH(__nv_bfloat16, 1, true); else PMX_TC_LAUNCH(__half, 1, true); }
+    else if (plan.tile_feat == 256) {
+      if (bf) st = launch_inst<__nv_bfloat16, 1, false, true>(mx, mw, mws, p, grid, smem, s);
+      else st = launch_inst<__half, 1, false, true>(mx, mw, mws, p, grid, smem, s);
+    }
     else        { if (bf) PMX_TC_LAUNCH(__nv_bfloat16, 1, false); else PMX_TC_LAUNCH(__half, 1, false); }
   }
 #undef PMX_TC_LAUNCH
